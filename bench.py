@@ -1,0 +1,366 @@
+"""Benchmark of the training-step hot path: fwd + bwd + Adam steps/s of the data-parallel
+wide MLP (4096 -> 8192 -> 8192 -> 4096, f32, global batch 65536, MSE, TF32 tensor-core
+GEMMs) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--precision tf32|fp32]
+
+N > 1 is launched by torchrun (one process per GPU); torch.distributed (gloo) carries only
+the rendezvous, barriers and the max-over-ranks of the timings, the gradients travel through
+the library's own NCCL communicator.  Rank 0 prints one JSON line.
+
+Keys beyond the base contract:
+  roofline      dominant kernel (the tcgen05 GEMM): algorithmic flop / event-timed duration,
+                against the measured dense peak in MEASURED_PEAKS.json (bf16/2 for TF32)
+  cpu_baseline  the CPU oracle (a restatement of the reference's single-threaded AVX2 path)
+                timed on a bounded row slice of the same workload and extrapolated
+  e2e           the same step including, every step, the upload of that step's batch from
+                pinned host memory and the read-back of the loss
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+DIMS = [4096, 8192, 8192, 4096]
+GLOBAL_BATCH = 65536
+SEED = 4
+METRIC = "fwd+bwd+Adam steps/s (MLP 4096-8192-8192-4096, global batch 65536)"
+
+
+def flop_per_step(batch: int) -> float:
+    """2*M*N*K for forward and dW of every layer, dX for every layer but the first."""
+    fwd = sum(2.0 * batch * DIMS[i] * DIMS[i + 1] for i in range(3))
+    dx = sum(2.0 * batch * DIMS[i] * DIMS[i + 1] for i in range(1, 3))
+    return 2.0 * fwd + dx
+
+
+def n_params() -> int:
+    return sum(DIMS[i] * DIMS[i + 1] + DIMS[i + 1] for i in range(3))
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def init_params(rng):
+    """Kaiming-uniform weights U(-sqrt(6/fan_in), sqrt(6/fan_in)), zero biases (synthetic, seed 4)."""
+    ws, bs = [], []
+    for i in range(3):
+        bound = np.sqrt(6.0 / DIMS[i])
+        ws.append(rng.uniform(-bound, bound, (DIMS[i], DIMS[i + 1])).astype(np.float32))
+        bs.append(np.zeros(DIMS[i + 1], np.float32))
+    return ws, bs
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons during the timed region (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.path = device, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        self.proc.terminate()   # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                c = [x.strip() for x in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    sm.append(float(c[1])); mx.append(float(c[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                    if v.lower() == "active":
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+class Dist:
+    """Rendezvous and host-side reductions for N > 1 (torch.distributed, gloo backend)."""
+
+    def __init__(self, n_gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            import torch.distributed as dist
+            dist.init_process_group(backend="gloo", rank=self.rank, world_size=self.world)
+            self.dist = dist
+        if n_gpus != self.world:
+            raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE is {self.world}: launch N > 1 with torch.distributed.run")
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def max(self, v: float) -> float:
+        if not self.dist:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def sum(self, v: float) -> float:
+        if not self.dist:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t[0])
+
+    def close(self):
+        if self.dist:
+            self.dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------ CPU arm
+def cpu_baseline(sample_rows: int = 32):
+    """Times the CPU oracle on `sample_rows` batch rows of the workload (all three layers, forward,
+    backward) plus one full-size Adam update, single thread as the reference is, and extrapolates the
+    row-proportional part to the global batch."""
+    ora = entry.load_oracle()
+    rng = np.random.default_rng(SEED)
+    ws, bs = init_params(rng)
+    x = rng.standard_normal((sample_rows, DIMS[0]), dtype=np.float32)
+    t = rng.standard_normal((sample_rows, DIMS[-1]), dtype=np.float32)
+    st = ora.MlpState(ws, bs)
+    t0 = time.perf_counter()
+    ora.mlp_step(st, x, t, loss_kind=ora.LOSS_MSE, do_adam=False, as_written=True)
+    t_rows = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for l in range(3):
+        ora.adam_update(st.w[l].reshape(-1), st.gw[l].reshape(-1), st.mw[l].reshape(-1), st.vw[l].reshape(-1), 1)
+        ora.adam_update(st.b[l], st.gb[l], st.mb[l], st.vb[l], 1)
+    t_adam = time.perf_counter() - t0
+    step_s = t_rows * (GLOBAL_BATCH / sample_rows) + t_adam
+    return {"value": 1.0 / step_s, "unit": "steps/s", "cores": 1, "kind": "port",
+            "sample": f"{sample_rows} of {GLOBAL_BATCH} batch rows through all layers fwd+bwd ({t_rows:.2f} s, scaled by rows) "
+                      f"+ full Adam over {n_params()} parameters ({t_adam:.2f} s); reference-style AVX2 path with its operand copies"}
+
+
+def run_reference(args, d: Dist):
+    if d.rank != 0:
+        return
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        vals.append(cpu_baseline())
+    base = vals[-1]
+    v = float(np.median([b["value"] for b in vals]))
+    base["value"] = v
+    line = {"metric": METRIC, "value": v, "unit": "steps/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": "C5 data-parallel wide MLP 4096-8192-8192-4096, global batch 65536, MSE, Adam",
+                       "note": "the reference is single-threaded CPU code with no multi-device path; timed on one host core"},
+            "cpu_baseline": base, "e2e": {"value": v, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------ GPU arm
+def run_gpu(args, d: Dist):
+    ts = entry.load_package()
+    lib = ts._ffi.lib()
+    ts.set_default_device(d.local_rank)
+    prec = {"tf32": ts.TF32, "fp32": ts.FP32}[args.precision]
+    ts.set_matmul_precision(prec)
+    if d.world > 1:
+        ids = [ts.distributed.get_unique_id() if d.rank == 0 else None]
+        d.dist.broadcast_object_list(ids, src=0)
+        ts.distributed.init(ids[0], d.rank, d.world)
+
+    r0, r1 = ts.distributed.shard_rows(GLOBAL_BATCH, d.rank, d.world)
+    local = r1 - r0
+    rng = np.random.default_rng(SEED)
+    ws, bs = init_params(rng)                      # identical on every rank
+    W = [ts.Tensor.from_slice(w, w.shape).with_requires_grad() for w in ws]
+    B = [ts.Tensor.from_slice(b, b.shape).with_requires_grad() for b in bs]
+    del ws, bs
+    params = [p for pair in zip(W, B) for p in pair]
+    opt = ts.Adam.with_learning_rate(1e-3)
+    opt.add_parameters(params)
+    if d.world > 1:
+        ts.distributed.register_parameters(params)
+        opt.grad_scale = 1.0 / d.world             # per-rank mean losses -> gradient of the global mean
+
+    # this rank's rows of the synthetic batch, in pinned host memory (two slots for the prefetching e2e loop)
+    rng_local = np.random.default_rng([SEED, d.rank])
+    pins_x = [ts.PinnedBuffer(local * DIMS[0]) for _ in range(2)]
+    pins_t = [ts.PinnedBuffer(local * DIMS[-1]) for _ in range(2)]
+    for px, pt in zip(pins_x, pins_t):
+        px.array[:] = rng_local.standard_normal(local * DIMS[0], dtype=np.float32)
+        pt.array[:] = rng_local.standard_normal(local * DIMS[-1], dtype=np.float32)
+
+    def step(X, T):
+        h = X
+        for i in range(3):
+            h = h.matmul(W[i]).add_tensor(B[i])
+            if i < 2:
+                h = h.relu()
+        loss = h.sub_tensor(T).pow_scalar(2.0).mean()
+        loss.backward(None)
+        opt.step(params)
+        opt.zero_grad(params)
+        return loss
+
+    X = ts.Tensor.from_pinned_async(pins_x[0], [local, DIMS[0]])
+    T = ts.Tensor.from_pinned_async(pins_t[0], [local, DIMS[-1]])
+
+    for _ in range(args.warmup):
+        loss = step(X, T)
+    ts.synchronize()
+
+    # ---- timed region 1: inputs resident in HBM
+    ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
+    lib.ts_profile_reset()
+    lib.ts_profile_enable(1)
+    sampler = ClockSampler(d.local_rank)
+    d.barrier(); ts.synchronize()
+    sampler.start()
+    launches0 = int(lib.ts_launch_count())
+    lib.ts_event_record(ev0, None)
+    for _ in range(args.steps):
+        loss = step(X, T)
+    lib.ts_event_record(ev1, None)
+    ts.synchronize(); d.barrier()
+    ms = float(lib.ts_event_elapsed_ms(ev0, ev1))
+    launches = int(lib.ts_launch_count()) - launches0
+    clocks = sampler.stop()
+    lib.ts_profile_enable(0)
+    ts._ffi.check(lib.ts_profile_collect(), "profile")
+    final_loss = loss.value()
+    ms = d.max(ms)
+    ms_per_step = ms / args.steps
+    value = 1000.0 / ms_per_step
+
+    def prof(cls):
+        n, t, w = C.c_ulonglong(), C.c_double(), C.c_double()
+        lib.ts_profile_get(cls, C.byref(n), C.byref(t), C.byref(w))
+        return int(n.value), float(t.value), float(w.value)
+
+    peaks = measured_peaks()
+    cls = 0 if prec == ts.TF32 else 1
+    gl, gms, gwork = prof(cls)
+    tf32_peak = peaks["bf16_sustained"] / 2.0   # no TF32 entry is measured: half the measured sustained bf16 rate
+    roof = {"bound": "tensor", "kernel": "gemm_tf32_kernel (tcgen05)" if cls == 0 else "sgemm_kernel (FFMA)",
+            "achieved": (gwork / (gms * 1e-3) / 1e12) if gms > 0 else None, "peak": tf32_peak, "unit": "TFLOP/s",
+            "frac": None, "traffic": None, "launches": gl, "avg_launch_ms": gms / gl if gl else None,
+            "peak_source": f"{peaks['source']}: bf16_tflops_sustained / 2 (derived; TF32 runs at half the bf16 rate)",
+            "share_of_step": gms / ms if ms > 0 else None}
+    if roof["achieved"]:
+        roof["frac"] = roof["achieved"] / roof["peak"]
+    al, ams, awork = prof(4)
+    el, ems, ework = prof(2)
+    rl, rms, rwork = prof(3)
+    other = {"adam": {"launches": al, "GBps": awork / (ams * 1e-3) / 1e9 if ams > 0 else None, "frac_of_hbm": None},
+             "elementwise": {"launches": el, "GBps": ework / (ems * 1e-3) / 1e9 if ems > 0 else None},
+             "reduce": {"launches": rl, "GBps": rwork / (rms * 1e-3) / 1e9 if rms > 0 else None},
+             "hbm_peak_GBps": peaks["hbm_gbs"]}
+    if other["adam"]["GBps"]:
+        other["adam"]["frac_of_hbm"] = other["adam"]["GBps"] / peaks["hbm_gbs"]
+
+    # ---- timed region 2: end to end, each step's batch uploaded from pinned memory, loss read back
+    h2d = 4 * local * (DIMS[0] + DIMS[-1])
+    d.barrier(); ts.synchronize()
+    nxt = (ts.Tensor.from_pinned_async(pins_x[1], [local, DIMS[0]]), ts.Tensor.from_pinned_async(pins_t[1], [local, DIMS[-1]]))
+    t0 = time.perf_counter()
+    lib.ts_event_record(ev0, None)
+    for s in range(args.steps):
+        cur = nxt
+        slot = s % 2   # the slot the step before last used is free again: its upload has been consumed
+        if s + 1 < args.steps:
+            nxt = (ts.Tensor.from_pinned_async(pins_x[slot], [local, DIMS[0]]),
+                   ts.Tensor.from_pinned_async(pins_t[slot], [local, DIMS[-1]]))
+        l = step(*cur)
+        _ = l.value()       # device -> host read of the step's result
+    lib.ts_event_record(ev1, None)
+    ts.synchronize(); d.barrier()
+    e2e_ms = d.max(float(lib.ts_event_elapsed_ms(ev0, ev1)))
+    e2e = {"value": 1000.0 * args.steps / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": h2d * d.world,
+           "d2h_bytes_per_step": 4 * d.world, "wall_ms_per_step_rank0": 1000.0 * (time.perf_counter() - t0) / args.steps}
+
+    stats = ts.allocator_stats()
+    line = {"metric": METRIC, "value": value, "unit": "steps/s", "n_gpus": d.world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "tf32" if prec == ts.TF32 else "f32", "data": "synthetic",
+            "config": {"workload": "C5 data-parallel wide MLP 4096-8192-8192-4096 f32, Kaiming-uniform init, ReLU, MSE, Adam(1e-3)",
+                       "global_batch": GLOBAL_BATCH, "rows_per_gpu": local, "parallelism": f"dp{d.world}", "seed": SEED,
+                       "gemm_precision": args.precision, "l2": "inputs and activations (>= 1 GiB each) are larger than the 126 MB L2",
+                       "allreduce": "NCCL sum of parameter gradients overlapped with backward" if d.world > 1 else "none"},
+            "tflops_per_gpu": flop_per_step(local) / (ms_per_step * 1e-3) / 1e12,
+            "tflops_total": flop_per_step(GLOBAL_BATCH) / (ms_per_step * 1e-3) / 1e12,
+            "loss": final_loss, "roofline": roof, "other_kernels": other, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "peak_device_bytes": stats["peak_bytes_in_use"]}
+    if d.rank == 0:
+        if d.world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if d.world > 1:
+        ts.distributed.finalize()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    d = Dist(args.gpus)
+    try:
+        if args.impl == "reference":
+            run_reference(args, d)
+        else:
+            run_gpu(args, d)
+    finally:
+        d.close()
+
+
+if __name__ == "__main__":
+    main()

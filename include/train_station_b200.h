@@ -1,0 +1,292 @@
+/*
+ * train_station_b200.h -- C ABI of libtrain_station_b200.so
+ *
+ * The device side of train-station's training-step hot path (MLP forward, gradtrack
+ * backward(), Adam::step) for NVIDIA B200 (sm_100a).  Plain pointers and sizes only.
+ * Reference citations are paths inside the train-station repository.
+ *
+ * Conventions, all inherited from the reference's FFI (src/cuda/cuda_wrapper.h:10-31,
+ * src/cuda/cuda_wrapper.cpp:37-94, src/cuda/mod.rs:139-208):
+ *   - sizes are counts of f32 elements, never bytes;
+ *   - tensors are row-major contiguous f32; matmul is A[m,k] . B[k,n] -> C[m,n];
+ *   - bool results: true = success; pointer results: NULL = failure; nothing throws,
+ *     nothing aborts; ts_last_error() holds the reason (per host thread);
+ *   - `stream == NULL` means the library's per-device compute stream;
+ *   - the caller owns every buffer it allocates;
+ *   - the current device, the autograd tape and the grad mode are per host thread,
+ *     as in the reference (src/device.rs:567, src/gradtrack/engine.rs:697-699), so
+ *     one host thread (or process) drives one GPU.
+ * There is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef TRAIN_STATION_B200_H
+#define TRAIN_STATION_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================================================================================
+ * 1. The reference's fifteen symbols, same names, same meaning
+ *    (src/cuda/cuda_wrapper.h:10-31; Rust imports at src/cuda/mod.rs:139-208).
+ * =================================================================================== */
+
+/* cuda_wrapper.h:10-11.  Initialises the runtime for this thread's current device. */
+bool cuda_ffi_initialize(void);
+void cuda_ffi_cleanup(void);
+
+/* cuda_wrapper.h:14-16.  The stub returns 0 devices; this returns the real count. */
+int get_cuda_device_count(void);
+bool set_cuda_device(int device_id);
+int get_current_cuda_device(void);
+
+/* cuda_wrapper.h:19-21.  size in f32 elements; kind 0 = host->device, 1 = device->host
+ * (src/cuda/memory.rs:73,95); kind 2 = device->device is an extension.  Memory comes
+ * from the caching allocator of the current device.  cuda_memcpy returns after the
+ * copy has completed. */
+float* cuda_malloc(unsigned long long size);
+void cuda_free(float* ptr);
+bool cuda_memcpy(float* dst, const float* src, unsigned long long size, int kind);
+
+/* cuda_wrapper.h:24-25 */
+void* create_cuda_stream(void);
+void destroy_cuda_stream(void* stream);
+
+/* cuda_wrapper.h:28-31.  Device pointers.  launch_matmul_kernel uses the process-wide
+ * GEMM precision mode (ts_set_matmul_precision). */
+bool launch_add_kernel(const float* a, const float* b, float* result, unsigned long long size, void* stream);
+bool launch_sub_kernel(const float* a, const float* b, float* result, unsigned long long size, void* stream);
+bool launch_mul_kernel(const float* a, const float* b, float* result, unsigned long long size, void* stream);
+bool launch_matmul_kernel(const float* a, const float* b, float* result, unsigned long long m,
+                          unsigned long long n, unsigned long long k, void* stream);
+
+/* ===================================================================================
+ * 2. Status, streams, allocator
+ * =================================================================================== */
+
+/* Pattern of libtorch_get_last_error (libtorch-validation/src/ffi/libtorch_wrapper.h:113-115).
+ * Valid until the next failing call on the same thread.  Never NULL. */
+const char* ts_last_error(void);
+/* Blocks until `stream` (NULL: the compute stream) is idle, then reports any deferred
+ * device-side error (for example a bounded wait inside a kernel that gave up). */
+bool ts_sync_stream(void* stream);
+/* The per-device compute stream as a cudaStream_t, for callers that time with events. */
+void* ts_compute_stream(void);
+/* Page-locked host memory for uploads that overlap compute (size in f32 elements). */
+float* ts_host_alloc_pinned(unsigned long long size);
+void ts_host_free_pinned(float* ptr);
+/* Asynchronous variant of cuda_memcpy on `stream`; host memory should be pinned. */
+bool ts_memcpy_async(float* dst, const float* src, unsigned long long size, int kind, void* stream);
+
+/* Device caching allocator; replaces one std::alloc per tensor
+ * (src/tensor/core/allocation.rs:105-118, src/tensor/core/utils.rs:145-171). */
+typedef struct ts_allocator_stats {
+    unsigned long long bytes_in_use;     /* handed out and not yet freed */
+    unsigned long long bytes_reserved;   /* obtained from the driver, in use or cached */
+    unsigned long long peak_bytes_in_use;
+    unsigned long long driver_allocations; /* calls that reached the driver */
+    unsigned long long cache_hits;
+} ts_allocator_stats;
+bool ts_allocator_get_stats(ts_allocator_stats* out);
+void ts_allocator_release_cached(void);              /* return cached blocks to the driver */
+void ts_allocator_set_limit(unsigned long long bytes); /* 0 = no limit; for out-of-memory tests */
+
+/* CUDA events on a stream of this library, for callers that time kernels without any other CUDA binding.
+ * ts_event_elapsed_ms waits for `end` and returns the milliseconds between the two records (negative on error). */
+void* ts_event_create(void);
+void ts_event_destroy(void* event);
+bool ts_event_record(void* event, void* stream);
+float ts_event_elapsed_ms(void* start, void* end);
+/* Kernels launched by this library on this thread's device since the library was loaded. */
+unsigned long long ts_launch_count(void);
+/* Built-in per-kernel-class timing.  While enabled, every launch is bracketed by two events on its own
+ * stream; ts_profile_collect waits for the compute stream and adds the measured durations to the totals.
+ * Classes: 0 tensor-core GEMM, 1 FP32 GEMM, 2 elementwise, 3 reductions, 4 Adam.
+ * `work` is the algorithmic work of the class in flop (GEMM) or bytes (the others). */
+#define TS_PROFILE_CLASSES 5
+void ts_profile_enable(int enabled);
+bool ts_profile_collect(void);
+void ts_profile_reset(void);
+bool ts_profile_get(int kernel_class, unsigned long long* launches, double* total_ms, double* work);
+
+/* GEMM precision: 0 = FP32 (FFMA, the reference's summation order),
+ * 1 = TF32 tensor cores (tcgen05), 2 = 3xTF32 split on tensor cores (FP32-accurate).
+ * Process-wide; the environment variable TS_MATMUL_PRECISION (fp32|tf32|tf32x3) sets the default. */
+bool ts_set_matmul_precision(int mode);
+int ts_get_matmul_precision(void);
+/* Lazy epilogue fusion in the tensor engine (bias add / ReLU / ReLU-mask folded into the
+ * producing GEMM).  1 = on (default), 0 = every op launches its own kernel. */
+void ts_set_fusion(int enabled);
+int ts_get_fusion(void);
+
+/* ===================================================================================
+ * 3. Raw kernel launchers beyond the stub set (device pointers, element counts)
+ * =================================================================================== */
+
+/* div.rs:347-420: IEEE division, no trap on zero. */
+bool launch_div_kernel(const float* a, const float* b, float* result, unsigned long long size, void* stream);
+/* Row-broadcast add with optional ReLU: out[i,j] = act(z[i,j] + bias[j])
+ * (add.rs:107-146 + broadcasting.rs:299-333 + relu.rs:77-90 in one pass). */
+bool launch_bias_act_kernel(const float* z, const float* bias, float* out, unsigned long long rows,
+                            unsigned long long cols, int relu, void* stream);
+/* relu.rs:175-215: max(x,0) with NaN -> 0 and -0 -> +0. */
+bool launch_relu_kernel(const float* x, float* out, unsigned long long size, void* stream);
+/* grad_fn/ops/relu.rs:4-16: gi = ref > 0 ? go : 0.  `ref` may be the ReLU input or its
+ * output (relu(x) > 0 <=> x > 0). */
+bool launch_relu_backward_kernel(const float* ref, const float* grad_out, float* grad_in,
+                                 unsigned long long size, void* stream);
+/* pow.rs:195-240 with exponent 2 (x*x) and grad_fn/ops/pow.rs:5-27 (go * (2*x)). */
+bool launch_square_kernel(const float* x, float* out, unsigned long long size, void* stream);
+bool launch_square_backward_kernel(const float* x, const float* grad_out, float* grad_in,
+                                   unsigned long long size, void* stream);
+/* grad_fn/ops/mul.rs:4-49: ga = go*b, gb = go*a.  Either output may be NULL. */
+bool launch_mul_backward_kernel(const float* a, const float* b, const float* grad_out, float* grad_a,
+                                float* grad_b, unsigned long long size, void* stream);
+/* grad_fn/ops/div.rs:4-49: ga = go/b, gb = -((go*a)/(b*b)).  Either output may be NULL. */
+bool launch_div_backward_kernel(const float* a, const float* b, const float* grad_out, float* grad_a,
+                                float* grad_b, unsigned long long size, void* stream);
+/* out = alpha * x  (negation for grad_fn/ops/sub.rs:26-31 is alpha = -1) */
+bool launch_scale_kernel(const float* x, float alpha, float* out, unsigned long long size, void* stream);
+/* init/basic.rs:304-360 (fill) */
+bool launch_fill_kernel(float* out, float value, unsigned long long size, void* stream);
+/* out[i] = scale * (*scalar): backward of sum()/mean() without a host round trip
+ * (grad_fn/reductions/sum.rs:4-16, mean.rs:4-30: scale = 1 or 1/numel as f32). */
+bool launch_fill_from_scalar_kernel(float* out, const float* scalar, float scale,
+                                    unsigned long long size, void* stream);
+/* reductions/sum.rs:80-143 and mean.rs:48-110: out[0] = sum(x) or sum(x)/(f32)size.
+ * Deterministic two-level tree (the reference adds sequentially).  `scratch` needs
+ * ts_reduce_scratch_elems() f32 elements of device memory. */
+unsigned long long ts_reduce_scratch_elems(void);
+bool launch_sum_kernel(const float* x, float* out, unsigned long long size, int mean, float* scratch,
+                       void* stream);
+/* sum_dims(&[0]) of a [rows, cols] matrix (reductions/sum.rs:225-306): out[j] = sum_i g[i,j].
+ * `scratch` needs ts_colsum_scratch_elems(rows, cols) elements. */
+unsigned long long ts_colsum_scratch_elems(unsigned long long rows, unsigned long long cols);
+bool launch_colsum_kernel(const float* g, float* out, unsigned long long rows, unsigned long long cols,
+                          float* scratch, void* stream);
+/* Fused ReLU backward + bias gradient: grad_in = ref > 0 ? go : 0 and
+ * bias_grad[j] = sum_i grad_in[i,j] in one pass over the data. */
+bool launch_relu_backward_colsum_kernel(const float* ref, const float* grad_out, float* grad_in,
+                                        float* bias_grad, unsigned long long rows,
+                                        unsigned long long cols, float* scratch, void* stream);
+
+/* General GEMM: C[m,n] = op(A) . op(B) with op = transpose when trans* != 0.
+ * A is stored [m,k] (or [k,m] when trans_a), B is stored [k,n] (or [n,k] when trans_b),
+ * all row-major contiguous.  Covers matmul forward (matmul/mod.rs:572-611) and the two
+ * backward GEMMs dA = dC . B^T, dB = A^T . dC (grad_fn/ops/matmul.rs:68-80) without the
+ * materialised transposes the reference makes.
+ * Epilogue (applied in this order, each optional):
+ *   bias   != NULL : C[i,j] += bias[j]
+ *   relu   != 0    : C = max(C, 0)
+ *   mask   != NULL : C[i,j] = mask[i,j] > 0 ? C[i,j] : 0      (mask is [m,n])
+ * precision: 0/1/2 as for ts_set_matmul_precision, -1 = the process-wide mode.  Shapes the
+ * tensor-core path cannot take (row strides that are not multiples of 4 elements, or very
+ * small problems) run on the FP32 kernel in every mode. */
+bool launch_gemm_kernel(const float* a, const float* b, float* c, unsigned long long m,
+                        unsigned long long n, unsigned long long k, int trans_a, int trans_b,
+                        const float* bias, int relu, const float* mask, int precision, void* stream);
+
+/* Fused multi-tensor Adam (optimizers/adam/mod.rs:485-556, 635-1030): one launch updates
+ * every tensor.  f1 = 1/bias_correction1, f2 = 1/bias_correction2 as computed on the host
+ * (adam/mod.rs:526-531, 793); grad_scale multiplies every gradient first (1.0, or 1/world
+ * after a gradient all-reduce).  The four pointer tables are host arrays of device pointers. */
+bool launch_adam_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m,
+                                     float* const* v, const unsigned long long* sizes, int n_tensors,
+                                     float lr, float beta1, float beta2, float eps, float weight_decay,
+                                     float f1, float f2, float grad_scale, void* stream);
+
+/* ===================================================================================
+ * 4. Tensor, gradtrack and Adam engine: what the reference's Rust API maps onto
+ * =================================================================================== */
+
+typedef struct ts_tensor ts_tensor;   /* src/tensor/core/mod.rs:231-299 */
+typedef struct ts_adam ts_adam;       /* src/optimizers/adam/mod.rs:201-206 */
+
+/* Constructors (core/utils.rs:121-171, init/basic.rs:137-180,304-360, init/data.rs:227-247).
+ * Every returned handle must be released with ts_tensor_free. */
+ts_tensor* ts_tensor_new(const unsigned long long* dims, int rank);            /* uninitialised */
+ts_tensor* ts_tensor_zeros(const unsigned long long* dims, int rank);
+ts_tensor* ts_tensor_ones(const unsigned long long* dims, int rank);
+ts_tensor* ts_tensor_from_slice(const float* host, const unsigned long long* dims, int rank);
+/* Upload queued on the copy stream; `host` must be pinned and stay valid until the tensor is
+ * first used (the compute stream then waits for the copy). */
+ts_tensor* ts_tensor_from_pinned_async(const float* host, const unsigned long long* dims, int rank);
+void ts_tensor_free(ts_tensor* t);
+
+unsigned long long ts_tensor_id(const ts_tensor* t);
+int ts_tensor_rank(const ts_tensor* t);
+unsigned long long ts_tensor_size(const ts_tensor* t);
+bool ts_tensor_dims(const ts_tensor* t, unsigned long long* dims_out);
+bool ts_tensor_requires_grad(const ts_tensor* t);
+bool ts_tensor_set_requires_grad(ts_tensor* t, bool requires_grad); /* with_requires_grad */
+/* Device pointer of the tensor's data (forces any deferred kernel to run). */
+float* ts_tensor_data_ptr(ts_tensor* t);
+/* Tensor::data() / value(): copies to host after the producing kernels finish. */
+bool ts_tensor_to_host(ts_tensor* t, float* host_out);
+/* Overwrites the data from host memory (data_mut()); bumps the storage version. */
+bool ts_tensor_copy_from_host(ts_tensor* t, const float* host);
+bool ts_tensor_fill(ts_tensor* t, float value);
+
+/* Ops.  Each returns a new tensor and records a GradFn when grad mode is on and an input
+ * requires grad (template: tensor/ops/relu.rs:77-90). */
+ts_tensor* ts_tensor_matmul(ts_tensor* a, ts_tensor* b);       /* matmul/mod.rs:263-310 */
+ts_tensor* ts_tensor_add_tensor(ts_tensor* a, ts_tensor* b);   /* add.rs:107-146 (+ broadcast) */
+ts_tensor* ts_tensor_sub_tensor(ts_tensor* a, ts_tensor* b);   /* sub.rs:121-160 */
+ts_tensor* ts_tensor_mul_tensor(ts_tensor* a, ts_tensor* b);   /* mul.rs:94-135 */
+ts_tensor* ts_tensor_div_tensor(ts_tensor* a, ts_tensor* b);   /* div.rs:109-150 */
+ts_tensor* ts_tensor_relu(ts_tensor* x);                       /* relu.rs:77-90 */
+ts_tensor* ts_tensor_pow_scalar(ts_tensor* x, float exponent); /* pow.rs:79-130; exponent 2 only */
+ts_tensor* ts_tensor_sum(ts_tensor* x);                        /* reductions/sum.rs:80-143 */
+ts_tensor* ts_tensor_mean(ts_tensor* x);                       /* reductions/mean.rs:48-110 */
+
+/* gradtrack (gradtrack/engine.rs:962-1047, core/utils.rs:492-534,634-636). */
+bool ts_tensor_backward(ts_tensor* t, ts_tensor* grad_output /* NULL = ones */);
+ts_tensor* ts_tensor_grad_by_value(const ts_tensor* t);        /* NULL if no gradient */
+void ts_clear_gradients(void);                                 /* engine.rs:812-816 */
+void ts_no_grad_push(void);                                    /* NoGradTrack::new */
+void ts_no_grad_pop(void);                                     /* drop(NoGradTrack) */
+bool ts_is_grad_enabled(void);
+unsigned long long ts_tape_len(void);                          /* recorded operations */
+
+/* Adam (optimizers/adam/mod.rs:91-117 config defaults 1e-3, 0.9, 0.999, 1e-8, 0, false). */
+ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float weight_decay);
+void ts_adam_free(ts_adam* opt);
+bool ts_adam_add_parameter(ts_adam* opt, const ts_tensor* p);  /* adam/mod.rs:287-320 */
+/* Optimizer::step (adam/mod.rs:1036-1044): parameters without a gradient are skipped with
+ * a message in ts_last_error(), as the reference prints and skips.  grad_scale as above. */
+bool ts_adam_step(ts_adam* opt, ts_tensor* const* params, int n, float grad_scale);
+/* Optimizer::zero_grad (adam/mod.rs:1061-1068): clears the whole tape of this thread. */
+void ts_adam_zero_grad(ts_adam* opt, ts_tensor* const* params, int n);
+float ts_adam_learning_rate(const ts_adam* opt);
+void ts_adam_set_learning_rate(ts_adam* opt, float lr);
+unsigned long long ts_adam_step_count(const ts_adam* opt);
+/* Device copies of the moment estimates, for parity checks (NULL if p is not linked). */
+ts_tensor* ts_adam_state_m(const ts_adam* opt, const ts_tensor* p);
+ts_tensor* ts_adam_state_v(const ts_adam* opt, const ts_tensor* p);
+
+/* ===================================================================================
+ * 5. Data parallelism: batch rows sharded over GPUs, one NCCL all-reduce of the parameter
+ *    gradients before Adam.  No counterpart in the reference (it is single-device).
+ * =================================================================================== */
+#define TS_DP_UNIQUE_ID_BYTES 128
+/* Rank 0 creates the id; the caller broadcasts the bytes to the other ranks by any means. */
+bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]);
+bool ts_dp_init(const unsigned char id[TS_DP_UNIQUE_ID_BYTES], int rank, int world_size);
+void ts_dp_finalize(void);
+int ts_dp_world_size(void);   /* 1 when not initialised */
+int ts_dp_rank(void);
+/* Registers the tensors whose gradients are to be summed across ranks.  During
+ * ts_tensor_backward each one's all-reduce is enqueued on a communication stream as soon
+ * as its gradient is final, overlapping the rest of backward; ts_adam_step waits for it. */
+bool ts_dp_register_parameters(ts_tensor* const* params, int n);
+/* Sums `size` elements in place across ranks on the communication stream and makes the
+ * compute stream wait for the result. */
+bool ts_dp_all_reduce(float* data, unsigned long long size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRAIN_STATION_B200_H */

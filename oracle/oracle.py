@@ -1,0 +1,282 @@
+"""ctypes front end of the CPU oracle (oracle/ts_oracle.c) plus an f64 numpy twin.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the CPU-baseline
+leg of the benchmark.  The product package never imports this module.
+
+The C functions restate the reference's f32 arithmetic in the reference's operation
+order (citations beside each function in ts_oracle.c).  The ``*_f64`` functions evaluate
+the same definitions in float64; they are the "truth" against which both the f32
+restatement and the device results are measured when summation order differs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libts_oracle.so")
+_f = C.POINTER(C.c_float)
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside it (gcc, a second or two)."""
+    src = os.path.join(_HERE, "ts_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
+    return _SO
+
+
+class _MlpArgs(C.Structure):
+    _fields_ = [
+        ("layers", C.c_int), ("dims", C.POINTER(C.c_size_t)), ("batch", C.c_size_t),
+        ("w", C.POINTER(_f)), ("b", C.POINTER(_f)), ("gw", C.POINTER(_f)), ("gb", C.POINTER(_f)),
+        ("mw", C.POINTER(_f)), ("vw", C.POINTER(_f)), ("mb", C.POINTER(_f)), ("vb", C.POINTER(_f)),
+        ("x", _f), ("target", _f), ("gx", _f), ("y_out", _f),
+        ("loss_kind", C.c_int), ("relu_last", C.c_int), ("as_written", C.c_int), ("do_adam", C.c_int),
+        ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
+        ("weight_decay", C.c_float), ("step", C.c_uint64),
+    ]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = C.CDLL(build())
+        sz = C.c_size_t
+        for name in ("ora_add", "ora_sub", "ora_mul", "ora_div"):
+            getattr(L, name).argtypes = [_f, _f, _f, sz]
+        L.ora_matmul.argtypes = [_f, _f, _f, sz, sz, sz]
+        L.ora_matmul_naive.argtypes = [_f, _f, _f, sz, sz, sz]
+        L.ora_transpose.argtypes = [_f, _f, sz, sz]
+        L.ora_add_row.argtypes = [_f, _f, _f, sz, sz]
+        L.ora_relu.argtypes = [_f, _f, sz]
+        L.ora_relu_bwd.argtypes = [_f, _f, _f, sz]
+        L.ora_square.argtypes = [_f, _f, sz]
+        L.ora_square_bwd.argtypes = [_f, _f, _f, sz]
+        L.ora_mul_bwd.argtypes = [_f, _f, _f, _f, _f, sz]
+        L.ora_div_bwd.argtypes = [_f, _f, _f, _f, _f, sz]
+        L.ora_neg.argtypes = [_f, _f, sz]
+        L.ora_fill.argtypes = [_f, C.c_float, sz]
+        L.ora_sum.argtypes = [_f, sz]
+        L.ora_sum.restype = C.c_float
+        L.ora_mean.argtypes = [_f, sz]
+        L.ora_mean.restype = C.c_float
+        L.ora_colsum.argtypes = [_f, _f, sz, sz]
+        L.ora_adam_update.argtypes = [_f, _f, _f, _f, sz, C.c_float, C.c_float, C.c_float,
+                                      C.c_float, C.c_float, C.c_uint64]
+        L.ora_mlp_step.argtypes = [C.POINTER(_MlpArgs)]
+        L.ora_mlp_step.restype = C.c_float
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags.c_contiguous
+    return a.ctypes.data_as(_f)
+
+
+def _c(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+# ----------------------------------------------------------------- f32 restatement
+
+def matmul(a, b, naive=False):
+    a, b = _c(a), _c(b)
+    m, k = a.shape
+    k2, n = b.shape
+    assert k == k2
+    c = np.empty((m, n), np.float32)
+    (lib().ora_matmul_naive if naive else lib().ora_matmul)(_p(a), _p(b), _p(c), m, n, k)
+    return c
+
+
+def _binary(name, a, b):
+    a, b = _c(a), _c(b)
+    assert a.shape == b.shape
+    o = np.empty_like(a)
+    getattr(lib(), name)(_p(a), _p(b), _p(o), a.size)
+    return o
+
+
+def add(a, b): return _binary("ora_add", a, b)
+def sub(a, b): return _binary("ora_sub", a, b)
+def mul(a, b): return _binary("ora_mul", a, b)
+def div(a, b): return _binary("ora_div", a, b)
+
+
+def add_row(z, b):
+    z, b = _c(z), _c(b)
+    o = np.empty_like(z)
+    lib().ora_add_row(_p(z), _p(b), _p(o), z.shape[0], z.shape[1])
+    return o
+
+
+def relu(x):
+    x = _c(x)
+    o = np.empty_like(x)
+    lib().ora_relu(_p(x), _p(o), x.size)
+    return o
+
+
+def relu_bwd(x, go):
+    x, go = _c(x), _c(go)
+    gi = np.empty_like(x)
+    lib().ora_relu_bwd(_p(x), _p(go), _p(gi), x.size)
+    return gi
+
+
+def square(x):
+    x = _c(x)
+    o = np.empty_like(x)
+    lib().ora_square(_p(x), _p(o), x.size)
+    return o
+
+
+def square_bwd(x, go):
+    x, go = _c(x), _c(go)
+    gi = np.empty_like(x)
+    lib().ora_square_bwd(_p(x), _p(go), _p(gi), x.size)
+    return gi
+
+
+def mul_bwd(a, b, go):
+    a, b, go = _c(a), _c(b), _c(go)
+    ga, gb = np.empty_like(a), np.empty_like(a)
+    lib().ora_mul_bwd(_p(a), _p(b), _p(go), _p(ga), _p(gb), a.size)
+    return ga, gb
+
+
+def div_bwd(a, b, go):
+    a, b, go = _c(a), _c(b), _c(go)
+    ga, gb = np.empty_like(a), np.empty_like(a)
+    lib().ora_div_bwd(_p(a), _p(b), _p(go), _p(ga), _p(gb), a.size)
+    return ga, gb
+
+
+def neg(x):
+    x = _c(x)
+    o = np.empty_like(x)
+    lib().ora_neg(_p(x), _p(o), x.size)
+    return o
+
+
+def total(x) -> np.float32:
+    x = _c(x)
+    return np.float32(lib().ora_sum(_p(x), x.size))
+
+
+def mean(x) -> np.float32:
+    x = _c(x)
+    return np.float32(lib().ora_mean(_p(x), x.size))
+
+
+def colsum(g):
+    g = _c(g)
+    o = np.empty(g.shape[1], np.float32)
+    lib().ora_colsum(_p(g), _p(o), g.shape[0], g.shape[1])
+    return o
+
+
+def adam_update(p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+    """In place on p, m, v (float32 arrays); step is the global step after increment."""
+    g = _c(g)
+    for a in (p, m, v):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().ora_adam_update(_p(p), _p(g), _p(m), _p(v), p.size, lr, beta1, beta2, eps, weight_decay,
+                          int(step))
+
+
+LOSS_SUM, LOSS_MEAN, LOSS_MSE = 0, 1, 2
+
+
+class MlpState:
+    """Parameters, gradients and Adam moments of an MLP held as float32 numpy arrays."""
+
+    def __init__(self, weights, biases):
+        self.w = [_c(w).copy() for w in weights]
+        self.b = [_c(b).copy() for b in biases]
+        self.gw = [np.zeros_like(w) for w in self.w]
+        self.gb = [np.zeros_like(b) for b in self.b]
+        self.mw = [np.zeros_like(w) for w in self.w]
+        self.vw = [np.zeros_like(w) for w in self.w]
+        self.mb = [np.zeros_like(b) for b in self.b]
+        self.vb = [np.zeros_like(b) for b in self.b]
+        self.step = 0
+
+
+def mlp_step(st: MlpState, x, target=None, loss_kind=LOSS_MSE, relu_last=False, do_adam=True,
+             as_written=False, want_gx=False, want_y=False, lr=1e-3, beta1=0.9, beta2=0.999,
+             eps=1e-8, weight_decay=0.0):
+    """One fwd + bwd (+ Adam) step of the reference's canonical loop. Returns a dict."""
+    x = _c(x)
+    L = len(st.w)
+    dims = (C.c_size_t * (L + 1))(*([st.w[0].shape[0]] + [w.shape[1] for w in st.w]))
+    arr = lambda lst: (_f * L)(*[_p(a) for a in lst])
+    gx = np.empty_like(x) if want_gx else None
+    nout = st.w[-1].shape[1]
+    y = np.empty((x.shape[0], nout), np.float32) if want_y else None
+    tgt = _c(target) if target is not None else None
+    if do_adam:
+        st.step += 1
+    keep = [arr(st.w), arr(st.b), arr(st.gw), arr(st.gb), arr(st.mw), arr(st.vw), arr(st.mb),
+            arr(st.vb)]
+    a = _MlpArgs(L, dims, x.shape[0], *keep, _p(x), _p(tgt) if tgt is not None else None,
+                 _p(gx) if gx is not None else None, _p(y) if y is not None else None,
+                 loss_kind, int(relu_last), int(as_written), int(do_adam), lr, beta1, beta2, eps,
+                 weight_decay, st.step)
+    loss = lib().ora_mlp_step(C.byref(a))
+    return {"loss": np.float32(loss), "gx": gx, "y": y}
+
+
+# ----------------------------------------------------------------------- f64 twin
+
+def matmul_f64(a, b):
+    return np.asarray(a, np.float64) @ np.asarray(b, np.float64)
+
+
+def mlp_step_f64(weights, biases, x, target=None, loss_kind=LOSS_MSE, relu_last=False):
+    """Forward and gradients of the same graph in float64 (no Adam). Returns a dict."""
+    w = [np.asarray(a, np.float64) for a in weights]
+    b = [np.asarray(a, np.float64) for a in biases]
+    h = [np.asarray(x, np.float64)]
+    z = []
+    L = len(w)
+    for l in range(L):
+        zl = h[l] @ w[l] + b[l]
+        z.append(zl)
+        h.append(np.maximum(zl, 0.0) if (l + 1 < L or relu_last) else zl)
+    y = h[-1]
+    if loss_kind == LOSS_SUM:
+        loss, g = y.sum(), np.ones_like(y)
+    elif loss_kind == LOSS_MEAN:
+        loss, g = y.mean(), np.full_like(y, 1.0 / y.size)
+    else:
+        d = y - np.asarray(target, np.float64)
+        loss, g = (d * d).mean(), 2.0 * d / y.size
+    gw, gb = [None] * L, [None] * L
+    for l in reversed(range(L)):
+        if l + 1 < L or relu_last:
+            g = g * (z[l] > 0)
+        gb[l] = g.sum(axis=0)
+        gw[l] = h[l].T @ g
+        g = g @ w[l].T
+    return {"loss": loss, "y": y, "z": z, "gw": gw, "gb": gb, "gx": g}
+
+
+def adam_update_f64(p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+    """Textbook Adam in float64 using the f32-rounded hyper-parameters, out of place."""
+    b1, b2 = float(np.float32(beta1)), float(np.float32(beta2))
+    lr, eps = float(np.float32(lr)), float(np.float32(eps))
+    p, g, m, v = (np.asarray(a, np.float64) for a in (p, g, m, v))
+    m = b1 * m + (1 - b1) * g
+    v = b2 * v + (1 - b2) * g * g
+    mh = m / (1 - b1 ** step)
+    vh = v / (1 - b2 ** step)
+    return p - lr * mh / (np.sqrt(vh) + eps), m, v

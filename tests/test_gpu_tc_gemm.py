@@ -1,0 +1,116 @@
+"""GPU: the tcgen05 (tensor-core) GEMM in TF32 mode against an f64 product, for every operand
+layout, edge tiles, and the fused epilogues; then whole training steps in TF32 mode within
+the tolerance the task states (rel 2e-3)."""
+import numpy as np
+import pytest
+
+from conftest import assert_bit_equal
+from devbuf import DevBuf
+
+pytestmark = pytest.mark.gpu
+
+TF32_RTOL = 2e-3   # relative to the magnitude sum_k |a||b| of each output element
+
+
+def _run(gpu, a_st, b_st, m, n, k, ta, tb, bias=None, relu=0, mask=None, precision=1):
+    da, db, dc = DevBuf(gpu, a_st), DevBuf(gpu, b_st), DevBuf(gpu, n=m * n)
+    dbias = DevBuf(gpu, bias) if bias is not None else None
+    dmask = DevBuf(gpu, mask) if mask is not None else None
+    gpu._ffi.check(gpu._ffi.lib().launch_gemm_kernel(da.ptr, db.ptr, dc.ptr, m, n, k, ta, tb, dbias.ptr if dbias else None, relu,
+                                                     dmask.ptr if dmask else None, precision, None))
+    gpu.synchronize()   # also surfaces a bounded wait that gave up inside the kernel
+    return dc.get().reshape(m, n)
+
+
+def _check(got, a, b, extra=None):
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    mag = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    if extra is not None:
+        exact = extra(exact)
+    err = np.abs(got - exact)
+    assert np.all(err <= TF32_RTOL * mag + 1e-30), f"max err/mag {np.max(err / (mag + 1e-30)):.3e}"
+
+
+SHAPES = [(128, 256, 32), (128, 128, 64), (256, 512, 128), (32, 128, 784), (100, 260, 36), (129, 132, 8), (4, 4, 4),
+          (512, 1024, 1024), (1000, 264, 520), (2048, 10 * 4, 96), (148 * 128 + 5, 256, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_tf32_gemm_all_layouts(gpu, m, n, k, ta, tb):
+    if (ta and m % 4) or (not ta and k % 4) or (tb and k % 4) or n % 4:
+        pytest.skip("row pitch not a multiple of 16 bytes: handled by the FP32 kernel")
+    rng = np.random.default_rng(m * 31 + n * 7 + k + ta * 2 + tb)
+    a, b = rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((k, n), dtype=np.float32)
+    a_st = np.ascontiguousarray(a.T) if ta else a
+    b_st = np.ascontiguousarray(b.T) if tb else b
+    _check(_run(gpu, a_st, b_st, m, n, k, ta, tb), a, b)
+
+
+def test_tf32_gemm_exact_on_small_integers(gpu):
+    """Integers up to 2^10 are exact in TF32 and their sums exact in FP32: any layout or descriptor slip shows as a wrong integer."""
+    rng = np.random.default_rng(0)
+    m, n, k = 384, 512, 160
+    a = rng.integers(-8, 9, (m, k)).astype(np.float32)
+    b = rng.integers(-8, 9, (k, n)).astype(np.float32)
+    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    for ta, tb in ((0, 0), (0, 1), (1, 0), (1, 1)):
+        got = _run(gpu, np.ascontiguousarray(a.T) if ta else a, np.ascontiguousarray(b.T) if tb else b, m, n, k, ta, tb)
+        assert np.array_equal(got, exact), (ta, tb, int((got != exact).sum()))
+
+
+def test_tf32_gemm_epilogues(gpu, ora):
+    rng = np.random.default_rng(5)
+    m, n, k = 300, 384, 200
+    a = rng.integers(-4, 5, (m, k)).astype(np.float32)
+    b = rng.integers(-4, 5, (k, n)).astype(np.float32)
+    bias = rng.integers(-50, 50, n).astype(np.float32)
+    mask = rng.standard_normal((m, n), dtype=np.float32)
+    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, bias=bias, relu=1), ora.relu(ora.add_row(exact, bias)), "bias+relu")
+    assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, mask=mask), ora.relu_bwd(mask, exact), "mask")
+    assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, bias=bias), ora.add_row(exact, bias), "bias")
+
+
+def test_tf32_long_k_accumulation(gpu):
+    rng = np.random.default_rng(6)
+    m, n, k = 256, 256, 16384
+    a, b = rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((k, n), dtype=np.float32)
+    _check(_run(gpu, np.ascontiguousarray(a.T), b, m, n, k, 1, 0), a, b)   # the dW layout with a long reduction
+
+
+def test_training_step_tf32_within_tolerance(gpu, ora):
+    """A 3-layer MLP step in TF32 mode vs the oracle: loss, gradients and post-Adam parameters within rel 2e-3."""
+    from test_gpu_engine import _mlp_device
+    rng = np.random.default_rng(4)
+    dims, batch = [256, 512, 512, 128], 384
+    ws = [rng.uniform(-np.sqrt(6 / dims[i]), np.sqrt(6 / dims[i]), (dims[i], dims[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(3)]
+    x, t = rng.standard_normal((batch, dims[0]), dtype=np.float32), rng.standard_normal((batch, dims[-1]), dtype=np.float32)
+    st = ora.MlpState(ws, bs)
+    ref = ora.mlp_step(st, x, t, loss_kind=ora.LOSS_MSE)
+    gpu.set_matmul_precision(gpu.TF32)
+    got = _mlp_device(gpu, ws, bs, x, t, "mse", False)
+    assert abs(got["loss"] - float(ref["loss"])) <= 2e-3 * abs(float(ref["loss"]))
+    for i in range(3):
+        scale = np.abs(st.gw[i]).max()
+        assert np.abs(got["gw"][i] - st.gw[i]).max() <= 2e-3 * scale
+        assert np.abs(got["gb"][i] - st.gb[i]).max() <= 2e-3 * np.abs(st.gb[i]).max()
+        assert np.abs(got["w"][i] - st.w[i]).max() <= 2.1e-3   # one Adam step moves a weight by at most lr = 1e-3 each way
+
+
+def test_relu_mask_is_exact_for_the_device_forward(gpu):
+    """The mask used in backward is exactly (z_device > 0) for the z this forward produced, in TF32 mode too."""
+    rng = np.random.default_rng(8)
+    gpu.set_matmul_precision(gpu.TF32)
+    x = rng.standard_normal((256, 128), dtype=np.float32)
+    w = rng.standard_normal((128, 256), dtype=np.float32)
+    X = gpu.Tensor.from_slice(x, x.shape).with_requires_grad()
+    W = gpu.Tensor.from_slice(w, w.shape)
+    y = X.matmul(W).relu()
+    y.sum().backward(None)
+    gx = X.grad_by_value().data()
+    mask = (y.data() > 0).astype(np.float32)
+    gpu.set_matmul_precision(gpu.FP32)
+    want = gpu.Tensor.from_slice(mask, mask.shape).matmul(gpu.Tensor.from_slice(np.ascontiguousarray(w.T), [256, 128])).data()
+    np.testing.assert_allclose(gx, want, rtol=2e-3, atol=2e-3 * np.abs(want).max())

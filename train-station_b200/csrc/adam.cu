@@ -1,0 +1,160 @@
+// Fused multi-tensor Adam: one launch updates every parameter tensor of the optimizer.
+// HBM-bound: 28 bytes per parameter (read p, g, m, v; write p, m, v).
+//
+// Arithmetic follows optimizers/adam/mod.rs operation by operation, each step rounded
+// separately (no FMA contraction), so that with identical gradients the updated
+// parameters and moments are bit-identical to the reference's:
+//   m = (beta1*m) + ((1-beta1)*g)                                        :685-687
+//   v = (beta2*v) + ((1-beta2)*(g*g))        elements below size/8*8     :761-765
+//   v = (beta2*v) + (((1-beta2)*g)*g)        the size%8 tail elements    :770-772
+//   p = p - ((lr*(m*f1)) / (sqrt(v*f2) + eps))                           :791-840, :984-1006
+// with g replaced by g + wd*p first when weight decay is on (:567-620).
+#include <cstring>
+
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr unsigned long long kChunk = 16384;   // elements per CTA: 256 threads x 4 floats x 16 trips
+
+struct ChunkEntry {
+    int tensor;
+    int pad;
+    unsigned long long offset;   // first element of the chunk inside the tensor
+};
+
+struct Scalars { float lr, beta1, beta2, eps, wd, f1, f2, grad_scale, c1, c2; };
+
+__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, bool body, const Scalars& sc) {
+    if (sc.grad_scale != 1.0f) g = __fmul_rn(g, sc.grad_scale);
+    if (sc.wd > 0.0f) g = __fadd_rn(g, __fmul_rn(sc.wd, p));
+    m = __fadd_rn(__fmul_rn(sc.beta1, m), __fmul_rn(sc.c1, g));
+    float gg = body ? __fmul_rn(sc.c2, __fmul_rn(g, g)) : __fmul_rn(__fmul_rn(sc.c2, g), g);
+    v = __fadd_rn(__fmul_rn(sc.beta2, v), gg);
+    float mh = __fmul_rn(m, sc.f1), vh = __fmul_rn(v, sc.f2);
+    p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, mh), __fadd_rn(__fsqrt_rn(vh), sc.eps)));
+}
+
+__global__ void __launch_bounds__(kThreads) adam_kernel(const AdamTensor* __restrict__ tensors, const ChunkEntry* __restrict__ chunks,
+                                                        Scalars sc) {
+    const ChunkEntry ce = chunks[blockIdx.x];
+    const AdamTensor t = tensors[ce.tensor];
+    const unsigned long long body = t.n / 8 * 8;
+    unsigned long long end = ce.offset + kChunk;
+    if (end > t.n) end = t.n;
+    const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
+                       reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+    if (vec) {
+        // ce.offset is a multiple of kChunk, hence of 4
+        const unsigned long long v0 = ce.offset / 4, v1 = end / 4;
+        float4* pp = reinterpret_cast<float4*>(t.p);
+        const float4* gp = reinterpret_cast<const float4*>(t.g);
+        float4* mp = reinterpret_cast<float4*>(t.m);
+        float4* vp = reinterpret_cast<float4*>(t.v);
+        for (unsigned long long i = v0 + threadIdx.x; i < v1; i += 2 * kThreads) {
+            // two float4 per array in flight
+            unsigned long long j = i + kThreads;
+            bool has2 = j < v1;
+            float4 p0 = pp[i], g0 = __ldcs(gp + i), m0 = mp[i], w0 = vp[i];
+            float4 p1, g1, m1, w1;
+            if (has2) { p1 = pp[j]; g1 = __ldcs(gp + j); m1 = mp[j]; w1 = vp[j]; }
+            unsigned long long e = i * 4;
+            adam_one(p0.x, g0.x, m0.x, w0.x, e < body, sc);
+            adam_one(p0.y, g0.y, m0.y, w0.y, e + 1 < body, sc);
+            adam_one(p0.z, g0.z, m0.z, w0.z, e + 2 < body, sc);
+            adam_one(p0.w, g0.w, m0.w, w0.w, e + 3 < body, sc);
+            pp[i] = p0; mp[i] = m0; vp[i] = w0;
+            if (has2) {
+                e = j * 4;
+                adam_one(p1.x, g1.x, m1.x, w1.x, e < body, sc);
+                adam_one(p1.y, g1.y, m1.y, w1.y, e + 1 < body, sc);
+                adam_one(p1.z, g1.z, m1.z, w1.z, e + 2 < body, sc);
+                adam_one(p1.w, g1.w, m1.w, w1.w, e + 3 < body, sc);
+                pp[j] = p1; mp[j] = m1; vp[j] = w1;
+            }
+        }
+        for (unsigned long long i = v1 * 4 + threadIdx.x; i < end; i += kThreads) {
+            float p = t.p[i], m = t.m[i], v = t.v[i];
+            adam_one(p, t.g[i], m, v, i < body, sc);
+            t.p[i] = p; t.m[i] = m; t.v[i] = v;
+        }
+    } else {
+        for (unsigned long long i = ce.offset + threadIdx.x; i < end; i += kThreads) {
+            float p = t.p[i], m = t.m[i], v = t.v[i];
+            adam_one(p, t.g[i], m, v, i < body, sc);
+            t.p[i] = p; t.m[i] = m; t.v[i] = v;
+        }
+    }
+}
+
+}  // namespace
+
+// The chunk map depends only on the tensor sizes, so callers build and upload it once per
+// parameter set; the tensor table (pointers) is refreshed every step.
+int adam_chunk_count(const unsigned long long* sizes, int n) {
+    size_t c = 0;
+    for (int i = 0; i < n; ++i) c += (size_t)((sizes[i] + kChunk - 1) / kChunk);
+    return (int)c;
+}
+size_t adam_chunk_bytes(int n_chunks) { return (size_t)n_chunks * sizeof(ChunkEntry); }
+void adam_build_chunks(const unsigned long long* sizes, int n, void* host_out) {
+    ChunkEntry* ce = (ChunkEntry*)host_out;
+    int c = 0;
+    for (int i = 0; i < n; ++i)
+        for (unsigned long long off = 0; off < sizes[i]; off += kChunk) ce[c++] = ChunkEntry{i, 0, off};
+}
+
+bool adam_launch(const AdamTensor* tensors_dev, const void* chunks_dev, int n_chunks, double total_elems, float lr, float beta1,
+                 float beta2, float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s) {
+    if (n_chunks == 0) return true;
+    Scalars sc{lr, beta1, beta2, eps, wd, f1, f2, grad_scale, 1.0f - beta1, 1.0f - beta2};
+    ProfScope prof(kProfAdam, s, 28.0 * total_elems);
+    adam_kernel<<<n_chunks, kThreads, 0, s>>>(tensors_dev, (const ChunkEntry*)chunks_dev, sc);
+    return cuda_ok(cudaGetLastError(), "adam launch");
+}
+
+}  // namespace k
+}  // namespace ts
+
+// ====================================================================== C ABI
+using namespace ts;
+
+TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m, float* const* v,
+                                            const unsigned long long* sizes, int n_tensors, float lr, float beta1, float beta2,
+                                            float eps, float weight_decay, float f1, float f2, float grad_scale, void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    DeviceCtx* c = ctx();
+    if (!s || !c) return false;
+    if (n_tensors <= 0) return true;
+    if (!params || !grads || !m || !v || !sizes) { set_error("launch_adam_multi_tensor_kernel: null table"); return false; }
+    std::vector<k::AdamTensor> t((size_t)n_tensors);
+    for (int i = 0; i < n_tensors; ++i) {
+        if (sizes[i] && (!params[i] || !grads[i] || !m[i] || !v[i])) { set_error("launch_adam_multi_tensor_kernel: null tensor pointer at index %d", i); return false; }
+        t[i] = k::AdamTensor{params[i], grads[i], m[i], v[i], sizes[i]};
+    }
+    std::vector<unsigned long long> sz(sizes, sizes + n_tensors);
+    int n_chunks = k::adam_chunk_count(sz.data(), n_tensors);
+    size_t tbytes = (((size_t)n_tensors * sizeof(k::AdamTensor)) + 255) & ~size_t(255);
+    size_t bytes = tbytes + k::adam_chunk_bytes(n_chunks);
+    std::vector<char> host(bytes);
+    memcpy(host.data(), t.data(), (size_t)n_tensors * sizeof(k::AdamTensor));
+    k::adam_build_chunks(sz.data(), n_tensors, host.data() + tbytes);
+    float* dev = c->alloc.alloc(bytes);
+    if (!dev) return false;
+    bool ok = cuda_ok(cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, s), "adam table upload");
+    // a pageable source has been staged by the time cudaMemcpyAsync returns
+    double total = 0;
+    for (int i = 0; i < n_tensors; ++i) total += (double)sizes[i];
+    ok = ok && k::adam_launch((const k::AdamTensor*)dev, (const char*)dev + tbytes, n_chunks, total, lr, beta1, beta2, eps,
+                              weight_decay, f1, f2, grad_scale, s);
+    // Freed blocks are only reused by later work, which is ordered after this kernel when it runs on
+    // the compute stream; a caller-supplied stream is drained first.
+    if (s != c->compute) cudaStreamSynchronize(s);
+    c->alloc.free(dev);
+    return ok;
+}

@@ -1,0 +1,138 @@
+// Internal declarations shared by the translation units of libtrain_station_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#define TS_API extern "C" __attribute__((visibility("default")))
+
+namespace ts {
+
+// ---------------------------------------------------------------- errors
+void set_error(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+const char* last_error();
+bool cuda_ok(cudaError_t e, const char* what);  // records the error text when e != success
+
+#define TS_CHECK(expr)                                   \
+    do {                                                 \
+        if (!::ts::cuda_ok((expr), #expr)) return false; \
+    } while (0)
+
+// ---------------------------------------------------------------- allocator
+// Size-bucketed caching allocator.  Blocks are reused in stream order on the compute
+// stream; a block used on another stream must be fenced by the caller with an event.
+class Allocator {
+public:
+    float* alloc(size_t bytes);
+    void free(float* p);
+    void release_cached();
+    void stats(unsigned long long* in_use, unsigned long long* reserved, unsigned long long* peak,
+               unsigned long long* driver_allocs, unsigned long long* hits);
+    void set_limit(size_t bytes) { limit_ = bytes; }
+    ~Allocator();
+
+private:
+    static size_t round_size(size_t bytes);
+    std::mutex mu_;
+    std::multimap<size_t, void*> cache_;            // free blocks by size
+    std::unordered_map<void*, size_t> live_;        // handed-out blocks
+    size_t in_use_ = 0, reserved_ = 0, peak_ = 0, limit_ = 0;
+    unsigned long long driver_allocs_ = 0, hits_ = 0;
+};
+
+// ---------------------------------------------------------------- per-device context
+struct DeviceCtx {
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t compute = nullptr;   // every engine kernel runs here
+    cudaStream_t copy = nullptr;      // asynchronous uploads
+    cudaStream_t comm = nullptr;      // NCCL
+    Allocator alloc;
+    float* reduce_scratch = nullptr;  // partial sums of sum()/mean()
+    int* error_flag = nullptr;        // device word set by kernels whose bounded waits gave up
+    int* error_flag_host = nullptr;   // pinned mirror
+};
+
+DeviceCtx* ctx();                     // context of this thread's current device, or nullptr (error set)
+int current_device();
+bool set_device(int dev);
+cudaStream_t pick_stream(void* user_stream);  // NULL -> compute stream of the current device
+
+// ---------------------------------------------------------------- launch accounting
+enum ProfClass { kProfGemmTc = 0, kProfGemmFp32 = 1, kProfElementwise = 2, kProfReduce = 3, kProfAdam = 4, kProfClasses = 5 };
+// Counts the launch and, when profiling is on, brackets the enclosed launches with two events.
+struct ProfScope {
+    ProfScope(ProfClass cls, cudaStream_t s, double work, int launches = 1);
+    ~ProfScope();
+    ProfClass cls;
+    cudaStream_t stream;
+    cudaEvent_t start = nullptr;
+    double work;
+};
+
+int matmul_precision();
+bool fusion_enabled();
+
+// ---------------------------------------------------------------- kernels (device pointers)
+namespace k {
+constexpr size_t kReduceScratchElems = 4096;
+
+bool binary(int op, const float* a, const float* b, float* o, size_t n, cudaStream_t s);  // 0 add 1 sub 2 mul 3 div
+bool bias_act(const float* z, const float* bias, float* o, size_t rows, size_t cols, bool relu, cudaStream_t s);
+bool add_scalar_bcast(const float* a, const float* scalar_dev, float* o, size_t n, cudaStream_t s);
+bool relu(const float* x, float* o, size_t n, cudaStream_t s);
+bool relu_bwd(const float* ref, const float* go, float* gi, size_t n, cudaStream_t s);
+bool square(const float* x, float* o, size_t n, cudaStream_t s);
+bool square_bwd(const float* x, const float* go, float* gi, size_t n, cudaStream_t s);
+bool mul_bwd(const float* a, const float* b, const float* go, float* ga, float* gb, size_t n, cudaStream_t s);
+bool div_bwd(const float* a, const float* b, const float* go, float* ga, float* gb, size_t n, cudaStream_t s);
+bool scale(const float* x, float alpha, float* o, size_t n, cudaStream_t s);
+bool fill(float* o, float v, size_t n, cudaStream_t s);
+bool fill_from_scalar(float* o, const float* scalar, float scale, size_t n, cudaStream_t s);
+// gy = ((inv_n) * (*upstream)) * (2 * (y - t)): ReduceMean -> PowScalar(2) -> Sub in one pass.
+bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s);
+bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaStream_t s);
+// loss[0] = mean((y-t)^2) without materialising the difference.
+bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s);
+size_t colsum_scratch_elems(size_t rows, size_t cols);
+bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s);
+bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols,
+                     float* scratch, cudaStream_t s);
+
+struct AdamTensor {
+    float* p;
+    const float* g;
+    float* m;
+    float* v;
+    unsigned long long n;
+};
+int adam_chunk_count(const unsigned long long* sizes, int n);
+size_t adam_chunk_bytes(int n_chunks);
+void adam_build_chunks(const unsigned long long* sizes, int n, void* host_out);
+bool adam_launch(const AdamTensor* tensors_dev, const void* chunks_dev, int n_chunks, double total_elems, float lr, float beta1,
+                 float beta2, float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s);
+
+struct GemmArgs {
+    const float* a;
+    const float* b;
+    float* c;
+    size_t m, n, k;
+    bool trans_a, trans_b;
+    const float* bias;   // [n] or null
+    bool relu;
+    const float* mask;   // [m,n] or null
+};
+bool sgemm(const GemmArgs& g, cudaStream_t s);                       // FFMA, reference summation order
+bool gemm_tc_supported(const GemmArgs& g);
+bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s);  // tcgen05 TF32 / 3xTF32
+bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s);   // dispatch
+}  // namespace k
+
+}  // namespace ts

@@ -1,0 +1,326 @@
+// Elementwise forward and backward kernels: HBM-bound, 128-bit vectorised, grid sized in
+// multiples of the SM count.  Every arithmetic step is a single IEEE-rounded operation
+// written with explicit intrinsics so that nvcc cannot contract a*b+c into an FMA: the
+// reference (Rust, no fast-math) rounds each operation separately.
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;        // float4 loads in flight per thread per input
+constexpr int kCtasPerSm = 8;
+
+inline int grid_for(size_t n_vec, int sm_count) {
+    size_t per_cta = (size_t)kThreads * kUnroll;
+    size_t want = (n_vec + per_cta - 1) / per_cta;
+    size_t cap = (size_t)sm_count * kCtasPerSm;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// F::apply(in[NIN], out[NOUT]) on scalars; the same functor serves the vector body and the tail.
+template <int NIN, int NOUT>
+struct Ptrs {
+    const float* in[NIN ? NIN : 1];
+    float* out[NOUT];   // an output may be null (skipped)
+};
+
+template <int NIN, int NOUT, class F>
+__global__ void __launch_bounds__(kThreads) ew_vec_kernel(Ptrs<NIN, NOUT> p, size_t n_vec, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
+    for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n_vec; base += stride) {
+        float4 vin[kUnroll][NIN ? NIN : 1];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            size_t i = base + (size_t)u * kThreads;
+            if (i < n_vec) {
+#pragma unroll
+                for (int a = 0; a < NIN; ++a) vin[u][a] = __ldcs(reinterpret_cast<const float4*>(p.in[a]) + i);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            size_t i = base + (size_t)u * kThreads;
+            if (i < n_vec) {
+                float xi[4][NIN ? NIN : 1], xo[4][NOUT];
+#pragma unroll
+                for (int a = 0; a < NIN; ++a) {
+                    xi[0][a] = vin[u][a].x; xi[1][a] = vin[u][a].y; xi[2][a] = vin[u][a].z; xi[3][a] = vin[u][a].w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) f.apply(xi[e], xo[e]);
+#pragma unroll
+                for (int o = 0; o < NOUT; ++o) {
+                    if (p.out[o]) {
+                        float4 v = make_float4(xo[0][o], xo[1][o], xo[2][o], xo[3][o]);
+                        __stcs(reinterpret_cast<float4*>(p.out[o]) + i, v);
+                    }
+                }
+            }
+        }
+    }
+    // scalar tail (n mod 4 elements), done by the first CTA
+    if (blockIdx.x == 0) {
+        size_t i = n_vec * 4 + threadIdx.x;
+        if (i < n) {
+            float xi[NIN ? NIN : 1], xo[NOUT];
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) xi[a] = p.in[a][i];
+            f.apply(xi, xo);
+#pragma unroll
+            for (int o = 0; o < NOUT; ++o)
+                if (p.out[o]) p.out[o][i] = xo[o];
+        }
+    }
+}
+
+// Fallback for pointers that are not 16-byte aligned (sub-buffers handed in through the raw ABI).
+template <int NIN, int NOUT, class F>
+__global__ void __launch_bounds__(kThreads) ew_scalar_kernel(Ptrs<NIN, NOUT> p, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        float xi[NIN == 0 ? 1 : NIN], xo[NOUT];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) xi[a] = p.in[a][i];
+        f.apply(xi, xo);
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o)
+            if (p.out[o]) p.out[o][i] = xo[o];
+    }
+}
+
+template <int NIN, int NOUT, class F>
+bool launch_ew(Ptrs<NIN, NOUT> p, size_t n, F f, cudaStream_t s) {
+    if (n == 0) return true;
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    for (int a = 0; a < NIN; ++a)
+        if (!p.in[a]) { set_error("elementwise kernel: null input pointer"); return false; }
+    bool any_out = false, al = true;
+    for (int a = 0; a < NIN; ++a) al = al && aligned16(p.in[a]);
+    for (int o = 0; o < NOUT; ++o) { any_out = any_out || p.out[o]; al = al && aligned16(p.out[o]); }
+    if (!any_out) { set_error("elementwise kernel: null output pointer"); return false; }
+    int n_arrays = NIN;
+    for (int o = 0; o < NOUT; ++o) n_arrays += p.out[o] ? 1 : 0;
+    ProfScope prof(kProfElementwise, s, 4.0 * (double)n * n_arrays);
+    if (al) {
+        size_t n_vec = n / 4;
+        ew_vec_kernel<NIN, NOUT, F><<<grid_for(n_vec, c->sm_count), kThreads, 0, s>>>(p, n_vec, n, f);
+    } else {
+        ew_scalar_kernel<NIN, NOUT, F><<<grid_for((n + 3) / 4, c->sm_count), kThreads, 0, s>>>(p, n, f);
+    }
+    return cuda_ok(cudaGetLastError(), "elementwise launch");
+}
+
+// ---- functors: one rounded IEEE operation per arithmetic step -------------------------
+struct AddF { __device__ void apply(const float* x, float* o) const { o[0] = __fadd_rn(x[0], x[1]); } };
+struct SubF { __device__ void apply(const float* x, float* o) const { o[0] = __fsub_rn(x[0], x[1]); } };
+struct MulF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[0], x[1]); } };
+struct DivF { __device__ void apply(const float* x, float* o) const { o[0] = __fdiv_rn(x[0], x[1]); } };
+// max(x,0) as the AVX2 maxps does it: NaN -> 0, -0 -> +0 (relu.rs:175-215).
+struct ReluF { __device__ void apply(const float* x, float* o) const { o[0] = x[0] > 0.0f ? x[0] : 0.0f; } };
+struct ReluBwdF { __device__ void apply(const float* x, float* o) const { o[0] = x[0] > 0.0f ? x[1] : 0.0f; } };
+struct SquareF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[0], x[0]); } };
+// go * (2 * x): grad_fn/ops/pow.rs:5-27 with exponent 2
+struct SquareBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[1], __fmul_rn(2.0f, x[0])); } };
+// inputs a, b, go -> go*b, go*a
+struct MulBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[2], x[1]); o[1] = __fmul_rn(x[2], x[0]); } };
+// inputs a, b, go -> go/b, -((go*a)/(b*b))
+struct DivBwdF {
+    __device__ void apply(const float* x, float* o) const {
+        o[0] = __fdiv_rn(x[2], x[1]);
+        o[1] = -__fdiv_rn(__fmul_rn(x[2], x[0]), __fmul_rn(x[1], x[1]));
+    }
+};
+struct ScaleF { float alpha; __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(alpha, x[0]); } };
+struct FillF { float v; __device__ void apply(const float*, float* o) const { o[0] = v; } };
+struct FillFromScalarF {
+    const float* scalar; float scale;
+    __device__ void apply(const float*, float* o) const { o[0] = __fmul_rn(scale, __ldg(scalar)); }
+};
+struct AddScalarBcastF {
+    const float* scalar;
+    __device__ void apply(const float* x, float* o) const { o[0] = __fadd_rn(x[0], __ldg(scalar)); }
+};
+// inputs y, t: ((inv_n * upstream) * (2 * (y - t))): ReduceMean -> PowScalar(2) -> Sub chain
+// (grad_fn/reductions/mean.rs:10-19, grad_fn/ops/pow.rs:5-27, grad_fn/ops/sub.rs:26-31).
+struct MseGradF {
+    const float* upstream; float inv_n;
+    __device__ void apply(const float* x, float* o) const {
+        float sc = __fmul_rn(inv_n, __ldg(upstream));
+        o[0] = __fmul_rn(sc, __fmul_rn(2.0f, __fsub_rn(x[0], x[1])));
+    }
+};
+
+// out[i,j] = act(z[i,j] + bias[j]); cols % 4 == 0 and aligned pointers take the vector path.
+template <bool RELU>
+__global__ void __launch_bounds__(kThreads) bias_act_vec_kernel(const float4* __restrict__ z, const float4* __restrict__ bias,
+                                                                float4* __restrict__ out, size_t n_vec, unsigned cols_vec) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec; i += stride) {
+        float4 v = __ldcs(z + i);
+        float4 b = __ldg(bias + (unsigned)(i % cols_vec));
+        v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+        if (RELU) {
+            v.x = v.x > 0.0f ? v.x : 0.0f; v.y = v.y > 0.0f ? v.y : 0.0f;
+            v.z = v.z > 0.0f ? v.z : 0.0f; v.w = v.w > 0.0f ? v.w : 0.0f;
+        }
+        __stcs(out + i, v);
+    }
+}
+template <bool RELU>
+__global__ void __launch_bounds__(kThreads) bias_act_scalar_kernel(const float* __restrict__ z, const float* __restrict__ bias,
+                                                                   float* __restrict__ out, size_t n, size_t cols) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        float v = __fadd_rn(z[i], __ldg(bias + (i % cols)));
+        if (RELU) v = v > 0.0f ? v : 0.0f;
+        out[i] = v;
+    }
+}
+
+}  // namespace
+
+bool binary(int op, const float* a, const float* b, float* o, size_t n, cudaStream_t s) {
+    Ptrs<2, 1> p{{a, b}, {o}};
+    switch (op) {
+        case 0: return launch_ew(p, n, AddF{}, s);
+        case 1: return launch_ew(p, n, SubF{}, s);
+        case 2: return launch_ew(p, n, MulF{}, s);
+        case 3: return launch_ew(p, n, DivF{}, s);
+    }
+    set_error("binary: unknown op %d", op);
+    return false;
+}
+bool relu(const float* x, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, ReluF{}, s); }
+bool relu_bwd(const float* ref, const float* go, float* gi, size_t n, cudaStream_t s) {
+    return launch_ew(Ptrs<2, 1>{{ref, go}, {gi}}, n, ReluBwdF{}, s);
+}
+bool square(const float* x, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, SquareF{}, s); }
+bool square_bwd(const float* x, const float* go, float* gi, size_t n, cudaStream_t s) {
+    return launch_ew(Ptrs<2, 1>{{x, go}, {gi}}, n, SquareBwdF{}, s);
+}
+bool mul_bwd(const float* a, const float* b, const float* go, float* ga, float* gb, size_t n, cudaStream_t s) {
+    return launch_ew(Ptrs<3, 2>{{a, b, go}, {ga, gb}}, n, MulBwdF{}, s);
+}
+bool div_bwd(const float* a, const float* b, const float* go, float* ga, float* gb, size_t n, cudaStream_t s) {
+    return launch_ew(Ptrs<3, 2>{{a, b, go}, {ga, gb}}, n, DivBwdF{}, s);
+}
+bool scale(const float* x, float alpha, float* o, size_t n, cudaStream_t s) {
+    return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, ScaleF{alpha}, s);
+}
+bool fill(float* o, float v, size_t n, cudaStream_t s) { return launch_ew(Ptrs<0, 1>{{nullptr}, {o}}, n, FillF{v}, s); }
+bool fill_from_scalar(float* o, const float* scalar, float sc, size_t n, cudaStream_t s) {
+    if (!scalar) { set_error("fill_from_scalar: null scalar"); return false; }
+    return launch_ew(Ptrs<0, 1>{{nullptr}, {o}}, n, FillFromScalarF{scalar, sc}, s);
+}
+bool add_scalar_bcast(const float* a, const float* scalar_dev, float* o, size_t n, cudaStream_t s) {
+    if (!scalar_dev) { set_error("add_scalar_bcast: null scalar"); return false; }
+    return launch_ew(Ptrs<1, 1>{{a}, {o}}, n, AddScalarBcastF{scalar_dev}, s);
+}
+bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {
+    if (!upstream) { set_error("mse_grad: null upstream"); return false; }
+    return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n}, s);
+}
+
+bool bias_act(const float* z, const float* bias, float* o, size_t rows, size_t cols, bool relu_on, cudaStream_t s) {
+    size_t n = rows * cols;
+    if (n == 0) return true;
+    if (!z || !bias || !o) { set_error("bias_act: null pointer"); return false; }
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    ProfScope prof(kProfElementwise, s, 8.0 * (double)n);
+    if (cols % 4 == 0 && aligned16(z) && aligned16(bias) && aligned16(o) && cols / 4 < (1ull << 32)) {
+        size_t n_vec = n / 4;
+        size_t want = (n_vec + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm * 2;
+        int grid = (int)(want < cap ? want : cap);
+        if (relu_on) bias_act_vec_kernel<true><<<grid, kThreads, 0, s>>>((const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
+        else bias_act_vec_kernel<false><<<grid, kThreads, 0, s>>>((const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
+    } else {
+        size_t want = (n + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm * 2;
+        int grid = (int)(want < cap ? want : cap);
+        if (relu_on) bias_act_scalar_kernel<true><<<grid, kThreads, 0, s>>>(z, bias, o, n, cols);
+        else bias_act_scalar_kernel<false><<<grid, kThreads, 0, s>>>(z, bias, o, n, cols);
+    }
+    return cuda_ok(cudaGetLastError(), "bias_act launch");
+}
+
+}  // namespace k
+}  // namespace ts
+
+// ====================================================================== C ABI
+using namespace ts;
+
+#define TS_STREAM_OR_FAIL(var)                 \
+    cudaStream_t var = ts::pick_stream(stream); \
+    if (!var) return false;
+
+TS_API bool launch_add_kernel(const float* a, const float* b, float* r, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!a || !b || !r) { if (n == 0) return true; set_error("launch_add_kernel: null pointer"); return false; }
+    return k::binary(0, a, b, r, n, s);
+}
+TS_API bool launch_sub_kernel(const float* a, const float* b, float* r, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!a || !b || !r) { if (n == 0) return true; set_error("launch_sub_kernel: null pointer"); return false; }
+    return k::binary(1, a, b, r, n, s);
+}
+TS_API bool launch_mul_kernel(const float* a, const float* b, float* r, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!a || !b || !r) { if (n == 0) return true; set_error("launch_mul_kernel: null pointer"); return false; }
+    return k::binary(2, a, b, r, n, s);
+}
+TS_API bool launch_div_kernel(const float* a, const float* b, float* r, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!a || !b || !r) { if (n == 0) return true; set_error("launch_div_kernel: null pointer"); return false; }
+    return k::binary(3, a, b, r, n, s);
+}
+TS_API bool launch_bias_act_kernel(const float* z, const float* bias, float* out, unsigned long long rows,
+                                   unsigned long long cols, int relu, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::bias_act(z, bias, out, rows, cols, relu != 0, s);
+}
+TS_API bool launch_relu_kernel(const float* x, float* out, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::relu(x, out, n, s);
+}
+TS_API bool launch_relu_backward_kernel(const float* ref, const float* go, float* gi, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::relu_bwd(ref, go, gi, n, s);
+}
+TS_API bool launch_square_kernel(const float* x, float* out, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::square(x, out, n, s);
+}
+TS_API bool launch_square_backward_kernel(const float* x, const float* go, float* gi, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::square_bwd(x, go, gi, n, s);
+}
+TS_API bool launch_mul_backward_kernel(const float* a, const float* b, const float* go, float* ga, float* gb,
+                                       unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::mul_bwd(a, b, go, ga, gb, n, s);
+}
+TS_API bool launch_div_backward_kernel(const float* a, const float* b, const float* go, float* ga, float* gb,
+                                       unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::div_bwd(a, b, go, ga, gb, n, s);
+}
+TS_API bool launch_scale_kernel(const float* x, float alpha, float* out, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::scale(x, alpha, out, n, s);
+}
+TS_API bool launch_fill_kernel(float* out, float value, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::fill(out, value, n, s);
+}
+TS_API bool launch_fill_from_scalar_kernel(float* out, const float* scalar, float scale, unsigned long long n, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    return k::fill_from_scalar(out, scalar, scale, n, s);
+}

@@ -1,0 +1,992 @@
+// Tensor, gradtrack and Adam engine behind the C ABI: the device counterpart of the
+// reference's src/tensor/core (storage, constructors), src/tensor/ops + reductions (the ops
+// of the MLP training step), src/gradtrack (tape, backward) and src/optimizers/adam.
+//
+// Design, B200-first rather than a translation:
+//   * every op only enqueues kernels on the per-device compute stream and returns;
+//   * saved tensors are held by reference (refcounted storage) with a version counter that
+//     makes an in-place write between forward and backward an error instead of a silent
+//     wrong gradient (the reference deep-copies, tensor/ops/matmul/mod.rs:296-297);
+//   * a matmul is not launched until its result is needed, so that a following row-broadcast
+//     add, ReLU, or (in backward) ReLU mask folds into the GEMM epilogue;
+//   * backward walks the tape in descending tensor-id order, which is a topological order
+//     because ids are handed out monotonically (tensor/core/mod.rs:131); the reference uses a
+//     LIFO worklist (gradtrack/engine.rs:962-1047) that computes the same sums;
+//   * binary ops give each operand its own gradient (the reference zips gradients to
+//     input ids positionally and mis-assigns them when only the second operand requires
+//     grad: tensor/ops/add.rs:135-142 vs gradtrack/engine.rs:1000-1001).
+#include <nccl.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <unordered_set>
+
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+
+// ------------------------------------------------------------------ storage and tensors
+struct Storage {
+    float* ptr = nullptr;
+    size_t n = 0;
+    DeviceCtx* c = nullptr;
+    uint64_t version = 0;
+    cudaEvent_t ready = nullptr;   // set while an upload on the copy stream is outstanding
+    ~Storage() {
+        if (ready) cudaEventDestroy(ready);
+        if (c && ptr) c->alloc.free(ptr);
+    }
+};
+using StorageP = std::shared_ptr<Storage>;
+
+struct TensorImpl;
+using TensorP = std::shared_ptr<TensorImpl>;
+
+// A GEMM that has been requested but not launched: op(a) . op(b) [+ bias] [relu] [mask].
+struct PendingGemm {
+    TensorP a, b;
+    bool ta = false, tb = false;
+    size_t m = 0, n = 0, k = 0;
+    TensorP bias, mask;
+    bool relu = false;
+};
+
+static std::atomic<uint64_t> g_next_id{1};
+
+struct TensorImpl {
+    uint64_t id;
+    std::vector<size_t> dims;
+    size_t size = 1;
+    StorageP st;                          // null while `pending` is set
+    std::unique_ptr<PendingGemm> pending;
+    bool requires_grad = false;
+    explicit TensorImpl(const std::vector<size_t>& d) : id(g_next_id.fetch_add(1)), dims(d) {
+        for (size_t x : d) size *= x;
+    }
+};
+
+}  // namespace ts
+
+struct ts_tensor { ts::TensorP t; };
+
+namespace ts {
+
+static StorageP new_storage(DeviceCtx* c, size_t n) {
+    float* p = c->alloc.alloc((n ? n : 1) * sizeof(float));
+    if (!p) return nullptr;
+    auto s = std::make_shared<Storage>();
+    s->ptr = p; s->n = n; s->c = c;
+    return s;
+}
+
+static TensorP new_tensor(DeviceCtx* c, const std::vector<size_t>& dims) {
+    auto t = std::make_shared<TensorImpl>(dims);
+    t->st = new_storage(c, t->size);
+    if (!t->st) return nullptr;
+    return t;
+}
+
+static bool materialize(const TensorP& t);
+
+// Device pointer for reading on the compute stream (launches a deferred GEMM, waits for an upload).
+static const float* rptr(const TensorP& t) {
+    if (!materialize(t)) return nullptr;
+    Storage* s = t->st.get();
+    if (s->ready) {
+        cudaStreamWaitEvent(s->c->compute, s->ready, 0);
+        cudaEventDestroy(s->ready);
+        s->ready = nullptr;
+    }
+    return s->ptr;
+}
+
+static bool materialize(const TensorP& t) {
+    if (!t->pending) return t->st != nullptr;
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    PendingGemm& p = *t->pending;
+    const float* a = rptr(p.a);
+    const float* b = rptr(p.b);
+    const float* bias = p.bias ? rptr(p.bias) : nullptr;
+    const float* mask = p.mask ? rptr(p.mask) : nullptr;
+    if (!a || !b || (p.bias && !bias) || (p.mask && !mask)) return false;
+    StorageP st = new_storage(c, t->size);
+    if (!st) return false;
+    k::GemmArgs g{a, b, st->ptr, p.m, p.n, p.k, p.ta, p.tb, bias, p.relu, mask};
+    if (!k::gemm(g, -1, c, c->compute)) return false;
+    t->st = st;
+    t->pending.reset();   // releases the operand references
+    return true;
+}
+
+// ------------------------------------------------------------------ tape
+enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean };
+
+struct Saved {
+    TensorP t;
+    uint64_t version = 0;
+    void set(const TensorP& x) { t = x; version = x->st ? x->st->version : 0; }
+    bool check(const char* what) const {
+        uint64_t now = t->st ? t->st->version : 0;
+        if (now != version) {
+            set_error("backward: the tensor saved for %s (id %llu) was modified in place after the forward pass", what,
+                      (unsigned long long)t->id);
+            return false;
+        }
+        return true;
+    }
+};
+
+struct Node {
+    Op op;
+    std::vector<uint64_t> inputs;       // ids, positional: [a, b] or [x]
+    std::vector<bool> needs;            // which inputs want a gradient
+    Saved s0, s1;                       // saved tensors (meaning depends on op)
+    std::vector<size_t> dims0, dims1;   // operand shapes
+    float scalar = 0.0f;
+};
+
+struct Graph {
+    std::unordered_map<uint64_t, Node> ops;
+    std::unordered_map<uint64_t, TensorP> grads;
+    std::unordered_map<uint64_t, TensorP> bias_grad_ready;   // column sums produced early by a fused kernel, keyed by the Add output id
+};
+
+static thread_local Graph g_graph;
+static thread_local int g_no_grad_depth = 0;
+static thread_local std::vector<std::weak_ptr<TensorImpl>> g_pending_registry;
+
+static bool grad_on() { return g_no_grad_depth == 0; }
+
+static void register_pending(const TensorP& t) {
+    if (g_pending_registry.size() > 4096) {
+        auto& v = g_pending_registry;
+        v.erase(std::remove_if(v.begin(), v.end(), [](const std::weak_ptr<TensorImpl>& w) { auto s = w.lock(); return !s || !s->pending; }), v.end());
+    }
+    g_pending_registry.push_back(t);
+}
+// Before any in-place write: launch what still depends on the old contents.
+static bool flush_pending() {
+    auto reg = std::move(g_pending_registry);
+    g_pending_registry.clear();
+    bool ok = true;
+    for (auto& w : reg) {
+        TensorP t = w.lock();
+        if (t && t->pending) ok = materialize(t) && ok;
+    }
+    return ok;
+}
+
+// ------------------------------------------------------------------ data-parallel state
+struct DpState {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    std::unordered_set<uint64_t> params;
+    cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
+    bool comm_outstanding = false;
+};
+static thread_local DpState g_dp;
+
+static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n) {
+    if (!g_dp.comm || g_dp.world <= 1) return true;
+    if (!g_dp.ev_compute) {
+        TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_compute, cudaEventDisableTiming));
+        TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_comm, cudaEventDisableTiming));
+    }
+    TS_CHECK(cudaEventRecord(g_dp.ev_compute, c->compute));
+    TS_CHECK(cudaStreamWaitEvent(c->comm, g_dp.ev_compute, 0));
+    ncclResult_t r = ncclAllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm);
+    if (r != ncclSuccess) { set_error("ncclAllReduce failed: %s", ncclGetErrorString(r)); return false; }
+    g_dp.comm_outstanding = true;
+    return true;
+}
+static bool dp_join(DeviceCtx* c) {
+    if (!g_dp.comm_outstanding) return true;
+    TS_CHECK(cudaEventRecord(g_dp.ev_comm, c->comm));
+    TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.ev_comm, 0));
+    g_dp.comm_outstanding = false;
+    return true;
+}
+
+// ------------------------------------------------------------------ helpers
+static bool same_dims(const std::vector<size_t>& a, const std::vector<size_t>& b) { return a == b; }
+
+static std::vector<size_t> strip_leading_ones(const std::vector<size_t>& d) {
+    size_t i = 0;
+    while (i + 1 < d.size() && d[i] == 1) ++i;
+    return std::vector<size_t>(d.begin() + i, d.end());
+}
+// `small` broadcasts over the leading dimensions of `big` (e.g. [M,N] + [N], [M,N] + [1,N]).
+static bool is_suffix_broadcast(const std::vector<size_t>& big, const std::vector<size_t>& small, size_t* rows, size_t* cols) {
+    std::vector<size_t> s = strip_leading_ones(small);
+    if (s.size() > big.size()) return false;
+    size_t off = big.size() - s.size();
+    size_t c = 1;
+    for (size_t i = 0; i < s.size(); ++i) {
+        if (s[i] != big[off + i]) return false;
+        c *= s[i];
+    }
+    size_t r = 1;
+    for (size_t i = 0; i < off; ++i) r *= big[i];
+    *rows = r; *cols = c;
+    return true;
+}
+
+static TensorP grad_lookup(uint64_t id) {
+    auto it = g_graph.grads.find(id);
+    return it == g_graph.grads.end() ? nullptr : it->second;
+}
+
+// gradtrack/engine.rs:514-524: existing + new into a fresh tensor.
+static bool accumulate(DeviceCtx* c, uint64_t id, const TensorP& g) {
+    auto it = g_graph.grads.find(id);
+    if (it == g_graph.grads.end()) { g_graph.grads[id] = g; return true; }
+    g_graph.bias_grad_ready.erase(id);   // a second contribution invalidates early column sums
+    const float* a = rptr(it->second);
+    const float* b = rptr(g);
+    if (!a || !b) return false;
+    if (it->second->size != g->size) { set_error("backward: gradient size mismatch for tensor %llu", (unsigned long long)id); return false; }
+    TensorP out = new_tensor(c, it->second->dims);
+    if (!out) return false;
+    if (!k::binary(0, a, b, out->st->ptr, out->size, c->compute)) return false;
+    it->second = out;
+    return true;
+}
+
+static TensorP reshaped_alias(const TensorP& t, const std::vector<size_t>& dims) {
+    if (t->dims == dims) return t;
+    if (!materialize(t)) return nullptr;
+    auto r = std::make_shared<TensorImpl>(dims);
+    r->st = t->st;
+    return r;
+}
+
+// ------------------------------------------------------------------ backward of one node
+static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& go, std::vector<TensorP>& gin) {
+    cudaStream_t s = c->compute;
+    gin.assign(nd.inputs.size(), nullptr);
+    switch (nd.op) {
+        case Op::Add: {
+            // grad_fn/ops/add.rs:4-28 + grad_fn/utils.rs:23-60: the gradient itself, summed back over
+            // broadcast dimensions for the smaller operand.
+            for (int i = 0; i < 2; ++i) {
+                if (!nd.needs[i]) continue;
+                const std::vector<size_t>& od = i == 0 ? nd.dims0 : nd.dims1;
+                const std::vector<size_t>& other = i == 0 ? nd.dims1 : nd.dims0;
+                size_t osz = 1; for (size_t x : od) osz *= x;
+                if (osz == go->size) { gin[i] = reshaped_alias(go, od); if (!gin[i]) return false; continue; }
+                size_t rows, cols;
+                if (!is_suffix_broadcast(other, od, &rows, &cols)) { set_error("backward(add): unsupported broadcast"); return false; }
+                auto pre = g_graph.bias_grad_ready.find(out_id);
+                if (pre != g_graph.bias_grad_ready.end() && pre->second->size == cols) {
+                    gin[i] = reshaped_alias(pre->second, od);
+                    g_graph.bias_grad_ready.erase(pre);
+                    continue;
+                }
+                const float* gp = rptr(go);
+                if (!gp) return false;
+                TensorP r = new_tensor(c, od);
+                if (!r) return false;
+                if (cols == 1) {
+                    if (!k::sum(gp, r->st->ptr, go->size, false, c->reduce_scratch, s)) return false;
+                } else {
+                    size_t sc = k::colsum_scratch_elems(rows, cols);
+                    float* scratch = c->alloc.alloc(sc * sizeof(float));
+                    if (!scratch) return false;
+                    bool ok = k::colsum(gp, r->st->ptr, rows, cols, scratch, s);
+                    c->alloc.free(scratch);   // reused only by later work on the same stream
+                    if (!ok) return false;
+                }
+                gin[i] = r;
+            }
+            return true;
+        }
+        case Op::Sub: {
+            // grad_fn/ops/sub.rs:4-33: (go, -go)
+            if (nd.needs[0]) gin[0] = go;
+            if (nd.needs[1]) {
+                const float* gp = rptr(go);
+                TensorP r = gp ? new_tensor(c, go->dims) : nullptr;
+                if (!r || !k::scale(gp, -1.0f, r->st->ptr, r->size, s)) return false;
+                gin[1] = r;
+            }
+            return true;
+        }
+        case Op::Mul:
+        case Op::Div: {
+            if (!nd.s0.check("mul/div") || !nd.s1.check("mul/div")) return false;
+            const float *a = rptr(nd.s0.t), *b = rptr(nd.s1.t), *gp = rptr(go);
+            if (!a || !b || !gp) return false;
+            TensorP ga = nd.needs[0] ? new_tensor(c, go->dims) : nullptr;
+            TensorP gb = nd.needs[1] ? new_tensor(c, go->dims) : nullptr;
+            if ((nd.needs[0] && !ga) || (nd.needs[1] && !gb)) return false;
+            bool ok = nd.op == Op::Mul ? k::mul_bwd(a, b, gp, ga ? ga->st->ptr : nullptr, gb ? gb->st->ptr : nullptr, go->size, s)
+                                       : k::div_bwd(a, b, gp, ga ? ga->st->ptr : nullptr, gb ? gb->st->ptr : nullptr, go->size, s);
+            if (!ok) return false;
+            gin[0] = ga; gin[1] = gb;
+            return true;
+        }
+        case Op::Relu: {
+            // grad_fn/ops/relu.rs:4-16 with the saved OUTPUT as the mask: relu(x) > 0 <=> x > 0.
+            if (!nd.needs[0]) return true;
+            if (!nd.s0.check("relu")) return false;
+            if (fusion_enabled() && go->pending && !go->pending->bias && !go->pending->relu && !go->pending->mask && go.use_count() == 1) {
+                go->pending->mask = nd.s0.t;   // fold the mask into the GEMM that produces this gradient
+                gin[0] = go;
+                return true;
+            }
+            const float *y = rptr(nd.s0.t), *gp = rptr(go);
+            if (!y || !gp) return false;
+            TensorP r = new_tensor(c, go->dims);
+            if (!r) return false;
+            // When the ReLU input came from a bias add, produce the bias gradient in the same pass.
+            auto prod = g_graph.ops.find(nd.inputs[0]);
+            if (fusion_enabled() && prod != g_graph.ops.end() && prod->second.op == Op::Add && g_graph.grads.find(nd.inputs[0]) == g_graph.grads.end()) {
+                Node& add = prod->second;
+                for (int i = 0; i < 2; ++i) {
+                    const std::vector<size_t>& od = i == 0 ? add.dims0 : add.dims1;
+                    const std::vector<size_t>& other = i == 0 ? add.dims1 : add.dims0;
+                    size_t osz = 1; for (size_t x : od) osz *= x;
+                    size_t rows, cols;
+                    if (add.needs[i] && osz != go->size && is_suffix_broadcast(other, od, &rows, &cols) && cols > 1) {
+                        TensorP db = new_tensor(c, {cols});
+                        if (!db) return false;
+                        size_t sc = k::colsum_scratch_elems(rows, cols);
+                        float* scratch = c->alloc.alloc(sc * sizeof(float));
+                        if (!scratch) return false;
+                        bool ok = k::relu_bwd_colsum(y, gp, r->st->ptr, db->st->ptr, rows, cols, scratch, s);
+                        c->alloc.free(scratch);
+                        if (!ok) return false;
+                        g_graph.bias_grad_ready[nd.inputs[0]] = db;
+                        gin[0] = r;
+                        return true;
+                    }
+                }
+            }
+            if (!k::relu_bwd(y, gp, r->st->ptr, r->size, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::MatMul: {
+            // grad_fn/ops/matmul.rs:68-80: dA = go . B^T, dB = A^T . go; the transposes are operand
+            // layouts of the GEMM, not copies.
+            if (!nd.s0.check("matmul") || !nd.s1.check("matmul")) return false;
+            const size_t m = nd.dims0.size() == 2 ? nd.dims0[0] : 1, kk = nd.dims0.back();
+            const size_t n = nd.dims1.size() == 2 ? nd.dims1[1] : 1;
+            if (nd.needs[0]) {
+                auto t = std::make_shared<TensorImpl>(nd.dims0);
+                t->pending.reset(new PendingGemm{go, nd.s1.t, false, true, m, kk, n, nullptr, nullptr, false});
+                register_pending(t);
+                gin[0] = t;
+            }
+            if (nd.needs[1]) {
+                auto t = std::make_shared<TensorImpl>(nd.dims1);
+                t->pending.reset(new PendingGemm{nd.s0.t, go, true, false, kk, n, m, nullptr, nullptr, false});
+                register_pending(t);
+                gin[1] = t;
+            }
+            return true;
+        }
+        case Op::PowScalar: {
+            if (!nd.needs[0]) return true;
+            if (!nd.s0.check("pow_scalar")) return false;
+            const float *x = rptr(nd.s0.t), *gp = rptr(go);
+            TensorP r = (x && gp) ? new_tensor(c, go->dims) : nullptr;
+            if (!r || !k::square_bwd(x, gp, r->st->ptr, r->size, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::ReduceSum:
+        case Op::ReduceMean: {
+            // grad_fn/reductions/sum.rs:4-16, mean.rs:4-30: fill with upstream, or (1/numel as f32) * upstream.
+            if (!nd.needs[0]) return true;
+            const float* gp = rptr(go);
+            TensorP r = gp ? new_tensor(c, nd.dims0) : nullptr;
+            if (!r) return false;
+            float scale = 1.0f;
+            if (nd.op == Op::ReduceMean) scale = r->size > 0 ? 1.0f / (float)r->size : 0.0f;
+            if (!k::fill_from_scalar(r->st->ptr, gp, scale, r->size, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+    }
+    set_error("backward: unknown op");
+    return false;
+}
+
+// A leaf's gradient is final: launch the GEMM that produces it and, under data parallelism,
+// start its all-reduce on the communication stream while the rest of backward proceeds.
+static bool finalize_leaf(DeviceCtx* c, uint64_t id, std::unordered_set<uint64_t>& reduced) {
+    TensorP lg = g_graph.grads[id];
+    if (!rptr(lg)) return false;
+    if (!g_dp.comm || !g_dp.params.count(id) || reduced.count(id)) return true;
+    if (lg->st.use_count() > 1) {
+        // the buffer is shared with another gradient: reduce a private copy
+        TensorP priv = new_tensor(c, lg->dims);
+        if (!priv || !cuda_ok(cudaMemcpyAsync(priv->st->ptr, lg->st->ptr, lg->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "gradient copy")) return false;
+        g_graph.grads[id] = priv;
+        lg = priv;
+    }
+    reduced.insert(id);
+    return dp_all_reduce_async(c, lg->st->ptr, lg->size);
+}
+
+static bool backward(const TensorP& root, const TensorP& grad_output) {
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    // seed: gradtrack/engine.rs:964-978
+    TensorP seed = grad_output;
+    if (!seed) {
+        seed = new_tensor(c, root->dims);
+        if (!seed || !k::fill(seed->st->ptr, 1.0f, seed->size, c->compute)) return false;
+    } else if (seed->size != root->size) {
+        set_error("backward: grad_output has %zu elements, tensor has %zu", seed->size, root->size);
+        return false;
+    }
+    if (!accumulate(c, root->id, seed)) return false;
+
+    // reachable operations, processed by descending id
+    std::vector<uint64_t> order, stack{root->id};
+    std::unordered_set<uint64_t> seen{root->id};
+    std::unordered_map<uint64_t, int> leaf_uses;   // leaf id -> number of reachable nodes that feed it a gradient
+    while (!stack.empty()) {
+        uint64_t id = stack.back();
+        stack.pop_back();
+        auto it = g_graph.ops.find(id);
+        if (it == g_graph.ops.end()) continue;
+        order.push_back(id);
+        Node& nd = it->second;
+        for (size_t i = 0; i < nd.inputs.size(); ++i) {
+            if (!nd.needs[i]) continue;
+            uint64_t in = nd.inputs[i];
+            if (g_graph.ops.find(in) == g_graph.ops.end()) leaf_uses[in]++;
+            if (seen.insert(in).second) stack.push_back(in);
+        }
+    }
+    std::sort(order.begin(), order.end(), std::greater<uint64_t>());
+
+    std::vector<TensorP> gin;
+    std::unordered_set<uint64_t> reduced;
+    for (uint64_t id : order) {
+        auto git = g_graph.grads.find(id);
+        if (git == g_graph.grads.end()) continue;
+        TensorP go = git->second;
+        if (id != root->id) g_graph.grads.erase(git);   // take_gradient, engine.rs:990-995; the root keeps its own
+        else go = git->second;
+        Node& nd = g_graph.ops[id];
+        if (!apply_node(c, id, nd, go, gin)) return false;
+        go.reset();
+        for (size_t i = 0; i < gin.size(); ++i) {
+            if (!gin[i]) continue;
+            uint64_t in = nd.inputs[i];
+            if (!accumulate(c, in, gin[i])) return false;
+            gin[i].reset();
+            auto lu = leaf_uses.find(in);
+            if (lu != leaf_uses.end() && --lu->second == 0) {
+                // the leaf's gradient is final: run its GEMM now and, under data parallelism,
+                // start its all-reduce while the rest of backward proceeds
+                if (!finalize_leaf(c, in, reduced)) return false;
+            }
+        }
+    }
+    // registered parameters whose gradient did not go through the counting above
+    if (g_dp.comm)
+        for (uint64_t id : g_dp.params)
+            if (!reduced.count(id) && g_graph.grads.count(id) && !finalize_leaf(c, id, reduced)) return false;
+    g_graph.bias_grad_ready.clear();
+    return dp_join(c);   // the compute stream continues only after every all-reduce has landed
+}
+
+// ------------------------------------------------------------------ Adam
+struct AdamState { StorageP m, v; uint64_t step = 0; size_t n = 0; };
+
+}  // namespace ts
+
+struct ts_adam {
+    float lr, beta1, beta2, eps, wd;
+    uint64_t step_count = 0;
+    std::unordered_map<uint64_t, ts::AdamState> states;
+    std::vector<uint64_t> order;                 // insertion order, adam/mod.rs:201-206
+    // launch tables
+    std::vector<unsigned long long> cached_sizes;
+    float* chunks_dev = nullptr;
+    int n_chunks = 0;
+    float* tensors_dev = nullptr;
+    ts::k::AdamTensor* tensors_host = nullptr;   // pinned
+    size_t tensors_cap = 0;
+    ts::DeviceCtx* c = nullptr;
+};
+
+using namespace ts;
+
+// ====================================================================== C ABI: tensors
+static std::vector<size_t> to_dims(const unsigned long long* dims, int rank) {
+    std::vector<size_t> d;
+    for (int i = 0; i < rank; ++i) d.push_back((size_t)dims[i]);
+    if (d.empty()) d.push_back(1);
+    return d;
+}
+static ts_tensor* wrap(const TensorP& t) {
+    if (!t) return nullptr;
+    ts_tensor* h = new ts_tensor();
+    h->t = t;
+    return h;
+}
+
+TS_API ts_tensor* ts_tensor_new(const unsigned long long* dims, int rank) {
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    if (rank < 0 || (rank > 0 && !dims)) { set_error("ts_tensor_new: bad shape"); return nullptr; }
+    return wrap(new_tensor(c, to_dims(dims, rank)));
+}
+static ts_tensor* filled(const unsigned long long* dims, int rank, float v) {
+    ts_tensor* h = ts_tensor_new(dims, rank);
+    if (!h) return nullptr;
+    if (!k::fill(h->t->st->ptr, v, h->t->size, h->t->st->c->compute)) { delete h; return nullptr; }
+    return h;
+}
+TS_API ts_tensor* ts_tensor_zeros(const unsigned long long* dims, int rank) { return filled(dims, rank, 0.0f); }
+TS_API ts_tensor* ts_tensor_ones(const unsigned long long* dims, int rank) { return filled(dims, rank, 1.0f); }
+
+TS_API ts_tensor* ts_tensor_from_slice(const float* host, const unsigned long long* dims, int rank) {
+    ts_tensor* h = ts_tensor_new(dims, rank);
+    if (!h) return nullptr;
+    if (h->t->size && !host) { set_error("ts_tensor_from_slice: null data"); delete h; return nullptr; }
+    DeviceCtx* c = h->t->st->c;
+    if (h->t->size) {
+        if (!cuda_ok(cudaMemcpyAsync(h->t->st->ptr, host, h->t->size * sizeof(float), cudaMemcpyHostToDevice, c->compute), "upload") ||
+            !cuda_ok(cudaStreamSynchronize(c->compute), "upload sync")) { delete h; return nullptr; }
+    }
+    return h;
+}
+
+TS_API ts_tensor* ts_tensor_from_pinned_async(const float* host, const unsigned long long* dims, int rank) {
+    ts_tensor* h = ts_tensor_new(dims, rank);
+    if (!h) return nullptr;
+    if (h->t->size && !host) { set_error("ts_tensor_from_pinned_async: null data"); delete h; return nullptr; }
+    DeviceCtx* c = h->t->st->c;
+    Storage* st = h->t->st.get();
+    // The block may have been used by kernels already queued on the compute stream: the copy waits for those.
+    cudaEvent_t before = nullptr;
+    bool ok = cuda_ok(cudaEventCreateWithFlags(&before, cudaEventDisableTiming), "event") &&
+              cuda_ok(cudaEventRecord(before, c->compute), "event record") &&
+              cuda_ok(cudaStreamWaitEvent(c->copy, before, 0), "stream wait") &&
+              cuda_ok(cudaMemcpyAsync(st->ptr, host, h->t->size * sizeof(float), cudaMemcpyHostToDevice, c->copy), "async upload") &&
+              cuda_ok(cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming), "event") &&
+              cuda_ok(cudaEventRecord(st->ready, c->copy), "event record");
+    if (before) cudaEventDestroy(before);
+    if (!ok) { delete h; return nullptr; }
+    return h;
+}
+
+TS_API void ts_tensor_free(ts_tensor* t) { delete t; }
+
+TS_API unsigned long long ts_tensor_id(const ts_tensor* t) { return t ? t->t->id : 0; }
+TS_API int ts_tensor_rank(const ts_tensor* t) { return t ? (int)t->t->dims.size() : 0; }
+TS_API unsigned long long ts_tensor_size(const ts_tensor* t) { return t ? t->t->size : 0; }
+TS_API bool ts_tensor_dims(const ts_tensor* t, unsigned long long* out) {
+    if (!t || !out) { set_error("ts_tensor_dims: null argument"); return false; }
+    for (size_t i = 0; i < t->t->dims.size(); ++i) out[i] = t->t->dims[i];
+    return true;
+}
+TS_API bool ts_tensor_requires_grad(const ts_tensor* t) { return t && t->t->requires_grad; }
+TS_API bool ts_tensor_set_requires_grad(ts_tensor* t, bool rg) {
+    if (!t) { set_error("ts_tensor_set_requires_grad: null tensor"); return false; }
+    t->t->requires_grad = rg;
+    return true;
+}
+TS_API float* ts_tensor_data_ptr(ts_tensor* t) {
+    if (!t) { set_error("ts_tensor_data_ptr: null tensor"); return nullptr; }
+    return const_cast<float*>(rptr(t->t));
+}
+TS_API bool ts_tensor_to_host(ts_tensor* t, float* out) {
+    if (!t || (!out && t->t->size)) { set_error("ts_tensor_to_host: null argument"); return false; }
+    const float* p = rptr(t->t);
+    if (!p) return false;
+    DeviceCtx* c = t->t->st->c;
+    if (t->t->size) TS_CHECK(cudaMemcpyAsync(out, p, t->t->size * sizeof(float), cudaMemcpyDeviceToHost, c->compute));
+    return ts_sync_stream(nullptr);
+}
+TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
+    if (!t || (!host && t->t->size)) { set_error("ts_tensor_copy_from_host: null argument"); return false; }
+    if (!flush_pending() || !rptr(t->t)) return false;
+    Storage* st = t->t->st.get();
+    TS_CHECK(cudaMemcpyAsync(st->ptr, host, t->t->size * sizeof(float), cudaMemcpyHostToDevice, st->c->compute));
+    TS_CHECK(cudaStreamSynchronize(st->c->compute));
+    st->version++;
+    return true;
+}
+TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
+    if (!t) { set_error("ts_tensor_fill: null tensor"); return false; }
+    if (!flush_pending() || !rptr(t->t)) return false;
+    Storage* st = t->t->st.get();
+    if (!k::fill(st->ptr, v, t->t->size, st->c->compute)) return false;
+    st->version++;
+    return true;
+}
+
+// ====================================================================== C ABI: ops
+static void record(const TensorP& out, Node&& nd) {
+    out->requires_grad = true;
+    g_graph.ops[out->id] = std::move(nd);
+}
+
+static ts_tensor* binary_op(ts_tensor* ha, ts_tensor* hb, int op, const char* name) {
+    if (!ha || !hb) { set_error("%s: null tensor", name); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP a = ha->t, b = hb->t;
+    TensorP out;
+    bool track = grad_on() && (a->requires_grad || b->requires_grad);
+    if (same_dims(a->dims, b->dims)) {
+        const float *pa = rptr(a), *pb = rptr(b);
+        out = (pa && pb) ? new_tensor(c, a->dims) : nullptr;
+        if (!out || !k::binary(op, pa, pb, out->st->ptr, out->size, c->compute)) return nullptr;
+    } else if (op == 0) {
+        // add with broadcasting (add.rs:107-146 -> broadcasting.rs:299-333), without materialising the broadcast
+        TensorP big = a->size >= b->size ? a : b, small = a->size >= b->size ? b : a;
+        size_t rows, cols;
+        if (!is_suffix_broadcast(big->dims, small->dims, &rows, &cols)) {
+            set_error("add_tensor: shapes are not broadcast-compatible on this path (a smaller operand must match the trailing dimensions)");
+            return nullptr;
+        }
+        // deferred GEMM + row bias: fold the add into the GEMM epilogue
+        if (fusion_enabled() && big->pending && !big->pending->bias && !big->pending->relu && !big->pending->mask && cols == big->pending->n && cols > 1) {
+            out = std::make_shared<TensorImpl>(big->dims);
+            out->pending.reset(new PendingGemm(*big->pending));
+            out->pending->bias = small;
+            register_pending(out);
+        } else {
+            const float *pb = rptr(big), *ps = rptr(small);
+            out = (pb && ps) ? new_tensor(c, big->dims) : nullptr;
+            if (!out) return nullptr;
+            bool ok = cols == 1 ? k::add_scalar_bcast(pb, ps, out->st->ptr, out->size, c->compute)
+                                : k::bias_act(pb, ps, out->st->ptr, rows, cols, false, c->compute);
+            if (!ok) return nullptr;
+        }
+    } else {
+        set_error("%s: operands must have the same shape on this path (broadcasting is implemented for add_tensor only)", name);
+        return nullptr;
+    }
+    if (track) {
+        Node nd;
+        nd.op = op == 0 ? Op::Add : op == 1 ? Op::Sub : op == 2 ? Op::Mul : Op::Div;
+        nd.inputs = {a->id, b->id};
+        nd.needs = {a->requires_grad, b->requires_grad};
+        nd.dims0 = a->dims; nd.dims1 = b->dims;
+        if (op >= 2) { nd.s0.set(a); nd.s1.set(b); }
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+TS_API ts_tensor* ts_tensor_add_tensor(ts_tensor* a, ts_tensor* b) { return binary_op(a, b, 0, "add_tensor"); }
+TS_API ts_tensor* ts_tensor_sub_tensor(ts_tensor* a, ts_tensor* b) { return binary_op(a, b, 1, "sub_tensor"); }
+TS_API ts_tensor* ts_tensor_mul_tensor(ts_tensor* a, ts_tensor* b) { return binary_op(a, b, 2, "mul_tensor"); }
+TS_API ts_tensor* ts_tensor_div_tensor(ts_tensor* a, ts_tensor* b) { return binary_op(a, b, 3, "div_tensor"); }
+
+TS_API ts_tensor* ts_tensor_matmul(ts_tensor* ha, ts_tensor* hb) {
+    if (!ha || !hb) { set_error("matmul: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP a = ha->t, b = hb->t;
+    const size_t ra = a->dims.size(), rb = b->dims.size();
+    if (ra < 1 || ra > 2 || rb < 1 || rb > 2) { set_error("matmul: only 1-D and 2-D operands are implemented on this path"); return nullptr; }
+    // rank dispatch: matmul/mod.rs:263-310
+    const size_t m = ra == 2 ? a->dims[0] : 1, ka = a->dims.back();
+    const size_t kb = b->dims[0], n = rb == 2 ? b->dims[1] : 1;
+    if (ka != kb) { set_error("matmul: inner dimensions differ (%zu vs %zu)", ka, kb); return nullptr; }
+    std::vector<size_t> od;
+    if (ra == 2) od.push_back(m);
+    if (rb == 2) od.push_back(n);   // 1-D . 1-D gives a rank-0 tensor with one element (matmul/mod.rs:88-98)
+    auto out = std::make_shared<TensorImpl>(od);
+    out->pending.reset(new PendingGemm{a, b, false, false, m, n, ka, nullptr, nullptr, false});
+    if (fusion_enabled()) register_pending(out);
+    else if (!materialize(out)) return nullptr;
+    if (grad_on() && (a->requires_grad || b->requires_grad)) {
+        Node nd;
+        nd.op = Op::MatMul;
+        nd.inputs = {a->id, b->id};
+        nd.needs = {a->requires_grad, b->requires_grad};
+        nd.dims0 = a->dims; nd.dims1 = b->dims;
+        nd.s0.set(a); nd.s1.set(b);
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+TS_API ts_tensor* ts_tensor_relu(ts_tensor* hx) {
+    if (!hx) { set_error("relu: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t, out;
+    if (fusion_enabled() && x->pending && !x->pending->relu && !x->pending->mask) {
+        out = std::make_shared<TensorImpl>(x->dims);
+        out->pending.reset(new PendingGemm(*x->pending));
+        out->pending->relu = true;
+        register_pending(out);
+    } else {
+        const float* px = rptr(x);
+        out = px ? new_tensor(c, x->dims) : nullptr;
+        if (!out || !k::relu(px, out->st->ptr, out->size, c->compute)) return nullptr;
+    }
+    if (grad_on() && x->requires_grad) {
+        Node nd;
+        nd.op = Op::Relu;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.s0.set(out);   // the output doubles as the mask
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+TS_API ts_tensor* ts_tensor_pow_scalar(ts_tensor* hx, float exponent) {
+    if (!hx) { set_error("pow_scalar: null tensor"); return nullptr; }
+    if (exponent != 2.0f) { set_error("pow_scalar: only exponent 2.0 is implemented on this path (got %g)", (double)exponent); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+    if (!out || !k::square(px, out->st->ptr, out->size, c->compute)) return nullptr;
+    if (grad_on() && x->requires_grad) {
+        Node nd;
+        nd.op = Op::PowScalar;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.scalar = exponent;
+        nd.s0.set(x);
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+static ts_tensor* reduce_all(ts_tensor* hx, bool mean) {
+    if (!hx) { set_error("sum/mean: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, {1}) : nullptr;
+    if (!out || !k::sum(px, out->st->ptr, x->size, mean, c->reduce_scratch, c->compute)) return nullptr;
+    // The reference registers these nodes even under NoGradTrack (reductions/sum.rs:131, mean.rs:99).
+    if (x->requires_grad) {
+        Node nd;
+        nd.op = mean ? Op::ReduceMean : Op::ReduceSum;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+TS_API ts_tensor* ts_tensor_sum(ts_tensor* x) { return reduce_all(x, false); }
+TS_API ts_tensor* ts_tensor_mean(ts_tensor* x) { return reduce_all(x, true); }
+
+// ====================================================================== C ABI: gradtrack
+TS_API bool ts_tensor_backward(ts_tensor* t, ts_tensor* grad_output) {
+    if (!t) { set_error("backward: null tensor"); return false; }
+    return ts::backward(t->t, grad_output ? grad_output->t : nullptr);
+}
+TS_API ts_tensor* ts_tensor_grad_by_value(const ts_tensor* t) {
+    if (!t) return nullptr;
+    TensorP g = grad_lookup(t->t->id);
+    if (!g) return nullptr;
+    if (!materialize(g)) return nullptr;
+    return wrap(reshaped_alias(g, t->t->dims));
+}
+TS_API void ts_clear_gradients(void) {
+    g_graph.ops.clear();
+    g_graph.grads.clear();
+    g_graph.bias_grad_ready.clear();
+}
+TS_API void ts_no_grad_push(void) { ++g_no_grad_depth; }
+TS_API void ts_no_grad_pop(void) { if (g_no_grad_depth > 0) --g_no_grad_depth; }
+TS_API bool ts_is_grad_enabled(void) { return grad_on(); }
+TS_API unsigned long long ts_tape_len(void) { return g_graph.ops.size(); }
+
+// ====================================================================== C ABI: Adam
+TS_API ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float weight_decay) {
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    ts_adam* o = new ts_adam();
+    o->lr = lr; o->beta1 = beta1; o->beta2 = beta2; o->eps = eps; o->wd = weight_decay;
+    o->c = c;
+    return o;
+}
+TS_API void ts_adam_free(ts_adam* o) {
+    if (!o) return;
+    if (o->c) {
+        o->c->alloc.free(o->chunks_dev);
+        o->c->alloc.free(o->tensors_dev);
+    }
+    if (o->tensors_host) cudaFreeHost(o->tensors_host);
+    delete o;
+}
+TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
+    if (!o || !p) { set_error("add_parameter: null argument"); return false; }
+    if (!p->t->requires_grad) { set_error("add_parameter: parameter must require gradients"); return false; }   // adam/mod.rs:287-300
+    if (o->states.count(p->t->id)) return true;
+    AdamState st;
+    st.n = p->t->size;
+    st.m = new_storage(o->c, st.n);
+    st.v = new_storage(o->c, st.n);
+    if (!st.m || !st.v) return false;
+    if (!k::fill(st.m->ptr, 0.0f, st.n, o->c->compute) || !k::fill(st.v->ptr, 0.0f, st.n, o->c->compute)) return false;
+    o->states[p->t->id] = st;
+    o->order.push_back(p->t->id);
+    return true;
+}
+
+TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad_scale) {
+    if (!o || (n > 0 && !params)) { set_error("adam step: null argument"); return false; }
+    DeviceCtx* c = o->c;
+    if (!flush_pending()) return false;
+    o->step_count += 1;   // adam/mod.rs:1037
+    std::vector<k::AdamTensor> tab;
+    std::vector<unsigned long long> sizes;
+    std::vector<StorageP> touched;
+    std::string skipped;
+    for (int i = 0; i < n; ++i) {
+        if (!params[i]) { set_error("adam step: null parameter at index %d", i); return false; }
+        TensorP p = params[i]->t;
+        auto it = o->states.find(p->id);
+        if (it == o->states.end()) {   // adam/mod.rs:489-492 asserts
+            set_error("adam step: parameter %llu is not linked to the optimizer; call add_parameter first", (unsigned long long)p->id);
+            return false;
+        }
+        TensorP g = grad_lookup(p->id);
+        if (!g) {   // adam/mod.rs:494-497, 1039-1042: reported and skipped
+            skipped += (skipped.empty() ? "" : ", ") + std::to_string(p->id);
+            continue;
+        }
+        const float* gp = rptr(g);
+        float* pp = const_cast<float*>(rptr(p));
+        if (!gp || !pp) return false;
+        if (g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
+        it->second.step += 1;
+        tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size});
+        sizes.push_back(p->size);
+        touched.push_back(p->st);
+    }
+    if (!dp_join(c)) return false;   // gradient all-reduces must have landed
+    if (!tab.empty()) {
+        if (sizes != o->cached_sizes) {
+            int nc = k::adam_chunk_count(sizes.data(), (int)sizes.size());
+            size_t bytes = k::adam_chunk_bytes(nc);
+            std::vector<char> host(bytes);
+            k::adam_build_chunks(sizes.data(), (int)sizes.size(), host.data());
+            c->alloc.free(o->chunks_dev);
+            o->chunks_dev = c->alloc.alloc(bytes ? bytes : 16);
+            if (!o->chunks_dev) return false;
+            TS_CHECK(cudaMemcpyAsync(o->chunks_dev, host.data(), bytes, cudaMemcpyHostToDevice, c->compute));
+            TS_CHECK(cudaStreamSynchronize(c->compute));
+            o->n_chunks = nc;
+            o->cached_sizes = sizes;
+        }
+        if (tab.size() > o->tensors_cap) {
+            if (o->tensors_host) cudaFreeHost(o->tensors_host);
+            c->alloc.free(o->tensors_dev);
+            o->tensors_cap = tab.size() + 8;
+            TS_CHECK(cudaMallocHost(&o->tensors_host, 2 * o->tensors_cap * sizeof(k::AdamTensor)));
+            o->tensors_dev = c->alloc.alloc(o->tensors_cap * sizeof(k::AdamTensor));
+            if (!o->tensors_dev) return false;
+        }
+        // Two pinned slots used alternately: the copy of step t may still be in flight when step t+1 fills its table.
+        k::AdamTensor* slot = o->tensors_host + (o->step_count & 1) * o->tensors_cap;
+        memcpy(slot, tab.data(), tab.size() * sizeof(k::AdamTensor));
+        TS_CHECK(cudaMemcpyAsync(o->tensors_dev, slot, tab.size() * sizeof(k::AdamTensor), cudaMemcpyHostToDevice, c->compute));
+        // bias corrections in f64 from the f32-rounded betas, then to f32: adam/mod.rs:526-531, :793
+        const float stepf = (float)o->step_count;
+        const float bc1 = (float)(1.0 - std::pow((double)o->beta1, (double)stepf));
+        const float bc2 = (float)(1.0 - std::pow((double)o->beta2, (double)stepf));
+        const float f1 = 1.0f / bc1, f2 = 1.0f / bc2;
+        double total = 0;
+        for (unsigned long long sz : sizes) total += (double)sz;
+        if (!k::adam_launch((const k::AdamTensor*)o->tensors_dev, o->chunks_dev, o->n_chunks, total, o->lr, o->beta1, o->beta2, o->eps,
+                            o->wd, f1, f2, grad_scale, c->compute))
+            return false;
+        for (auto& s : touched) s->version++;
+    }
+    if (!skipped.empty()) {
+        set_error("adam step: parameter(s) %s have no gradient and were skipped", skipped.c_str());
+    } else {
+        set_error("%s", "");
+    }
+    return true;
+}
+
+TS_API void ts_adam_zero_grad(ts_adam* o, ts_tensor* const* params, int n) {
+    (void)o; (void)params; (void)n;
+    ts_clear_gradients();   // adam/mod.rs:1061-1068 clears the whole thread-local graph
+}
+TS_API float ts_adam_learning_rate(const ts_adam* o) { return o ? o->lr : 0.0f; }
+TS_API void ts_adam_set_learning_rate(ts_adam* o, float lr) { if (o) o->lr = lr; }
+TS_API unsigned long long ts_adam_step_count(const ts_adam* o) { return o ? o->step_count : 0; }
+
+static ts_tensor* state_view(const ts_adam* o, const ts_tensor* p, bool second) {
+    if (!o || !p) return nullptr;
+    auto it = o->states.find(p->t->id);
+    if (it == o->states.end()) return nullptr;
+    auto t = std::make_shared<TensorImpl>(p->t->dims);
+    t->st = second ? it->second.v : it->second.m;
+    return wrap(t);
+}
+TS_API ts_tensor* ts_adam_state_m(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, false); }
+TS_API ts_tensor* ts_adam_state_v(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, true); }
+
+// ====================================================================== C ABI: data parallel
+TS_API bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]) {
+    static_assert(sizeof(ncclUniqueId) == TS_DP_UNIQUE_ID_BYTES, "NCCL unique id size");
+    if (!id_out) { set_error("ts_dp_get_unique_id: null buffer"); return false; }
+    ncclUniqueId id;
+    ncclResult_t r = ncclGetUniqueId(&id);
+    if (r != ncclSuccess) { set_error("ncclGetUniqueId failed: %s", ncclGetErrorString(r)); return false; }
+    memcpy(id_out, &id, sizeof(id));
+    return true;
+}
+TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int rank, int world) {
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    if (!id_in || world < 1 || rank < 0 || rank >= world) { set_error("ts_dp_init: bad arguments (rank %d, world %d)", rank, world); return false; }
+    if (g_dp.comm) { set_error("ts_dp_init: already initialised on this thread"); return false; }
+    g_dp.rank = rank; g_dp.world = world;
+    if (world == 1) return true;
+    ncclUniqueId id;
+    memcpy(&id, id_in, sizeof(id));
+    ncclResult_t r = ncclCommInitRank(&g_dp.comm, world, id, rank);
+    if (r != ncclSuccess) { g_dp.comm = nullptr; set_error("ncclCommInitRank failed: %s", ncclGetErrorString(r)); return false; }
+    return true;
+}
+TS_API void ts_dp_finalize(void) {
+    DeviceCtx* c = ctx();
+    if (c) { cudaStreamSynchronize(c->comm); cudaStreamSynchronize(c->compute); }
+    if (g_dp.comm) { ncclCommDestroy(g_dp.comm); g_dp.comm = nullptr; }
+    if (g_dp.ev_compute) { cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); g_dp.ev_compute = g_dp.ev_comm = nullptr; }
+    g_dp.params.clear();
+    g_dp.rank = 0; g_dp.world = 1; g_dp.comm_outstanding = false;
+}
+TS_API int ts_dp_world_size(void) { return g_dp.world; }
+TS_API int ts_dp_rank(void) { return g_dp.rank; }
+TS_API bool ts_dp_register_parameters(ts_tensor* const* params, int n) {
+    if (n > 0 && !params) { set_error("ts_dp_register_parameters: null argument"); return false; }
+    g_dp.params.clear();
+    for (int i = 0; i < n; ++i) {
+        if (!params[i]) { set_error("ts_dp_register_parameters: null parameter at index %d", i); return false; }
+        g_dp.params.insert(params[i]->t->id);
+    }
+    return true;
+}
+TS_API bool ts_dp_all_reduce(float* data, unsigned long long size) {
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    if (!data && size) { set_error("ts_dp_all_reduce: null data"); return false; }
+    if (!dp_all_reduce_async(c, data, size)) return false;
+    return dp_join(c);
+}

@@ -1,0 +1,477 @@
+// TF32 GEMM on the 5th-generation tensor cores of sm_100a: TMA -> shared-memory ring ->
+// tcgen05.mma (kind::tf32, operands from shared memory, FP32 accumulators in tensor
+// memory) -> tcgen05.ld epilogue (bias / ReLU / ReLU-mask) -> global stores.
+//
+// One persistent CTA per SM walks a grouped tile order.  Warp roles:
+//   warp 0      : TMA producer (one lane)
+//   warp 1      : tensor-memory allocation (whole warp) and MMA issue (one lane)
+//   warps 2..5  : epilogue; warp w reads the TMEM lanes 32*(w%4) .. +31, one output row per thread
+// The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Operand layouts.  C[m,n] = sum_k A(m,k) B(k,n), all matrices row-major in global memory:
+//   A stored [m][k]  -> "K-major":  TMA box 32(k) x 128 rows, 128-byte swizzle
+//   A stored [k][m]  -> "MN-major": TMA boxes 32(m) x 32(k), four per tile, 128-byte swizzle
+//   B stored [n][k]  -> K-major;   B stored [k][n] -> MN-major (BN/32 boxes per tile)
+// so forward (A K-major, B MN-major), dA = dC.B^T (both K-major) and dB = A^T.dC (both
+// MN-major) all run without materialising a transpose.
+//
+// Every wait is bounded: when a barrier does not complete in about two seconds the waiting
+// thread raises the CTA's abort flag, writes an error code to a global word that the host
+// checks at its next synchronisation, drains its own copies (again bounded), and the CTA
+// frees its tensor memory and returns.
+//
+// No TMA load in this file uses cluster multicast: each CTA fetches its own tiles.
+#include <cuda.h>
+
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+namespace k {
+
+namespace {
+
+constexpr int BM = 128;          // rows of C per tile = TMEM lanes
+constexpr int BK = 32;           // f32 elements of K per pipeline stage = one 128-byte swizzle row
+constexpr int UMMA_K = 8;        // K of one tcgen05.mma.kind::tf32
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr long long kWaitCycles = 4000000000ll;   // about two seconds at 1.9 GHz
+
+enum ErrCode { kErrFullWait = 101, kErrEmptyWait = 102, kErrAccFullWait = 103, kErrAccEmptyWait = 104, kErrDrain = 105 };
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or when another thread of the CTA already had.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive columns of 32-bit accumulators: one row of 32 values per thread.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2 in bits 61..63), descriptor
+// version 1 in bits 46..47.  Addresses and offsets are stored without their 4 low bits.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::tf32 with FP32 accumulation:
+// bits 4-5 D format (1 = F32), 7-9 A format (2 = TF32), 10-12 B format, 15 A major, 16 B major
+// (0 = K, 1 = MN), 17-22 N >> 3, 24-28 M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 4;     // 16 KiB
+    static constexpr int kBBytes = BN * BK * 4;     // 32 or 16 KiB
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;        // two accumulator buffers
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // + alignment slack
+};
+
+struct KernelArgs {
+    float* c;
+    const float* bias;
+    const float* mask;
+    int relu;
+    uint32_t m, n, k;
+    int* error_flag;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, KernelArgs args) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle atoms are 1024 bytes: align the ring to that.
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + 2 + a); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * C::kStages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (args.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), kEpiThreads); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // grouped tile order: 16 row-tiles share their B panels in L2 while they sweep the columns
+    constexpr uint32_t kGroup = 16;
+    auto tile_coords = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
+        const uint32_t per_group = kGroup * tiles_n;
+        const uint32_t g = tile / per_group, r = tile % per_group;
+        const uint32_t first = g * kGroup;
+        const uint32_t gsz = (tiles_m - first) < kGroup ? (tiles_m - first) : kGroup;
+        tm = first + r % gsz;
+        tn = r / gsz;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int armed_parity[C::kStages];
+#pragma unroll
+            for (int s = 0; s < C::kStages; ++s) armed_parity[s] = -1;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t tm, tn;
+                tile_coords(tile, tm, tn);
+                const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); ok = false; break; }
+                    const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
+                    const int k0 = (int)(kb * BK);
+                    mbar_expect_tx(full_bar(stage), C::kStageBytes);
+                    if (A_MN) {
+#pragma unroll
+                        for (int b = 0; b < BM / 32; ++b) tma_load_2d(sa + b * 4096, &tm_a, full_bar(stage), m0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(sa, &tm_a, full_bar(stage), k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int b = 0; b < BN / 32; ++b) tma_load_2d(sb + b * 4096, &tm_b, full_bar(stage), n0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(sb, &tm_b, full_bar(stage), k0, n0);
+                    }
+#pragma unroll
+                    for (int s = 0; s < C::kStages; ++s)
+                        if (s == (int)stage) armed_parity[s] = (int)phase;
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // bounded drain of this thread's own copies before the CTA retires
+#pragma unroll
+                for (int s = 0; s < C::kStages; ++s) {
+                    if (armed_parity[s] >= 0) {
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(full_bar(s), (uint32_t)armed_parity[s])) {
+                            if (clock64() - t0 > kWaitCycles) { atomicCAS(args.error_flag, 0, kErrDrain); break; }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(A_MN, B_MN, BN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrFullWait); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // K-major: 32 bytes further inside the 128-byte swizzled row, 8-row groups 1024 B apart.
+                        // MN-major: the next group of eight k-rows (1024 B); 32-element column groups 4096 B apart.
+                        const uint64_t da = A_MN ? smem_desc(sa + kk * 1024, 4096, 1024) : smem_desc(sa + kk * 32, 16, 1024);
+                        const uint64_t db = B_MN ? smem_desc(sb + kk * 1024, 4096, 1024) : smem_desc(sb + kk * 32, 16, 1024);
+                        umma_tf32(d_tmem, da, db, idesc, (kb | (uint32_t)kk) != 0u ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar(acc));      // accumulator complete
+            }
+            if (!ok || *abort_flag) {
+                umma_commit(drain_bar);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(drain_bar, 0)) {
+                    if (clock64() - t0 > kWaitCycles) { atomicCAS(args.error_flag, 0, kErrDrain); break; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t lane_group = (uint32_t)(warp & 3);
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            uint32_t tm, tn;
+            tile_coords(tile, tm, tn);
+            const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+            if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccFullWait); ok = false; break; }
+            tc_fence_after();
+            const uint32_t row = tm * BM + lane_group * 32 + lane;
+            const bool row_ok = row < args.m;
+            float* crow = args.c + (size_t)row * args.n;
+            const float* mrow = args.mask ? args.mask + (size_t)row * args.n : nullptr;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((lane_group * 32u) << 16) + acc * BN + ch * 32, r);
+                tmem_ld_wait();
+                const uint32_t col0 = tn * BN + ch * 32;
+                if (row_ok) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const uint32_t col = col0 + q * 4;
+                        if (col < args.n) {   // n % 4 == 0: a float4 is either fully inside or fully outside
+                            float4 v = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                                                   __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+                            if (args.bias) {
+                                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+                                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+                            }
+                            if (args.relu) {
+                                v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f; v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
+                            }
+                            if (mrow) {
+                                const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
+                                v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
+                            }
+                            *reinterpret_cast<float4*>(crow + col) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty_bar(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// 2-D row-major f32 matrix [rows][cols]; box = box_cols (inner) x box_rows.
+bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) { set_error("gemm: cuTensorMapEncodeTiled is not available from the driver"); return false; }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("gemm: cuTensorMapEncodeTiled failed with code %d (rows %zu cols %zu box %u x %u)", (int)r, rows, cols, box_cols, box_rows); return false; }
+    return true;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+    using Cf = Cfg<BN>;
+    CUtensorMap tm_a, tm_b;
+    // A: stored [k][m] when transposed (MN-major) else [m][k]
+    if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32)) return false; }
+    else { if (!make_map(&tm_a, g.a, g.m, g.k, BK, BM)) return false; }
+    // B: stored [k][n] when not transposed (MN-major) else [n][k]
+    if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32)) return false; }
+    else { if (!make_map(&tm_b, g.b, g.n, g.k, BK, BN)) return false; }
+    auto kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
+    static bool attr_set[64] = {false};   // the attribute is per device
+    if (!attr_set[c->device]) {
+        TS_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes));
+        attr_set[c->device] = true;
+    }
+    size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN);
+    int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
+    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+    ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
+    kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, ka);
+    return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
+}
+
+template <int BN>
+bool launch_tc_bn(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+    const bool a_mn = g.trans_a, b_mn = !g.trans_b;
+    if (a_mn) return b_mn ? launch_tc<BN, true, true>(g, c, s) : launch_tc<BN, true, false>(g, c, s);
+    return b_mn ? launch_tc<BN, false, true>(g, c, s) : launch_tc<BN, false, false>(g, c, s);
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmArgs& g) {
+    if (g.m == 0 || g.n == 0 || g.k == 0) return false;
+    if (g.m >= (1ull << 31) || g.n >= (1ull << 31) || g.k >= (1ull << 31)) return false;
+    // TMA needs 16-byte aligned bases and row pitches; the epilogue stores float4.
+    const size_t a_cols = g.trans_a ? g.m : g.k, b_cols = g.trans_b ? g.k : g.n;
+    if (a_cols % 4 || b_cols % 4 || g.n % 4) return false;
+    if (!al16(g.a) || !al16(g.b) || !al16(g.c)) return false;
+    if (g.bias && !al16(g.bias)) return false;
+    if (g.mask && !al16(g.mask)) return false;
+    return true;
+}
+
+bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
+    (void)split3;
+    if (!gemm_tc_supported(g)) { set_error("gemm: shape or alignment not supported by the tensor-core kernel"); return false; }
+    size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
+    if (g.n <= 128 || tiles256 < (size_t)c->sm_count) return launch_tc_bn<128>(g, c, s);
+    return launch_tc_bn<256>(g, c, s);
+}
+
+bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
+    if (precision < 0) precision = matmul_precision();
+    if (precision >= 1 && gemm_tc_supported(g)) return gemm_tc(g, precision == 2, c, s);
+    return sgemm(g, s);
+}
+
+}  // namespace k
+}  // namespace ts
+
+// ====================================================================== C ABI
+using namespace ts;
+
+TS_API bool launch_gemm_kernel(const float* a, const float* b, float* cc, unsigned long long m, unsigned long long n,
+                               unsigned long long kk, int trans_a, int trans_b, const float* bias, int relu, const float* mask,
+                               int precision, void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    DeviceCtx* c = ctx();
+    if (!s || !c) return false;
+    if (precision < -1 || precision > 2) { set_error("launch_gemm_kernel: precision %d out of range", precision); return false; }
+    if (m && n && (!cc || (kk && (!a || !b)))) { set_error("launch_gemm_kernel: null pointer"); return false; }
+    k::GemmArgs g{a, b, cc, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0, bias, relu != 0, mask};
+    return k::gemm(g, precision, c, s);
+}
+
+TS_API bool launch_matmul_kernel(const float* a, const float* b, float* result, unsigned long long m, unsigned long long n,
+                                 unsigned long long kk, void* stream) {
+    if (!a || !b || !result) { set_error("launch_matmul_kernel: null pointer"); return false; }   // cuda_wrapper.cpp:82
+    return launch_gemm_kernel(a, b, result, m, n, kk, 0, 0, nullptr, 0, nullptr, -1, stream);
+}

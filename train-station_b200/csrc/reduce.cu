@@ -1,0 +1,282 @@
+// Reductions: full-tensor sum / mean (and the fused MSE loss), column sums for bias
+// gradients, and the fused ReLU-backward + column-sum.  All are HBM-bound single passes
+// over the data followed by a tiny second stage; both stages add in a fixed order, so
+// results are deterministic run to run.  The reference adds sequentially in f32
+// (reductions/sum.rs:93-105, :255-290); a tree differs from that in the last bits and is
+// closer to the exact sum.
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Block-wide sum; the result is valid in thread 0.
+__device__ __forceinline__ float block_sum(float v) {
+    __shared__ float sm[kThreads / 32];
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.0f;
+    if (threadIdx.x < 32) {
+        r = threadIdx.x < kThreads / 32 ? sm[threadIdx.x] : 0.0f;
+        r = warp_sum(r);
+    }
+    __syncthreads();
+    return r;
+}
+
+// MODE 0: sum(x); MODE 1: sum((x-y)^2)
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) sum_stage1(const float* __restrict__ x, const float* __restrict__ y,
+                                                       float* __restrict__ partial, size_t n, int vec_ok) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * kThreads;
+    if (vec_ok) {
+        const size_t n_vec = n / 4;
+        const float4* xv = reinterpret_cast<const float4*>(x);
+        const float4* yv = reinterpret_cast<const float4*>(y);
+        size_t i = tid;
+        // four independent loads in flight per thread
+        for (; i + 3 * nthreads < n_vec; i += 4 * nthreads) {
+            float4 a[4], b[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) a[u] = __ldcs(xv + i + u * nthreads);
+            if (MODE == 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) b[u] = __ldcs(yv + i + u * nthreads);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (MODE == 1) {
+                    float d0 = __fsub_rn(a[u].x, b[u].x), d1 = __fsub_rn(a[u].y, b[u].y);
+                    float d2 = __fsub_rn(a[u].z, b[u].z), d3 = __fsub_rn(a[u].w, b[u].w);
+                    acc[0] += __fmul_rn(d0, d0); acc[1] += __fmul_rn(d1, d1);
+                    acc[2] += __fmul_rn(d2, d2); acc[3] += __fmul_rn(d3, d3);
+                } else {
+                    acc[0] += a[u].x; acc[1] += a[u].y; acc[2] += a[u].z; acc[3] += a[u].w;
+                }
+            }
+        }
+        for (; i < n_vec; i += nthreads) {
+            float4 a = __ldcs(xv + i);
+            if (MODE == 1) {
+                float4 b = __ldcs(yv + i);
+                float d0 = __fsub_rn(a.x, b.x), d1 = __fsub_rn(a.y, b.y), d2 = __fsub_rn(a.z, b.z), d3 = __fsub_rn(a.w, b.w);
+                acc[0] += __fmul_rn(d0, d0); acc[1] += __fmul_rn(d1, d1); acc[2] += __fmul_rn(d2, d2); acc[3] += __fmul_rn(d3, d3);
+            } else {
+                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+            }
+        }
+        size_t t = n_vec * 4 + tid;   // n mod 4 leftovers
+        if (t < n) {
+            float a = x[t];
+            if (MODE == 1) { float d = __fsub_rn(a, y[t]); a = __fmul_rn(d, d); }
+            acc[0] += a;
+        }
+    } else {
+        for (size_t i = tid; i < n; i += nthreads) {
+            float a = x[i];
+            if (MODE == 1) { float d = __fsub_rn(a, y[i]); a = __fmul_rn(d, d); }
+            acc[0] += a;
+        }
+    }
+    float v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    v = block_sum(v);
+    if (threadIdx.x == 0) partial[blockIdx.x] = v;
+}
+
+__global__ void __launch_bounds__(kThreads) sum_stage2(const float* __restrict__ partial, int n_partial, float* __restrict__ out,
+                                                       float divisor) {
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < n_partial; i += kThreads) v += partial[i];
+    v = block_sum(v);
+    if (threadIdx.x == 0) out[0] = divisor > 0.0f ? __fdiv_rn(v, divisor) : v;
+}
+
+template <int MODE>
+bool sum_impl(const float* x, const float* y, float* out, size_t n, bool mean, float* scratch, cudaStream_t s) {
+    if (!out) { set_error("sum: null output"); return false; }
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    if (n == 0) return fill(out, 0.0f, 1, s);   // sum.rs:82-83 / mean.rs:50-52: empty -> 0
+    if (!x || (MODE == 1 && !y) || !scratch) { set_error("sum: null pointer"); return false; }
+    size_t per_cta = (size_t)kThreads * 16;
+    size_t want = (n + per_cta - 1) / per_cta;
+    size_t cap = (size_t)c->sm_count * 4;
+    if (cap > kReduceScratchElems) cap = kReduceScratchElems;
+    int grid = (int)(want < cap ? want : cap);
+    int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && (MODE == 0 || (reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    ProfScope prof(kProfReduce, s, 4.0 * (double)n * (MODE == 1 ? 2 : 1), 2);
+    sum_stage1<MODE><<<grid, kThreads, 0, s>>>(x, y, scratch, n, vec_ok);
+    sum_stage2<<<1, kThreads, 0, s>>>(scratch, grid, out, mean ? (float)n : 0.0f);
+    return cuda_ok(cudaGetLastError(), "sum launch");
+}
+
+// ---------------------------------------------------------------- column sums
+// CTA = 32 column lanes x 8 row lanes; a column lane owns 4 adjacent columns (one float4).
+constexpr int kColLanes = 32, kRowLanes = 8, kTileCols = kColLanes * 4;
+
+struct ColsumPlan { int col_tiles; int splits; size_t rows_per_split; bool vec; };
+
+ColsumPlan plan_colsum(size_t rows, size_t cols, int sm_count, bool aligned) {
+    ColsumPlan p;
+    p.vec = aligned && (cols % 4 == 0);
+    size_t tile = p.vec ? kTileCols : kColLanes;
+    p.col_tiles = (int)((cols + tile - 1) / tile);
+    size_t target = (size_t)sm_count * 4;
+    size_t s = (target + p.col_tiles - 1) / p.col_tiles;
+    size_t max_s = (rows + 63) / 64;            // at least 64 rows per split
+    if (s > max_s) s = max_s;
+    if (s < 1) s = 1;
+    if (s > 1024) s = 1024;
+    p.rows_per_split = (rows + s - 1) / s;
+    p.splits = (int)((rows + p.rows_per_split - 1) / p.rows_per_split);
+    return p;
+}
+
+// FUSED: gi = ref > 0 ? go : 0 is written and its column sums accumulated; otherwise plain sums of g.
+template <bool FUSED, bool VEC>
+__global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restrict__ g, const float* __restrict__ ref,
+                                                          float* __restrict__ gi, float* __restrict__ partial, size_t rows,
+                                                          size_t cols, size_t rows_per_split) {
+    const int cl = threadIdx.x % kColLanes, rl = threadIdx.x / kColLanes;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_split;
+    size_t r1 = r0 + rows_per_split;
+    if (r1 > rows) r1 = rows;
+    __shared__ float4 sm[kRowLanes][kColLanes];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (VEC) {
+        const size_t col = ((size_t)blockIdx.x * kColLanes + cl) * 4;
+        if (col < cols) {
+            for (size_t r = r0 + rl; r < r1; r += kRowLanes) {
+                size_t off = (r * cols + col) / 4;
+                float4 v = __ldcs(reinterpret_cast<const float4*>(g) + off);
+                if (FUSED) {
+                    float4 x = __ldcs(reinterpret_cast<const float4*>(ref) + off);
+                    v.x = x.x > 0.0f ? v.x : 0.0f; v.y = x.y > 0.0f ? v.y : 0.0f;
+                    v.z = x.z > 0.0f ? v.z : 0.0f; v.w = x.w > 0.0f ? v.w : 0.0f;
+                    __stcs(reinterpret_cast<float4*>(gi) + off, v);
+                }
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+    } else {
+        const size_t col = (size_t)blockIdx.x * kColLanes + cl;
+        if (col < cols) {
+            for (size_t r = r0 + rl; r < r1; r += kRowLanes) {
+                size_t off = r * cols + col;
+                float v = g[off];
+                if (FUSED) { v = ref[off] > 0.0f ? v : 0.0f; gi[off] = v; }
+                acc.x += v;
+            }
+        }
+    }
+    sm[rl][cl] = acc;
+    __syncthreads();
+    if (rl == 0) {
+        float4 t = sm[0][cl];
+#pragma unroll
+        for (int i = 1; i < kRowLanes; ++i) { float4 u = sm[i][cl]; t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
+        float* dst = partial + (size_t)blockIdx.y * cols;
+        if (VEC) {
+            const size_t col = ((size_t)blockIdx.x * kColLanes + cl) * 4;
+            if (col < cols) { dst[col] = t.x; dst[col + 1] = t.y; dst[col + 2] = t.z; dst[col + 3] = t.w; }
+        } else {
+            const size_t col = (size_t)blockIdx.x * kColLanes + cl;
+            if (col < cols) dst[col] = t.x;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) colsum_stage2(const float* __restrict__ partial, float* __restrict__ out, size_t cols,
+                                                          int splits) {
+    size_t col = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    if (col >= cols) return;
+    float v = 0.0f;
+    for (int s = 0; s < splits; ++s) v += partial[(size_t)s * cols + col];
+    out[col] = v;
+}
+
+template <bool FUSED>
+bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
+    if (cols == 0) return true;
+    if (!out) { set_error("colsum: null output"); return false; }
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    if (rows == 0) return fill(out, 0.0f, cols, s);
+    if (!g || (FUSED && (!ref || !gi))) { set_error("colsum: null pointer"); return false; }
+    bool aligned = (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
+                   (!FUSED || ((reinterpret_cast<uintptr_t>(ref) & 15) == 0 && (reinterpret_cast<uintptr_t>(gi) & 15) == 0));
+    ColsumPlan p = plan_colsum(rows, cols, c->sm_count, aligned);
+    if (p.splits > 1 && !scratch) { set_error("colsum: scratch buffer required"); return false; }
+    float* partial = p.splits > 1 ? scratch : out;
+    dim3 grid(p.col_tiles, p.splits);
+    ProfScope prof(kProfReduce, s, 4.0 * (double)rows * (double)cols * (FUSED ? 3 : 1), p.splits > 1 ? 2 : 1);
+    if (p.vec) colsum_stage1<FUSED, true><<<grid, kThreads, 0, s>>>(g, ref, gi, partial, rows, cols, p.rows_per_split);
+    else colsum_stage1<FUSED, false><<<grid, kThreads, 0, s>>>(g, ref, gi, partial, rows, cols, p.rows_per_split);
+    if (p.splits > 1) colsum_stage2<<<(unsigned)((cols + kThreads - 1) / kThreads), kThreads, 0, s>>>(partial, out, cols, p.splits);
+    return cuda_ok(cudaGetLastError(), "colsum launch");
+}
+
+}  // namespace
+
+bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaStream_t s) {
+    return sum_impl<0>(x, nullptr, out, n, mean, scratch, s);
+}
+bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s) {
+    return sum_impl<1>(y, t, out, n, true, scratch, s);
+}
+
+size_t colsum_scratch_elems(size_t rows, size_t cols) {
+    // Upper bound over every plan: at most 1024 row splits, and never more than rows/64 + 1.
+    size_t s = (rows + 63) / 64;
+    if (s > 1024) s = 1024;
+    if (s < 1) s = 1;
+    return s * cols;
+}
+bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
+    return colsum_impl<false>(g, nullptr, nullptr, out, rows, cols, scratch, s);
+}
+bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols, float* scratch,
+                     cudaStream_t s) {
+    return colsum_impl<true>(go, ref, gi, bias_grad, rows, cols, scratch, s);
+}
+
+}  // namespace k
+}  // namespace ts
+
+// ====================================================================== C ABI
+using namespace ts;
+
+TS_API unsigned long long ts_reduce_scratch_elems(void) { return k::kReduceScratchElems; }
+TS_API bool launch_sum_kernel(const float* x, float* out, unsigned long long n, int mean, float* scratch, void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    if (!s) return false;
+    return k::sum(x, out, n, mean != 0, scratch, s);
+}
+TS_API unsigned long long ts_colsum_scratch_elems(unsigned long long rows, unsigned long long cols) {
+    return k::colsum_scratch_elems(rows, cols);
+}
+TS_API bool launch_colsum_kernel(const float* g, float* out, unsigned long long rows, unsigned long long cols, float* scratch,
+                                 void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    if (!s) return false;
+    return k::colsum(g, out, rows, cols, scratch, s);
+}
+TS_API bool launch_relu_backward_colsum_kernel(const float* ref, const float* go, float* gi, float* bias_grad,
+                                               unsigned long long rows, unsigned long long cols, float* scratch, void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    if (!s) return false;
+    return k::relu_bwd_colsum(ref, go, gi, bias_grad, rows, cols, scratch, s);
+}

@@ -1,0 +1,170 @@
+// FP32 GEMM on the CUDA cores (FFMA), any shape, any transposition.
+//
+// This is the FP32 precision mode and the path for shapes the tensor-core kernel cannot
+// take.  It reproduces the reference's summation order exactly: every output element is
+// one chain over p = 0..k-1 of acc = fma(A[i,p], B[p,j], acc), which is what the AVX2
+// micro-kernels compute (tensor/ops/matmul/kernels.rs:278-305, :378-385, :474-497; k-blocks
+// are accumulated through C, which is exact).  The reference's n mod 8 trailing columns use
+// a rounded multiply followed by an add instead of an FMA (kernels.rs:312-335); the
+// HAS_TAIL variant does the same for those columns.  With identical inputs the result is
+// therefore bit-identical to the reference's CPU path.
+#include "../../include/train_station_b200.h"
+#include "common.h"
+
+namespace ts {
+namespace k {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 8, kThreads = 256;
+
+template <bool TA, bool TB, bool HAS_TAIL>
+__global__ void __launch_bounds__(kThreads) sgemm_kernel(GemmArgs g) {
+    __shared__ __align__(16) float As[2][BK][BM];
+    __shared__ __align__(16) float Bs[2][BK][BN];
+    const int t = threadIdx.x;
+    const size_t m0 = (size_t)blockIdx.y * BM, n0 = (size_t)blockIdx.x * BN;
+    const size_t M = g.m, N = g.n, K = g.k;
+    const int ty = t / 16, tx = t % 16;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    // which of this thread's 8 columns are reference "tail" columns (mul+add instead of fma)
+    bool tailc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        size_t col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+        tailc[j] = HAS_TAIL && col >= N / 8 * 8;
+    }
+
+    float ra[4], rb[4];
+    auto load_tiles = [&](size_t k0) {
+        if (TA) {  // A stored [K][M]: M contiguous
+            int kr = t / 32, mc = (t % 32) * 4;
+            size_t p = k0 + kr;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                size_t i = m0 + mc + e;
+                ra[e] = (p < K && i < M) ? g.a[p * M + i] : 0.0f;
+            }
+        } else {   // A stored [M][K]: K contiguous
+            int mr = t / 2, kc = (t % 2) * 4;
+            size_t i = m0 + mr;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                size_t p = k0 + kc + e;
+                ra[e] = (p < K && i < M) ? g.a[i * K + p] : 0.0f;
+            }
+        }
+        if (TB) {  // B stored [N][K]: K contiguous
+            int nr = t / 2, kc = (t % 2) * 4;
+            size_t j = n0 + nr;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                size_t p = k0 + kc + e;
+                rb[e] = (p < K && j < N) ? g.b[j * K + p] : 0.0f;
+            }
+        } else {   // B stored [K][N]: N contiguous
+            int kr = t / 32, nc = (t % 32) * 4;
+            size_t p = k0 + kr;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                size_t j = n0 + nc + e;
+                rb[e] = (p < K && j < N) ? g.b[p * N + j] : 0.0f;
+            }
+        }
+    };
+    auto store_tiles = [&](int buf) {
+        if (TA) {
+            int kr = t / 32, mc = (t % 32) * 4;
+            *reinterpret_cast<float4*>(&As[buf][kr][mc]) = make_float4(ra[0], ra[1], ra[2], ra[3]);
+        } else {
+            int mr = t / 2, kc = (t % 2) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) As[buf][kc + e][mr] = ra[e];
+        }
+        if (TB) {
+            int nr = t / 2, kc = (t % 2) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) Bs[buf][kc + e][nr] = rb[e];
+        } else {
+            int kr = t / 32, nc = (t % 32) * 4;
+            *reinterpret_cast<float4*>(&Bs[buf][kr][nc]) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+        }
+    };
+
+    const size_t ktiles = (K + BK - 1) / BK;
+    if (ktiles > 0) {
+        load_tiles(0);
+        store_tiles(0);
+    }
+    __syncthreads();
+    for (size_t kt = 0; kt < ktiles; ++kt) {
+        int buf = (int)(kt & 1);
+        if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+#pragma unroll
+        for (int p = 0; p < BK; ++p) {
+            float4 a0 = *reinterpret_cast<const float4*>(&As[buf][p][ty * 4]);
+            float4 a1 = *reinterpret_cast<const float4*>(&As[buf][p][64 + ty * 4]);
+            float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][p][tx * 4]);
+            float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][p][64 + tx * 4]);
+            float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (HAS_TAIL && tailc[j]) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+                    else acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                }
+        }
+        if (kt + 1 < ktiles) store_tiles(buf ^ 1);
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        size_t row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (row >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            size_t col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+            if (col >= N) continue;
+            float v = acc[i][j];
+            if (g.bias) v = __fadd_rn(v, __ldg(g.bias + col));
+            if (g.relu) v = v > 0.0f ? v : 0.0f;
+            if (g.mask) v = g.mask[row * N + col] > 0.0f ? v : 0.0f;
+            g.c[row * N + col] = v;
+        }
+    }
+}
+
+template <bool TA, bool TB>
+void launch(const GemmArgs& g, dim3 grid, cudaStream_t s) {
+    if (g.n % 8 != 0) sgemm_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
+    else sgemm_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+}
+
+}  // namespace
+
+bool sgemm(const GemmArgs& g, cudaStream_t s) {
+    if (g.m == 0 || g.n == 0) return true;
+    if (!g.a || !g.b || !g.c) {
+        if (g.k == 0 && g.c) { /* fallthrough: zero-filled result */ }
+        else { set_error("gemm: null pointer"); return false; }
+    }
+    size_t gx = (g.n + BN - 1) / BN, gy = (g.m + BM - 1) / BM;
+    if (gy > 65535) { set_error("gemm: m = %zu too large for the FP32 kernel's grid", g.m); return false; }
+    dim3 grid((unsigned)gx, (unsigned)gy);
+    ProfScope prof(kProfGemmFp32, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
+    if (g.trans_a) { if (g.trans_b) launch<true, true>(g, grid, s); else launch<true, false>(g, grid, s); }
+    else { if (g.trans_b) launch<false, true>(g, grid, s); else launch<false, false>(g, grid, s); }
+    return cuda_ok(cudaGetLastError(), "sgemm launch");
+}
+
+}  // namespace k
+}  // namespace ts

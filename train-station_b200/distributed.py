@@ -1,0 +1,67 @@
+"""Data parallelism over the batch: every rank holds all parameters, runs forward and
+backward on its contiguous block of batch rows, and the parameter gradients are summed
+with one NCCL all-reduce per tensor (overlapped with the rest of backward) before Adam
+divides by the world size.  The reference has no multi-device code; this module is the
+host side of section 5 of the C ABI.
+
+Rendezvous (who is rank 0, how the NCCL id reaches the others) is the caller's business:
+``init_from_torch_distributed`` uses an existing torch.distributed process group of any
+backend for that and nothing else."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence, Tuple
+
+from . import _ffi
+from ._ffi import check, vp
+from .tensor import Tensor
+
+UNIQUE_ID_BYTES = 128
+
+
+def get_unique_id() -> bytes:
+    buf = C.create_string_buffer(UNIQUE_ID_BYTES)
+    check(_ffi.lib().ts_dp_get_unique_id(buf), "ts_dp_get_unique_id")
+    return buf.raw
+
+
+def init(unique_id: bytes, rank: int, world_size: int) -> None:
+    assert len(unique_id) == UNIQUE_ID_BYTES
+    check(_ffi.lib().ts_dp_init(C.create_string_buffer(unique_id, UNIQUE_ID_BYTES), int(rank), int(world_size)),
+          "ts_dp_init")
+
+
+def init_from_torch_distributed() -> Tuple[int, int]:
+    """Bootstraps the library's NCCL communicator through torch.distributed (id broadcast)."""
+    import torch
+    import torch.distributed as dist
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ids = [get_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    init(ids[0], rank, world)
+    return rank, world
+
+
+def finalize() -> None:
+    _ffi.lib().ts_dp_finalize()
+
+
+def world_size() -> int:
+    return int(_ffi.lib().ts_dp_world_size())
+
+
+def rank() -> int:
+    return int(_ffi.lib().ts_dp_rank())
+
+
+def register_parameters(params: Sequence[Tensor]) -> None:
+    arr = (vp * max(len(params), 1))(*[p._h for p in params])
+    check(_ffi.lib().ts_dp_register_parameters(arr, len(params)), "ts_dp_register_parameters")
+
+
+def shard_rows(n_rows: int, rank_: int, world: int) -> Tuple[int, int]:
+    """Contiguous block [start, stop) of batch rows for a rank; the first n_rows % world
+    ranks get one extra row."""
+    base, extra = divmod(int(n_rows), int(world))
+    start = rank_ * base + min(rank_, extra)
+    return start, start + base + (1 if rank_ < extra else 0)

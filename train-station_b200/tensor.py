@@ -1,0 +1,219 @@
+"""Host-side mirror of the reference's ``Tensor`` API for the training-step hot path.
+
+Method names, argument meaning and error behaviour follow the Rust API
+(src/tensor/core/utils.rs, src/tensor/ops/*.rs, src/tensor/reductions/*.rs) so that tests
+read like the reference's own: ``x.matmul(w).add_tensor(b).relu().sum().backward(None)``.
+All data lives on the GPU; every method forwards to the C ABI.  Where the reference
+panics (shape mismatch), these raise ``TrainStationError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _ffi
+from ._ffi import TrainStationError, check, u64, vp
+
+
+def _dims(shape: Sequence[int]):
+    shape = [int(s) for s in shape]
+    return (u64 * max(len(shape), 1))(*shape), len(shape)
+
+
+class Shape:
+    """Subset of the reference's ``Shape`` (src/tensor/core/shape.rs:96-143): ``dims`` and ``size``."""
+
+    def __init__(self, dims):
+        self.dims = list(dims)
+        self.size = int(np.prod(dims)) if len(dims) else 1
+
+    def rank(self) -> int:
+        return len(self.dims)
+
+    def __eq__(self, other):
+        return isinstance(other, Shape) and self.dims == other.dims
+
+    def __repr__(self):
+        return f"Shape(dims={self.dims})"
+
+
+class Tensor:
+    __slots__ = ("_h", "_keep")
+
+    def __init__(self, handle, keep=None):
+        if not handle:
+            raise TrainStationError(_ffi.last_error())
+        self._h = vp(handle)
+        self._keep = keep  # host buffers that must outlive an asynchronous upload
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _ffi.lib().ts_tensor_free(h)
+            except Exception:
+                pass
+
+    # ------------------------------------------------------------------ constructors
+    @staticmethod
+    def new(shape_dims: Sequence[int]) -> "Tensor":
+        """Uninitialised tensor (core/utils.rs:121-171)."""
+        d, r = _dims(shape_dims)
+        return Tensor(_ffi.lib().ts_tensor_new(d, r))
+
+    @staticmethod
+    def zeros(shape_dims: Sequence[int]) -> "Tensor":
+        d, r = _dims(shape_dims)
+        return Tensor(_ffi.lib().ts_tensor_zeros(d, r))
+
+    @staticmethod
+    def ones(shape_dims: Sequence[int]) -> "Tensor":
+        d, r = _dims(shape_dims)
+        return Tensor(_ffi.lib().ts_tensor_ones(d, r))
+
+    @staticmethod
+    def from_slice(data, shape_dims: Sequence[int]) -> "Tensor":
+        """init/data.rs:227-247: errors when the data length does not match the shape."""
+        a = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        n = int(np.prod([int(s) for s in shape_dims])) if len(shape_dims) else 1
+        if a.size != n:
+            raise TrainStationError(f"from_slice: data has {a.size} elements, shape {list(shape_dims)} needs {n}")
+        d, r = _dims(shape_dims)
+        return Tensor(_ffi.lib().ts_tensor_from_slice(a.ctypes.data_as(vp), d, r))
+
+    @staticmethod
+    def from_pinned_async(pinned: "PinnedBuffer", shape_dims: Sequence[int]) -> "Tensor":
+        """Upload from page-locked memory on the copy stream; overlaps kernels already queued."""
+        d, r = _dims(shape_dims)
+        n = int(np.prod([int(s) for s in shape_dims]))
+        if n > pinned.size:
+            raise TrainStationError("from_pinned_async: shape larger than the pinned buffer")
+        return Tensor(_ffi.lib().ts_tensor_from_pinned_async(pinned.ptr, d, r), keep=pinned)
+
+    # ------------------------------------------------------------------ properties
+    def id(self) -> int:
+        return int(_ffi.lib().ts_tensor_id(self._h))
+
+    def size(self) -> int:
+        return int(_ffi.lib().ts_tensor_size(self._h))
+
+    def shape(self) -> Shape:
+        r = _ffi.lib().ts_tensor_rank(self._h)
+        buf = (u64 * max(r, 1))()
+        check(_ffi.lib().ts_tensor_dims(self._h, buf), "shape")
+        return Shape([int(buf[i]) for i in range(r)])
+
+    def requires_grad(self) -> bool:
+        return bool(_ffi.lib().ts_tensor_requires_grad(self._h))
+
+    def with_requires_grad(self) -> "Tensor":
+        check(_ffi.lib().ts_tensor_set_requires_grad(self._h, True), "with_requires_grad")
+        return self
+
+    def set_requires_grad(self, flag: bool) -> None:
+        check(_ffi.lib().ts_tensor_set_requires_grad(self._h, bool(flag)), "set_requires_grad")
+
+    def data_ptr(self) -> int:
+        p = _ffi.lib().ts_tensor_data_ptr(self._h)
+        check(p, "data_ptr")
+        return int(p)
+
+    def data(self) -> np.ndarray:
+        """Tensor::data(): a host copy, shaped like the tensor."""
+        sh = self.shape().dims
+        out = np.empty(self.size(), np.float32)
+        check(_ffi.lib().ts_tensor_to_host(self._h, out.ctypes.data_as(vp)), "data")
+        return out.reshape(sh)
+
+    def value(self) -> float:
+        """Tensor::value(): the single element of a one-element tensor."""
+        if self.size() != 1:
+            raise TrainStationError("value() can only be called on tensors with exactly one element")
+        return float(self.data().reshape(-1)[0])
+
+    def get(self, idx: Sequence[int]) -> float:
+        return float(self.data()[tuple(idx)])
+
+    def copy_from_host(self, data) -> None:
+        a = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        if a.size != self.size():
+            raise TrainStationError("copy_from_host: size mismatch")
+        check(_ffi.lib().ts_tensor_copy_from_host(self._h, a.ctypes.data_as(vp)), "copy_from_host")
+
+    def fill(self, value: float) -> None:
+        check(_ffi.lib().ts_tensor_fill(self._h, float(value)), "fill")
+
+    # ------------------------------------------------------------------ ops
+    def _bin(self, other: "Tensor", fn) -> "Tensor":
+        if not isinstance(other, Tensor):
+            raise TypeError("operand must be a Tensor")
+        return Tensor(fn(self._h, other._h))
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        return self._bin(other, _ffi.lib().ts_tensor_matmul)
+
+    def add_tensor(self, other: "Tensor") -> "Tensor":
+        return self._bin(other, _ffi.lib().ts_tensor_add_tensor)
+
+    def sub_tensor(self, other: "Tensor") -> "Tensor":
+        return self._bin(other, _ffi.lib().ts_tensor_sub_tensor)
+
+    def mul_tensor(self, other: "Tensor") -> "Tensor":
+        return self._bin(other, _ffi.lib().ts_tensor_mul_tensor)
+
+    def div_tensor(self, other: "Tensor") -> "Tensor":
+        return self._bin(other, _ffi.lib().ts_tensor_div_tensor)
+
+    def relu(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_relu(self._h))
+
+    def pow_scalar(self, exponent: float) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_pow_scalar(self._h, float(exponent)))
+
+    def sum(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_sum(self._h))
+
+    def mean(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_mean(self._h))
+
+    # operator sugar, as tensor/core/operators.rs:120-185 forwards to the *_tensor methods
+    __add__ = add_tensor
+    __sub__ = sub_tensor
+    __mul__ = mul_tensor
+    __truediv__ = div_tensor
+    __matmul__ = matmul
+
+    # ------------------------------------------------------------------ gradtrack
+    def backward(self, grad_output: Optional["Tensor"] = None) -> None:
+        """core/utils.rs:634-636 -> gradtrack/engine.rs:962-1047."""
+        g = grad_output._h if grad_output is not None else None
+        check(_ffi.lib().ts_tensor_backward(self._h, g), "backward")
+
+    def grad_by_value(self) -> Optional["Tensor"]:
+        """core/utils.rs:525-534: the accumulated gradient, or None."""
+        h = _ffi.lib().ts_tensor_grad_by_value(self._h)
+        return Tensor(h) if h else None
+
+    def __repr__(self):
+        return f"Tensor(id={self.id()}, dims={self.shape().dims}, requires_grad={self.requires_grad()})"
+
+
+class PinnedBuffer:
+    """Page-locked host memory viewed as a float32 numpy array (for overlapped uploads)."""
+
+    def __init__(self, n_elements: int):
+        self.size = int(n_elements)
+        p = _ffi.lib().ts_host_alloc_pinned(self.size)
+        check(p, "ts_host_alloc_pinned")
+        self.ptr = vp(p)
+        self.array = np.ctypeslib.as_array(C.cast(self.ptr, C.POINTER(C.c_float)), shape=(self.size,))
+
+    def __del__(self):
+        p, self.ptr = getattr(self, "ptr", None), None
+        if p:
+            try:
+                _ffi.lib().ts_host_free_pinned(p)
+            except Exception:
+                pass
