@@ -222,6 +222,10 @@ static std::vector<size_t> strip_leading_ones(const std::vector<size_t>& d) {
 }
 // `small` broadcasts over the leading dimensions of `big` (e.g. [M,N] + [N], [M,N] + [1,N]).
 static bool is_suffix_broadcast(const std::vector<size_t>& big, const std::vector<size_t>& small, size_t* rows, size_t* cols) {
+    size_t small_n = 1, big_n = 1;
+    for (size_t x : small) small_n *= x;
+    for (size_t x : big) big_n *= x;
+    if (small_n == 1) { *rows = big_n; *cols = 1; return true; }   // a one-element tensor broadcasts over everything
     std::vector<size_t> s = strip_leading_ones(small);
     if (s.size() > big.size()) return false;
     size_t off = big.size() - s.size();

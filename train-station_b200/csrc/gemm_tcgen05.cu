@@ -11,7 +11,7 @@
 //
 // Operand layouts.  C[m,n] = sum_k A(m,k) B(k,n), all matrices row-major in global memory:
 //   A stored [m][k]  -> "K-major":  TMA box 32(k) x 128 rows, 128-byte swizzle
-//   A stored [k][m]  -> "MN-major": TMA boxes 32(m) x 32(k), four per tile, 128-byte swizzle
+//   A stored [k][m]  -> "MN-major": TMA boxes 32(m) x 32(k), four per tile, 128-byte swizzle of 32-byte chunks
 //   B stored [n][k]  -> K-major;   B stored [k][n] -> MN-major (BN/32 boxes per tile)
 // so forward (A K-major, B MN-major), dA = dC.B^T (both K-major) and dB = A^T.dC (both
 // MN-major) all run without materialising a transpose.
@@ -123,15 +123,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2 in bits 61..63), descriptor
-// version 1 in bits 46..47.  Addresses and offsets are stored without their 4 low bits.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor: layout type in bits 61..63, descriptor version 1 in bits 46..47.
+// Addresses and offsets are stored without their 4 low bits.
+// Layout types used here: 2 = 128-byte swizzle of 16-byte chunks (K-major operands);
+// 1 = 128-byte swizzle of 32-byte chunks, the only swizzled layout the tensor core accepts for
+// MN-major 32-bit operands (its atom is four k-rows of 128 bytes).
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)layout_type << 61;
     return d;
 }
 
@@ -279,9 +283,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // K-major: 32 bytes further inside the 128-byte swizzled row, 8-row groups 1024 B apart.
-                        // MN-major: the next group of eight k-rows (1024 B); 32-element column groups 4096 B apart.
-                        const uint64_t da = A_MN ? smem_desc(sa + kk * 1024, 4096, 1024) : smem_desc(sa + kk * 32, 16, 1024);
-                        const uint64_t db = B_MN ? smem_desc(sb + kk * 1024, 4096, 1024) : smem_desc(sb + kk * 32, 16, 1024);
+                        // MN-major: eight k-rows (two 4-row swizzle atoms, 512 B apart) per MMA, so 1024 B per
+                        // step; the 32-element column groups (one TMA box each) are 4096 B apart.
+                        const uint64_t da = A_MN ? smem_desc(sa + kk * 1024, 4096, 512, kLayoutSw128Base32)
+                                                 : smem_desc(sa + kk * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t db = B_MN ? smem_desc(sb + kk * 1024, 4096, 512, kLayoutSw128Base32)
+                                                 : smem_desc(sb + kk * 32, 16, 1024, kLayoutSw128);
                         umma_tf32(d_tmem, da, db, idesc, (kb | (uint32_t)kk) != 0u ? 1u : 0u);
                     }
                     umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
@@ -378,7 +385,7 @@ EncodeTiledFn get_encode() {
 }
 
 // 2-D row-major f32 matrix [rows][cols]; box = box_cols (inner) x box_rows.
-bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows) {
+bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows, bool mn_major) {
     EncodeTiledFn enc = get_encode();
     if (!enc) { set_error("gemm: cuTensorMapEncodeTiled is not available from the driver"); return false; }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -386,7 +393,8 @@ bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint3
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("gemm: cuTensorMapEncodeTiled failed with code %d (rows %zu cols %zu box %u x %u)", (int)r, rows, cols, box_cols, box_rows); return false; }
     return true;
 }
@@ -396,11 +404,11 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     using Cf = Cfg<BN>;
     CUtensorMap tm_a, tm_b;
     // A: stored [k][m] when transposed (MN-major) else [m][k]
-    if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32)) return false; }
-    else { if (!make_map(&tm_a, g.a, g.m, g.k, BK, BM)) return false; }
+    if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32, true)) return false; }
+    else { if (!make_map(&tm_a, g.a, g.m, g.k, BK, BM, false)) return false; }
     // B: stored [k][n] when not transposed (MN-major) else [n][k]
-    if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32)) return false; }
-    else { if (!make_map(&tm_b, g.b, g.n, g.k, BK, BN)) return false; }
+    if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32, true)) return false; }
+    else { if (!make_map(&tm_b, g.b, g.n, g.k, BK, BN, false)) return false; }
     auto kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
     static bool attr_set[64] = {false};   // the attribute is per device
     if (!attr_set[c->device]) {
