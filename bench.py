@@ -343,8 +343,96 @@ def run_gpu(args, d: Dist):
         ts.distributed.finalize()
 
 
+# ------------------------------------------------------------------------ single-kernel cases
+MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "adam", "add", "mul_backward", "relu_backward_colsum",
+               "colsum", "sum")
+
+
+def run_micro(args):
+    """One kernel on a case that is larger than L2 but holds about a gigabyte on the device: the
+    case the ncu captures under profiles/ are taken on, and a quick per-kernel roofline check."""
+    ts = entry.load_package()
+    lib, chk = ts._ffi.lib(), ts._ffi.check
+    ts.set_default_device(0)
+    rng = np.random.default_rng(0)
+    peaks = measured_peaks()
+    vp = C.c_void_p
+
+    def dev(a):
+        a = np.ascontiguousarray(a, np.float32)
+        p = lib.cuda_malloc(a.size)
+        chk(p, "cuda_malloc")
+        chk(lib.cuda_memcpy(p, a.ctypes.data, a.size, 0), "upload")
+        return p
+
+    def empty(n):
+        p = lib.cuda_malloc(n)
+        chk(p, "cuda_malloc")
+        return p
+
+    name, n = args.micro, args.micro_size
+    if name.startswith("gemm"):
+        m = nn = k = n or 8192
+        a, b, c = dev(rng.standard_normal((m, k), dtype=np.float32)), dev(rng.standard_normal((k, nn), dtype=np.float32)), empty(m * nn)
+        ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0)}[name]
+        prec = 0 if name.endswith("fp32") else 1
+        launch = lambda: chk(lib.launch_gemm_kernel(a, b, c, m, nn, k, ta, tb, None, 0, None, prec, None), name)
+        work, unit, peak = 2.0 * m * nn * k, "TFLOP/s", (peaks["bf16_burst"] / 2.0 if prec else None)
+    elif name == "adam":
+        n = n or (1 << 26)
+        bufs = [dev(rng.standard_normal(n, dtype=np.float32)) for _ in range(2)] + [dev(np.zeros(n, np.float32)) for _ in range(2)]
+        tab = lambda p: (vp * 1)(p)
+        sizes = (C.c_ulonglong * 1)(n)
+        launch = lambda: chk(lib.launch_adam_multi_tensor_kernel(tab(bufs[0]), tab(bufs[1]), tab(bufs[2]), tab(bufs[3]), sizes, 1,
+                                                                 1e-3, 0.9, 0.999, 1e-8, 0.0, 10.0, 1000.0, 1.0, None), name)
+        work, unit, peak = 28.0 * n, "GB/s", peaks["hbm_gbs"]
+    elif name in ("add", "mul_backward"):
+        n = n or (1 << 26)
+        x, y, g = (dev(rng.standard_normal(n, dtype=np.float32)) for _ in range(3))
+        o1, o2 = empty(n), empty(n)
+        if name == "add":
+            launch = lambda: chk(lib.launch_add_kernel(x, y, o1, n, None), name)
+            work = 12.0 * n
+        else:
+            launch = lambda: chk(lib.launch_mul_backward_kernel(x, y, g, o1, o2, n, None), name)
+            work = 20.0 * n
+        unit, peak = "GB/s", peaks["hbm_gbs"]
+    elif name in ("colsum", "relu_backward_colsum"):
+        rows, cols = (n or 16384), 8192
+        g, ref = dev(rng.standard_normal((rows, cols), dtype=np.float32)), dev(rng.standard_normal((rows, cols), dtype=np.float32))
+        out, gi, sc = empty(cols), empty(rows * cols), empty(int(lib.ts_colsum_scratch_elems(rows, cols)))
+        if name == "colsum":
+            launch = lambda: chk(lib.launch_colsum_kernel(g, out, rows, cols, sc, None), name)
+            work = 4.0 * rows * cols
+        else:
+            launch = lambda: chk(lib.launch_relu_backward_colsum_kernel(ref, g, gi, out, rows, cols, sc, None), name)
+            work = 12.0 * rows * cols
+        unit, peak = "GB/s", peaks["hbm_gbs"]
+    else:
+        n = n or (1 << 27)
+        x, out, sc = dev(rng.standard_normal(n, dtype=np.float32)), empty(1), empty(int(lib.ts_reduce_scratch_elems()))
+        launch = lambda: chk(lib.launch_sum_kernel(x, out, n, 0, sc, None), name)
+        work, unit, peak = 4.0 * n, "GB/s", peaks["hbm_gbs"]
+
+    for _ in range(args.warmup):
+        launch()
+    ts.synchronize()
+    ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
+    lib.ts_event_record(ev0, None)
+    for _ in range(args.steps):
+        launch()
+    lib.ts_event_record(ev1, None)
+    ts.synchronize()
+    ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"micro": name, "size": n, "launches": args.steps, "ms_per_launch": ms, "achieved": rate, "unit": unit,
+                      "peak": peak, "frac": rate / peak if peak else None, "peak_source": peaks["source"]}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=MICRO_CASES, help="time one kernel on a small standalone case")
+    ap.add_argument("--micro-size", type=int, default=0)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -352,6 +440,9 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.micro:
+        run_micro(args)
+        return
     d = Dist(args.gpus)
     try:
         if args.impl == "reference":

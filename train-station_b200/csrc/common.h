@@ -128,7 +128,10 @@ struct GemmArgs {
     const float* bias;   // [n] or null
     bool relu;
     const float* mask;   // [m,n] or null
+    bool round_tf32 = false;   // tensor-core path only: store the result rounded to nearest TF32
 };
+// out = x rounded to the nearest TF32 value (10 explicit mantissa bits, ties away from zero).
+bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s);
 bool sgemm(const GemmArgs& g, cudaStream_t s);                       // FFMA, reference summation order
 bool gemm_tc_supported(const GemmArgs& g);
 bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s);  // tcgen05 TF32 / 3xTF32

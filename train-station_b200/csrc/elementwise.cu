@@ -148,6 +148,14 @@ struct AddScalarBcastF {
     const float* scalar;
     __device__ void apply(const float* x, float* o) const { o[0] = __fadd_rn(x[0], __ldg(scalar)); }
 };
+// round to the nearest TF32 value, ties away from zero; the low 13 mantissa bits of the result are zero
+struct RoundTf32F {
+    __device__ void apply(const float* x, float* o) const {
+        uint32_t r;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x[0]));
+        o[0] = __uint_as_float(r);
+    }
+};
 // inputs y, t: ((inv_n * upstream) * (2 * (y - t))): ReduceMean -> PowScalar(2) -> Sub chain
 // (grad_fn/reductions/mean.rs:10-19, grad_fn/ops/pow.rs:5-27, grad_fn/ops/sub.rs:26-31).
 struct MseGradF {
@@ -224,6 +232,7 @@ bool add_scalar_bcast(const float* a, const float* scalar_dev, float* o, size_t 
     if (!scalar_dev) { set_error("add_scalar_bcast: null scalar"); return false; }
     return launch_ew(Ptrs<1, 1>{{a}, {o}}, n, AddScalarBcastF{scalar_dev}, s);
 }
+bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, RoundTf32F{}, s); }
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {
     if (!upstream) { set_error("mse_grad: null upstream"); return false; }
     return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n}, s);

@@ -36,8 +36,15 @@ struct Storage {
     DeviceCtx* c = nullptr;
     uint64_t version = 0;
     cudaEvent_t ready = nullptr;   // set while an upload on the copy stream is outstanding
+    // TF32 mode: the tensor core drops the low 13 mantissa bits of an FP32 operand (truncation, a
+    // bias toward zero).  Operands are therefore rounded to nearest first: either the producing
+    // GEMM stored them already rounded (tf32_clean), or a rounded copy is kept beside the data.
+    bool tf32_clean = false;
+    float* tf32_copy = nullptr;
+    uint64_t tf32_copy_version = 0;
     ~Storage() {
         if (ready) cudaEventDestroy(ready);
+        if (c && tf32_copy) c->alloc.free(tf32_copy);
         if (c && ptr) c->alloc.free(ptr);
     }
 };
@@ -90,11 +97,13 @@ static TensorP new_tensor(DeviceCtx* c, const std::vector<size_t>& dims) {
     return t;
 }
 
-static bool materialize(const TensorP& t);
+// for_gemm: the caller is a tensor-core GEMM (or knows the result feeds one), so in TF32 mode
+// the deferred GEMM may store its result already rounded to TF32.
+static bool materialize(const TensorP& t, bool for_gemm = false);
 
 // Device pointer for reading on the compute stream (launches a deferred GEMM, waits for an upload).
-static const float* rptr(const TensorP& t) {
-    if (!materialize(t)) return nullptr;
+static const float* rptr(const TensorP& t, bool for_gemm = false) {
+    if (!materialize(t, for_gemm)) return nullptr;
     Storage* s = t->st.get();
     if (s->ready) {
         cudaStreamWaitEvent(s->c->compute, s->ready, 0);
@@ -104,19 +113,42 @@ static const float* rptr(const TensorP& t) {
     return s->ptr;
 }
 
-static bool materialize(const TensorP& t) {
+// The operand as the TF32 tensor core should see it: the data itself when it is already exactly
+// representable in TF32, otherwise a rounded-to-nearest copy cached beside it (refreshed when the
+// data's version changes; the forward and the two backward GEMMs of a layer share it).
+static const float* tf32_operand(DeviceCtx* c, const TensorP& t) {
+    Storage* s = t->st.get();
+    if (s->tf32_clean) return s->ptr;
+    if (s->tf32_copy && s->tf32_copy_version == s->version) return s->tf32_copy;
+    if (!s->tf32_copy) {
+        s->tf32_copy = c->alloc.alloc((s->n ? s->n : 1) * sizeof(float));
+        if (!s->tf32_copy) return nullptr;
+    }
+    if (!k::round_to_tf32(s->ptr, s->tf32_copy, s->n, c->compute)) return nullptr;
+    s->tf32_copy_version = s->version;
+    return s->tf32_copy;
+}
+
+static bool materialize(const TensorP& t, bool for_gemm) {
     if (!t->pending) return t->st != nullptr;
     DeviceCtx* c = ctx();
     if (!c) return false;
     PendingGemm& p = *t->pending;
-    const float* a = rptr(p.a);
-    const float* b = rptr(p.b);
+    const float* a = rptr(p.a, true);
+    const float* b = rptr(p.b, true);
     const float* bias = p.bias ? rptr(p.bias) : nullptr;
     const float* mask = p.mask ? rptr(p.mask) : nullptr;
     if (!a || !b || (p.bias && !bias) || (p.mask && !mask)) return false;
     StorageP st = new_storage(c, t->size);
     if (!st) return false;
     k::GemmArgs g{a, b, st->ptr, p.m, p.n, p.k, p.ta, p.tb, bias, p.relu, mask};
+    if (matmul_precision() == 1 && k::gemm_tc_supported(g)) {
+        g.a = tf32_operand(c, p.a);
+        g.b = tf32_operand(c, p.b);
+        if (!g.a || !g.b) return false;
+        g.round_tf32 = for_gemm;
+        st->tf32_clean = for_gemm;
+    }
     if (!k::gemm(g, -1, c, c->compute)) return false;
     t->st = st;
     t->pending.reset();   // releases the operand references
@@ -291,7 +323,11 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
                     g_graph.bias_grad_ready.erase(pre);
                     continue;
                 }
-                const float* gp = rptr(go);
+                // When the other operand came out of a matmul, this gradient goes on into that matmul's
+                // two backward GEMMs: let a deferred GEMM that produces it store TF32-rounded values.
+                auto other_prod = g_graph.ops.find(nd.inputs[1 - i]);
+                const bool feeds_gemm = other_prod != g_graph.ops.end() && other_prod->second.op == Op::MatMul;
+                const float* gp = rptr(go, feeds_gemm);
                 if (!gp) return false;
                 TensorP r = new_tensor(c, od);
                 if (!r) return false;
@@ -622,6 +658,7 @@ TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
     TS_CHECK(cudaMemcpyAsync(st->ptr, host, t->t->size * sizeof(float), cudaMemcpyHostToDevice, st->c->compute));
     TS_CHECK(cudaStreamSynchronize(st->c->compute));
     st->version++;
+    st->tf32_clean = false;
     return true;
 }
 TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
@@ -630,6 +667,7 @@ TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
     Storage* st = t->t->st.get();
     if (!k::fill(st->ptr, v, t->t->size, st->c->compute)) return false;
     st->version++;
+    st->tf32_clean = false;
     return true;
 }
 
@@ -916,7 +954,7 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         if (!k::adam_launch((const k::AdamTensor*)o->tensors_dev, o->chunks_dev, o->n_chunks, total, o->lr, o->beta1, o->beta2, o->eps,
                             o->wd, f1, f2, grad_scale, c->compute))
             return false;
-        for (auto& s : touched) s->version++;
+        for (auto& s : touched) { s->version++; s->tf32_clean = false; }
     }
     if (!skipped.empty()) {
         set_error("adam step: parameter(s) %s have no gradient and were skipped", skipped.c_str());

@@ -84,6 +84,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -163,9 +170,17 @@ struct KernelArgs {
     const float* bias;
     const float* mask;
     int relu;
+    int round_out;
+    int a_grouped, b_grouped;   // MN-major operand described by a 3-D [group][k][32] tensor map
     uint32_t m, n, k;
     int* error_flag;
 };
+
+__device__ __forceinline__ float rn_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -233,15 +248,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
                     const int k0 = (int)(kb * BK);
                     mbar_expect_tx(full_bar(stage), C::kStageBytes);
+                    // An MN-major tile is BM/32 (BN/32) boxes of 32 columns x 32 k-rows.  When the row length is a
+                    // multiple of 32 the matrix is also described as [column group][k][32] and one 3-D copy brings
+                    // all boxes of the tile; otherwise one 2-D copy per box.
                     if (A_MN) {
+                        if (args.a_grouped) {
+                            tma_load_3d(sa, &tm_a, full_bar(stage), 0, k0, m0 / 32);
+                        } else {
 #pragma unroll
-                        for (int b = 0; b < BM / 32; ++b) tma_load_2d(sa + b * 4096, &tm_a, full_bar(stage), m0 + 32 * b, k0);
+                            for (int b = 0; b < BM / 32; ++b) tma_load_2d(sa + b * 4096, &tm_a, full_bar(stage), m0 + 32 * b, k0);
+                        }
                     } else {
                         tma_load_2d(sa, &tm_a, full_bar(stage), k0, m0);
                     }
                     if (B_MN) {
+                        if (args.b_grouped) {
+                            tma_load_3d(sb, &tm_b, full_bar(stage), 0, k0, n0 / 32);
+                        } else {
 #pragma unroll
-                        for (int b = 0; b < BN / 32; ++b) tma_load_2d(sb + b * 4096, &tm_b, full_bar(stage), n0 + 32 * b, k0);
+                            for (int b = 0; b < BN / 32; ++b) tma_load_2d(sb + b * 4096, &tm_b, full_bar(stage), n0 + 32 * b, k0);
+                        }
                     } else {
                         tma_load_2d(sb, &tm_b, full_bar(stage), k0, n0);
                     }
@@ -345,6 +371,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                 const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
                                 v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
                             }
+                            if (args.round_out) { v.x = rn_tf32(v.x); v.y = rn_tf32(v.y); v.z = rn_tf32(v.z); v.w = rn_tf32(v.w); }
                             *reinterpret_cast<float4*>(crow + col) = v;
                         }
                     }
@@ -399,15 +426,37 @@ bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint3
     return true;
 }
 
+// The same [rows][cols] matrix (cols a multiple of 32) seen as [cols/32 groups][rows][32]: dimension 0 is
+// the 32 contiguous elements of a group, dimension 1 the row (pitch cols*4 bytes), dimension 2 the group
+// (pitch 128 bytes).  A box of 32 x box_rows x box_groups lands in shared memory group by group, each
+// group box_rows rows of 128 bytes: the layout of box_groups separate 2-D boxes, in one copy.
+bool make_map_grouped(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint32_t box_rows, uint32_t box_groups) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) { set_error("gemm: cuTensorMapEncodeTiled is not available from the driver"); return false; }
+    cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(cols / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * sizeof(float), 128};
+    cuuint32_t box[3] = {32, box_rows, box_groups};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("gemm: cuTensorMapEncodeTiled (grouped) failed with code %d (rows %zu cols %zu)", (int)r, rows, cols); return false; }
+    return true;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     using Cf = Cfg<BN>;
     CUtensorMap tm_a, tm_b;
+    // the grouped description is an optimisation: if the driver refuses it, the per-box maps still work
+    bool a_grouped = A_MN && g.m % 32 == 0 && make_map_grouped(&tm_a, g.a, g.k, g.m, BK, BM / 32);
+    bool b_grouped = B_MN && g.n % 32 == 0 && make_map_grouped(&tm_b, g.b, g.k, g.n, BK, BN / 32);
     // A: stored [k][m] when transposed (MN-major) else [m][k]
-    if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32, true)) return false; }
+    if (a_grouped) {}
+    else if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32, true)) return false; }
     else { if (!make_map(&tm_a, g.a, g.m, g.k, BK, BM, false)) return false; }
     // B: stored [k][n] when not transposed (MN-major) else [n][k]
-    if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32, true)) return false; }
+    if (b_grouped) {}
+    else if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32, true)) return false; }
     else { if (!make_map(&tm_b, g.b, g.n, g.k, BK, BN, false)) return false; }
     auto kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
     static bool attr_set[64] = {false};   // the attribute is per device
@@ -417,7 +466,7 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     }
     size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN);
     int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
-    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");

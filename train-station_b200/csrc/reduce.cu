@@ -159,7 +159,18 @@ __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restric
     if (VEC) {
         const size_t col = ((size_t)blockIdx.x * kColLanes + cl) * 4;
         if (col < cols) {
-            for (size_t r = r0 + rl; r < r1; r += kRowLanes) {
+            size_t r = r0 + rl;
+            if (!FUSED) {
+                // four rows in flight per thread: the plain column sum has nothing else to hide latency with
+                for (; r + 3 * kRowLanes < r1; r += 4 * kRowLanes) {
+                    float4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(g) + ((r + u * kRowLanes) * cols + col) / 4);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+                }
+            }
+            for (; r < r1; r += kRowLanes) {
                 size_t off = (r * cols + col) / 4;
                 float4 v = __ldcs(reinterpret_cast<const float4*>(g) + off);
                 if (FUSED) {
