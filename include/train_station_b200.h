@@ -167,6 +167,23 @@ bool launch_sum_kernel(const float* x, float* out, unsigned long long size, int 
 unsigned long long ts_colsum_scratch_elems(unsigned long long rows, unsigned long long cols);
 bool launch_colsum_kernel(const float* g, float* out, unsigned long long rows, unsigned long long cols,
                           float* scratch, void* stream);
+/* launch_colsum_kernel for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  A host that lives inside someone else's fixed memory budget, that has already given all
+ * device memory away, or that must not enter the driver's allocator on its hot loop (the allocator can
+ * synchronise the whole device) has no scratch buffer to hand to launch_colsum_kernel; this variant
+ * keeps the partial sums in a 512 KiB array built into the library (held on every GPU that loads the
+ * library, until the process exits) and itself calls no allocation routine of any kind.
+ *   - Limit: the row splits times `cols` must fit 131,072 elements (for example 65536 x 8192 needs
+ *     81,920); larger problems are refused with a message in ts_last_error().
+ *   - The library must already be initialised on the current device (cuda_ffi_initialize() allocates
+ *     and therefore is not done here); otherwise the call fails with a message.
+ *   - The first call on each device looks up the device address of the built-in array; make that
+ *     first call before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the last call left in it.  Each
+ *     call overwrites every element it later reads, so nothing needs clearing, but two calls that
+ *     overlap on the GPU (different streams, no ordering between them) race on it. */
+bool launch_colsum_kernel_static_scratch(const float* g, float* out, unsigned long long rows,
+                                         unsigned long long cols, void* stream);
 /* Fused ReLU backward + bias gradient: grad_in = ref > 0 ? go : 0 and
  * bias_grad[j] = sum_i grad_in[i,j] in one pass over the data. */
 bool launch_relu_backward_colsum_kernel(const float* ref, const float* grad_out, float* grad_in,

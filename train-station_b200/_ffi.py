@@ -79,6 +79,7 @@ SIGNATURES = {
     "launch_sum_kernel": (C.c_bool, [vp, vp, u64, C.c_int, vp, vp]),
     "ts_colsum_scratch_elems": (u64, [u64, u64]),
     "launch_colsum_kernel": (C.c_bool, [vp, vp, u64, u64, vp, vp]),
+    "launch_colsum_kernel_static_scratch": (C.c_bool, [vp, vp, u64, u64, vp]),
     "launch_relu_backward_colsum_kernel": (C.c_bool, [vp, vp, vp, vp, u64, u64, vp, vp]),
     "launch_gemm_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, C.c_int, C.c_int, vp, C.c_int, vp, C.c_int, vp]),
     "launch_adam_multi_tensor_kernel": (C.c_bool, [C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u64p,

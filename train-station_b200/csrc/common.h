@@ -61,6 +61,7 @@ struct DeviceCtx {
 };
 
 DeviceCtx* ctx();                     // context of this thread's current device, or nullptr (error set)
+DeviceCtx* ctx_if_initialized();      // the same, but never creates one (no allocation); nullptr when absent
 int current_device();
 bool set_device(int dev);
 cudaStream_t pick_stream(void* user_stream);  // NULL -> compute stream of the current device

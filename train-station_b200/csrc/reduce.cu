@@ -291,3 +291,60 @@ TS_API bool launch_relu_backward_colsum_kernel(const float* ref, const float* go
     if (!s) return false;
     return k::relu_bwd_colsum(ref, go, gi, bias_grad, rows, cols, scratch, s);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Column sum for callers that must not allocate.
+//
+// Some hosts of this library cannot obtain device memory at the moment they need a bias gradient:
+// a plugin that runs inside another framework's memory budget and may not grow it, a service whose
+// device memory was carved up at start-up and is now fully handed out, or a latency-bound loop in
+// which a call into the driver's allocator (which may synchronise the device) is not acceptable.
+// launch_colsum_kernel asks such callers for a scratch buffer they have no way to provide.
+// The first call on a device performs the symbol look-up below: make it before any stream capture.
+//
+// This variant keeps the scratch (the per-row-split partial sums) in a fixed array that is part of
+// the library image: every GPU that loads the library holds these 512 KiB until the process exits.
+// The array's name below is, in host code, only a handle of the host-side shadow of the symbol, not
+// a device address; the device address is obtained once per device with cudaGetSymbolAddress while
+// that device is current, and that pointer is what the kernels receive.
+constexpr size_t kStaticColsumScratchElems = size_t(1) << 17;   // 131072 floats = 512 KiB
+static __device__ __align__(256) float g_colsum_static_scratch[kStaticColsumScratchElems];
+static float* g_colsum_static_ptr[64] = {nullptr};   // per device, filled at the first call on that device
+static std::mutex g_colsum_static_mu;
+
+TS_API bool launch_colsum_kernel_static_scratch(const float* g, float* out, unsigned long long rows, unsigned long long cols,
+                                                void* stream) {
+    // The library must already be initialised on this device (cuda_ffi_initialize or any earlier call):
+    // creating the per-device context allocates, and this entry point must not.
+    DeviceCtx* c = ctx_if_initialized();
+    if (!c) {
+        set_error("launch_colsum_kernel_static_scratch: the library is not initialised on the current device; call "
+                  "cuda_ffi_initialize() first (this entry point never allocates, so it cannot do that itself)");
+        return false;
+    }
+    cudaStream_t s = stream ? (cudaStream_t)stream : c->compute;
+    if (cols == 0) return true;
+    if (!out || (rows && !g)) { set_error("launch_colsum_kernel_static_scratch: null pointer"); return false; }
+    bool aligned = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+    k::ColsumPlan p = k::plan_colsum((size_t)rows ? (size_t)rows : 1, (size_t)cols, c->sm_count, aligned);
+    size_t need = p.splits > 1 ? (size_t)p.splits * (size_t)cols : 0;
+    if (need > kStaticColsumScratchElems) {
+        set_error("launch_colsum_kernel_static_scratch: a %llu x %llu column sum needs %zu scratch elements, the built-in scratch holds "
+                  "%zu; use launch_colsum_kernel with a caller-provided buffer", rows, cols, need, kStaticColsumScratchElems);
+        return false;
+    }
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_colsum_static_mu);
+        if (!g_colsum_static_ptr[c->device]) {
+            // one-time set-up for this device (which ctx_if_initialized made current): resolve the symbol
+            void* p_dev = nullptr;
+            if (!cuda_ok(cudaGetSymbolAddress(&p_dev, g_colsum_static_scratch), "cudaGetSymbolAddress(static colsum scratch)")) return false;
+            g_colsum_static_ptr[c->device] = (float*)p_dev;
+        }
+        scratch = g_colsum_static_ptr[c->device];
+    }
+    // Every partial the second stage reads is written by the first stage of the same call, so nothing in the
+    // array has to start at zero and stale contents of an earlier call are never read.
+    return k::colsum(g, out, rows, cols, scratch, s);
+}

@@ -173,6 +173,14 @@ DeviceCtx* ctx() {
     return g_ctxs[dev];
 }
 
+DeviceCtx* ctx_if_initialized() {
+    int dev = current_device();
+    if (dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    if (g_ctxs[dev]) cudaSetDevice(dev);
+    return g_ctxs[dev];
+}
+
 cudaStream_t pick_stream(void* user_stream) {
     if (user_stream) return (cudaStream_t)user_stream;
     DeviceCtx* c = ctx();
