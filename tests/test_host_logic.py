@@ -1,0 +1,100 @@
+"""CPU: host-side logic of the data-parallel path, with two gloo ranks standing in for two GPUs.
+
+What is checked is the arithmetic contract the device path implements (distributed.py, ts_dp_* in
+engine.cu): contiguous row shards, per-rank mean loss, SUM all-reduce of the parameter gradients,
+Adam reading gradients scaled by 1/world, identical parameters on every rank afterwards and equal
+(to rounding) to the single-process step on the whole batch.  The per-rank math here is done by the
+CPU oracle; the GPU tests cover the kernels themselves.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_shard_rows_partitions_the_batch(ts):
+    sr = ts.distributed.shard_rows
+    for n, w in [(65536, 1), (65536, 8), (10, 4), (7, 8), (0, 2)]:
+        blocks = [sr(n, r, w) for r in range(w)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == n
+        assert all(blocks[i][1] == blocks[i + 1][0] for i in range(w - 1))
+        sizes = [b - a for a, b in blocks]
+        assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+    assert sr(65536, 3, 8) == (24576, 32768)
+
+
+def test_unique_id_buffer_size(ts):
+    assert ts.distributed.UNIQUE_ID_BYTES == 128
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    ora = entry.load_oracle()
+    ts = entry.load_package()
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    # the rendezvous pattern bench.py uses for the NCCL id: rank 0 makes 128 bytes, everyone receives them
+    ids = [bytes(range(128)) if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    assert ids[0] == bytes(range(128))
+
+    rng = np.random.default_rng(4)          # same seed on every rank: identical parameters and global batch
+    dims, batch = [24, 40, 40, 12], 64
+    ws = [rng.uniform(-np.sqrt(6 / dims[i]), np.sqrt(6 / dims[i]), (dims[i], dims[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(3)]
+    x = rng.standard_normal((batch, dims[0]), dtype=np.float32)
+    t = rng.standard_normal((batch, dims[-1]), dtype=np.float32)
+    a, b = ts.distributed.shard_rows(batch, rank, world)
+    st = ora.MlpState(ws, bs)
+    losses = []
+    for step in range(1, 4):
+        r = ora.mlp_step(st, x[a:b], t[a:b], loss_kind=ora.LOSS_MSE, do_adam=False)   # local mean loss, local gradients
+        losses.append(float(r["loss"]))
+        for g in st.gw + st.gb:
+            tg = torch.from_numpy(g)
+            dist.all_reduce(tg, op=dist.ReduceOp.SUM)                                   # in place, like ncclAllReduce
+        scale = np.float32(1.0 / world)
+        for l in range(3):                                                              # Adam with grad_scale = 1/world
+            ora.adam_update(st.w[l].reshape(-1), (st.gw[l] * scale).reshape(-1), st.mw[l].reshape(-1), st.vw[l].reshape(-1), step)
+            ora.adam_update(st.b[l], st.gb[l] * scale, st.mb[l], st.vb[l], step)
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *st.w, *st.b, losses=np.array(losses))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_two_rank_data_parallel_step_matches_single_process(ora, tmp_path):
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    keys = [k for k in r0.files if k.startswith("arr_")]
+    for k in keys:                                    # replicas stay bit-identical
+        assert np.array_equal(r0[k], r1[k]), k
+    # single process on the whole batch
+    rng = np.random.default_rng(4)
+    dims, batch = [24, 40, 40, 12], 64
+    ws = [rng.uniform(-np.sqrt(6 / dims[i]), np.sqrt(6 / dims[i]), (dims[i], dims[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(3)]
+    x = rng.standard_normal((batch, dims[0]), dtype=np.float32)
+    t = rng.standard_normal((batch, dims[-1]), dtype=np.float32)
+    st = ora.MlpState(ws, bs)
+    full_losses = [float(ora.mlp_step(st, x, t, loss_kind=ora.LOSS_MSE)["loss"]) for _ in range(3)]
+    single = st.w + st.b
+    for i, k in enumerate(keys):
+        # Adam normalises by sqrt(v): last-bit differences in the summed gradient move a parameter by ~1e-3 * lr
+        np.testing.assert_allclose(r0[k], single[i], rtol=1e-5, atol=3e-6)
+    # the global mean loss is the mean of the per-rank mean losses (equal shard sizes)
+    np.testing.assert_allclose((r0["losses"] + r1["losses"]) / 2, full_losses, rtol=1e-5)
