@@ -344,7 +344,7 @@ def run_gpu(args, d: Dist):
 
 
 # ------------------------------------------------------------------------ single-kernel cases
-MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "adam", "add", "mul_backward", "relu_backward_colsum",
+MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum")
 
 
@@ -374,10 +374,12 @@ def run_micro(args):
     if name.startswith("gemm"):
         m = nn = k = n or 8192
         a, b, c = dev(rng.standard_normal((m, k), dtype=np.float32)), dev(rng.standard_normal((k, nn), dtype=np.float32)), empty(m * nn)
-        ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0)}[name]
-        prec = 0 if name.endswith("fp32") else 1
+        ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0), "gemm_nn_tf32x3": (0, 0)}[name]
+        prec = 0 if name.endswith("fp32") else 2 if name.endswith("x3") else 1
         launch = lambda: chk(lib.launch_gemm_kernel(a, b, c, m, nn, k, ta, tb, None, 0, None, prec, None), name)
-        work, unit, peak = 2.0 * m * nn * k, "TFLOP/s", (peaks["bf16_burst"] / 2.0 if prec else None)
+        # 3xTF32 does three tensor-core sweeps (plus the operand split) for the same algorithmic flop: its roofline is a third
+        peak = {0: None, 1: peaks["bf16_burst"] / 2.0, 2: peaks["bf16_burst"] / 6.0}[prec]
+        work, unit = 2.0 * m * nn * k, "TFLOP/s"
     elif name == "adam":
         n = n or (1 << 26)
         bufs = [dev(rng.standard_normal(n, dtype=np.float32)) for _ in range(2)] + [dev(np.zeros(n, np.float32)) for _ in range(2)]

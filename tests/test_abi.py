@@ -46,7 +46,9 @@ def test_library_does_not_link_torch_or_the_oracle():
     import subprocess
     out = subprocess.run(["ldd", os.path.join(ROOT, "train-station_b200", "libtrain_station_b200.so")],
                          capture_output=True, text=True).stdout
-    assert "torch" not in out and "oracle" not in out and "nccl" in out
+    # NCCL is bound with dlopen on first use of data parallelism, so that a process which also imports
+    # PyTorch (which bundles its own libnccl.so.2) ends up with a single copy whichever is loaded first
+    assert "torch" not in out and "oracle" not in out and "nccl" not in out
 
 
 def test_fails_loudly_without_a_gpu(ts):

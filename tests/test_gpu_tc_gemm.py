@@ -72,6 +72,42 @@ def test_tf32_gemm_epilogues(gpu, ora):
     assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, bias=bias), ora.add_row(exact, bias), "bias")
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1000, 264, 520), (512, 1024, 2048)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_tf32x3_gemm_is_fp32_accurate(gpu, m, n, k, ta, tb):
+    """3xTF32 (operands split into TF32-exact high and low parts, three tensor-core sweeps): error at the FP32 level."""
+    rng = np.random.default_rng(m + n + k + ta * 2 + tb)
+    a, b = rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((k, n), dtype=np.float32)
+    a_st = np.ascontiguousarray(a.T) if ta else a
+    b_st = np.ascontiguousarray(b.T) if tb else b
+    got = _run(gpu, a_st, b_st, m, n, k, ta, tb, precision=2)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    mag = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    err = np.abs(got - exact) / mag
+    assert err.max() <= 2e-6, f"max err/mag {err.max():.3e}"      # a sequential f32 chain over k is allowed k * 6e-8
+    fp32 = _run(gpu, a_st, b_st, m, n, k, ta, tb, precision=0)
+    # the FP32 kernel's own sequential chain carries up to ~sqrt(k) * 6e-8 * mag of rounding error
+    assert np.all(np.abs(got - fp32) <= 4e-6 * mag)
+    assert np.abs(got - exact).max() <= np.abs(fp32 - exact).max() * 2 + 1e-30   # and 3xTF32 is no worse than it
+
+
+def test_training_step_tf32x3_meets_fp32_tolerance(gpu, ora):
+    from test_gpu_engine import _mlp_device
+    rng = np.random.default_rng(12)
+    dims, batch = [256, 512, 512, 128], 384
+    ws = [rng.uniform(-np.sqrt(6 / dims[i]), np.sqrt(6 / dims[i]), (dims[i], dims[i + 1])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(3)]
+    x, t = rng.standard_normal((batch, dims[0]), dtype=np.float32), rng.standard_normal((batch, dims[-1]), dtype=np.float32)
+    st = ora.MlpState(ws, bs)
+    ref = ora.mlp_step(st, x, t, loss_kind=ora.LOSS_MSE)
+    gpu.set_matmul_precision(gpu.TF32X3)
+    got = _mlp_device(gpu, ws, bs, x, t, "mse", False)
+    assert abs(got["loss"] - float(ref["loss"])) <= 1e-5 * abs(float(ref["loss"]))
+    for i in range(3):
+        np.testing.assert_allclose(got["gw"][i], st.gw[i], rtol=1e-5, atol=1e-6)     # the task's FP32-mode tolerance
+        np.testing.assert_allclose(got["w"][i], st.w[i], rtol=1e-5, atol=2e-6)
+
+
 def test_tf32_long_k_accumulation(gpu):
     rng = np.random.default_rng(6)
     m, n, k = 256, 256, 16384

@@ -56,7 +56,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if verbose and out:
             print(out)
         objs.append(obj)
-    link = [nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-lnccl", "-Xcompiler", "-fPIC"]
+    # NCCL is opened with dlopen when data parallelism is first used (see engine.cu), so it is not linked here
+    link = [nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-ldl", "-Xcompiler", "-fPIC"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")

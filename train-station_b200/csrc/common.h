@@ -130,7 +130,12 @@ struct GemmArgs {
     bool relu;
     const float* mask;   // [m,n] or null
     bool round_tf32 = false;   // tensor-core path only: store the result rounded to nearest TF32
+    // 3xTF32: when both are set, a and b hold the TF32-exact high parts and these the low parts
+    const float* a_lo = nullptr;
+    const float* b_lo = nullptr;
 };
+// hi = x rounded to nearest TF32, lo = (x - hi) rounded to nearest TF32: x = hi + lo to about 2^-22 relative.
+bool split_tf32(const float* x, float* hi, float* lo, size_t n, cudaStream_t s);
 // out = x rounded to the nearest TF32 value (10 explicit mantissa bits, ties away from zero).
 bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s);
 bool sgemm(const GemmArgs& g, cudaStream_t s);                       // FFMA, reference summation order

@@ -156,6 +156,17 @@ struct RoundTf32F {
         o[0] = __uint_as_float(r);
     }
 };
+// x = hi + lo with both parts exact in TF32 (the subtraction is exact in FP32: hi shares x's leading bits)
+struct SplitTf32F {
+    __device__ void apply(const float* x, float* o) const {
+        uint32_t h, l;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x[0]));
+        const float hi = __uint_as_float(h);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(__fsub_rn(x[0], hi)));
+        o[0] = hi;
+        o[1] = __uint_as_float(l);
+    }
+};
 // inputs y, t: ((inv_n * upstream) * (2 * (y - t))): ReduceMean -> PowScalar(2) -> Sub chain
 // (grad_fn/reductions/mean.rs:10-19, grad_fn/ops/pow.rs:5-27, grad_fn/ops/sub.rs:26-31).
 struct MseGradF {
@@ -231,6 +242,10 @@ bool fill_from_scalar(float* o, const float* scalar, float sc, size_t n, cudaStr
 bool add_scalar_bcast(const float* a, const float* scalar_dev, float* o, size_t n, cudaStream_t s) {
     if (!scalar_dev) { set_error("add_scalar_bcast: null scalar"); return false; }
     return launch_ew(Ptrs<1, 1>{{a}, {o}}, n, AddScalarBcastF{scalar_dev}, s);
+}
+bool split_tf32(const float* x, float* hi, float* lo, size_t n, cudaStream_t s) {
+    if (!hi || !lo) { set_error("split_tf32: null output"); return false; }
+    return launch_ew(Ptrs<1, 2>{{x}, {hi, lo}}, n, SplitTf32F{}, s);
 }
 bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, RoundTf32F{}, s); }
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {

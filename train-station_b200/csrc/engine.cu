@@ -15,7 +15,8 @@
 //   * binary ops give each operand its own gradient (the reference zips gradients to
 //     input ids positionally and mis-assigns them when only the second operand requires
 //     grad: tensor/ops/add.rs:135-142 vs gradtrack/engine.rs:1000-1001).
-#include <nccl.h>
+#include <dlfcn.h>
+#include <nccl.h>   // types only: the functions are resolved at run time, see NcclApi
 
 #include <algorithm>
 #include <atomic>
@@ -42,9 +43,12 @@ struct Storage {
     bool tf32_clean = false;
     float* tf32_copy = nullptr;
     uint64_t tf32_copy_version = 0;
+    float* tf32_lo = nullptr;          // 3xTF32 mode: rn_tf32(data - tf32_copy)
+    uint64_t tf32_lo_version = 0;
     ~Storage() {
         if (ready) cudaEventDestroy(ready);
         if (c && tf32_copy) c->alloc.free(tf32_copy);
+        if (c && tf32_lo) c->alloc.free(tf32_lo);
         if (c && ptr) c->alloc.free(ptr);
     }
 };
@@ -129,6 +133,22 @@ static const float* tf32_operand(DeviceCtx* c, const TensorP& t) {
     return s->tf32_copy;
 }
 
+// 3xTF32 mode: the operand as a TF32-exact high part plus a TF32-exact low part, cached like the copy above.
+static bool tf32_split_operand(DeviceCtx* c, const TensorP& t, const float** hi, const float** lo) {
+    Storage* s = t->st.get();
+    const bool fresh = s->tf32_copy && s->tf32_lo && s->tf32_copy_version == s->version && s->tf32_lo_version == s->version;
+    if (!fresh) {
+        const size_t bytes = (s->n ? s->n : 1) * sizeof(float);
+        if (!s->tf32_copy && !(s->tf32_copy = c->alloc.alloc(bytes))) return false;
+        if (!s->tf32_lo && !(s->tf32_lo = c->alloc.alloc(bytes))) return false;
+        if (!k::split_tf32(s->ptr, s->tf32_copy, s->tf32_lo, s->n, c->compute)) return false;
+        s->tf32_copy_version = s->tf32_lo_version = s->version;
+    }
+    *hi = s->tf32_copy;
+    *lo = s->tf32_lo;
+    return true;
+}
+
 static bool materialize(const TensorP& t, bool for_gemm) {
     if (!t->pending) return t->st != nullptr;
     DeviceCtx* c = ctx();
@@ -148,6 +168,8 @@ static bool materialize(const TensorP& t, bool for_gemm) {
         if (!g.a || !g.b) return false;
         g.round_tf32 = for_gemm;
         st->tf32_clean = for_gemm;
+    } else if (matmul_precision() == 2 && k::gemm_tc_supported(g)) {
+        if (!tf32_split_operand(c, p.a, &g.a, &g.a_lo) || !tf32_split_operand(c, p.b, &g.b, &g.b_lo)) return false;
     }
     if (!k::gemm(g, -1, c, c->compute)) return false;
     t->st = st;
@@ -213,6 +235,40 @@ static bool flush_pending() {
     return ok;
 }
 
+// ------------------------------------------------------------------ NCCL, bound at run time
+// NCCL is opened with dlopen when data parallelism is first used, not linked: a process that also
+// imports PyTorch must end up with ONE libnccl.so.2 (PyTorch bundles a newer one than the system's,
+// and whichever is loaded first is the one both get).  Loading it lazily means a single-GPU process
+// never loads NCCL at all, and a multi-GPU process that imported PyTorch first shares PyTorch's copy.
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+static NcclApi* nccl_api() {
+    static NcclApi api;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    if (api.ok) return &api;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
+    if (!h) { set_error("data parallelism needs NCCL: dlopen(libnccl.so.2) failed: %s", dlerror()); return nullptr; }
+    api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+    api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
+    api.AllReduce = (decltype(api.AllReduce))dlsym(h, "ncclAllReduce");
+    api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
+    api.GetErrorString = (decltype(api.GetErrorString))dlsym(h, "ncclGetErrorString");
+    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString) {
+        set_error("data parallelism needs NCCL: a required symbol is missing from libnccl.so.2");
+        return nullptr;
+    }
+    api.ok = true;
+    return &api;
+}
+
 // ------------------------------------------------------------------ data-parallel state
 struct DpState {
     ncclComm_t comm = nullptr;
@@ -231,8 +287,10 @@ static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n) {
     }
     TS_CHECK(cudaEventRecord(g_dp.ev_compute, c->compute));
     TS_CHECK(cudaStreamWaitEvent(c->comm, g_dp.ev_compute, 0));
-    ncclResult_t r = ncclAllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm);
-    if (r != ncclSuccess) { set_error("ncclAllReduce failed: %s", ncclGetErrorString(r)); return false; }
+    NcclApi* nc = nccl_api();
+    if (!nc) return false;
+    ncclResult_t r = nc->AllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm);
+    if (r != ncclSuccess) { set_error("ncclAllReduce failed: %s", nc->GetErrorString(r)); return false; }
     g_dp.comm_outstanding = true;
     return true;
 }
@@ -987,9 +1045,11 @@ TS_API ts_tensor* ts_adam_state_v(const ts_adam* o, const ts_tensor* p) { return
 TS_API bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]) {
     static_assert(sizeof(ncclUniqueId) == TS_DP_UNIQUE_ID_BYTES, "NCCL unique id size");
     if (!id_out) { set_error("ts_dp_get_unique_id: null buffer"); return false; }
+    NcclApi* nc = nccl_api();
+    if (!nc) return false;
     ncclUniqueId id;
-    ncclResult_t r = ncclGetUniqueId(&id);
-    if (r != ncclSuccess) { set_error("ncclGetUniqueId failed: %s", ncclGetErrorString(r)); return false; }
+    ncclResult_t r = nc->GetUniqueId(&id);
+    if (r != ncclSuccess) { set_error("ncclGetUniqueId failed: %s", nc->GetErrorString(r)); return false; }
     memcpy(id_out, &id, sizeof(id));
     return true;
 }
@@ -1000,16 +1060,18 @@ TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int ran
     if (g_dp.comm) { set_error("ts_dp_init: already initialised on this thread"); return false; }
     g_dp.rank = rank; g_dp.world = world;
     if (world == 1) return true;
+    NcclApi* nc = nccl_api();
+    if (!nc) return false;
     ncclUniqueId id;
     memcpy(&id, id_in, sizeof(id));
-    ncclResult_t r = ncclCommInitRank(&g_dp.comm, world, id, rank);
-    if (r != ncclSuccess) { g_dp.comm = nullptr; set_error("ncclCommInitRank failed: %s", ncclGetErrorString(r)); return false; }
+    ncclResult_t r = nc->CommInitRank(&g_dp.comm, world, id, rank);
+    if (r != ncclSuccess) { g_dp.comm = nullptr; set_error("ncclCommInitRank failed: %s", nc->GetErrorString(r)); return false; }
     return true;
 }
 TS_API void ts_dp_finalize(void) {
     DeviceCtx* c = ctx();
     if (c) { cudaStreamSynchronize(c->comm); cudaStreamSynchronize(c->compute); }
-    if (g_dp.comm) { ncclCommDestroy(g_dp.comm); g_dp.comm = nullptr; }
+    if (g_dp.comm) { if (NcclApi* nc = nccl_api()) nc->CommDestroy(g_dp.comm); g_dp.comm = nullptr; }
     if (g_dp.ev_compute) { cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); g_dp.ev_compute = g_dp.ev_comm = nullptr; }
     g_dp.params.clear();
     g_dp.rank = 0; g_dp.world = 1; g_dp.comm_outstanding = false;

@@ -172,6 +172,7 @@ struct KernelArgs {
     int relu;
     int round_out;
     int a_grouped, b_grouped;   // MN-major operand described by a 3-D [group][k][32] tensor map
+    int passes;                 // 1 = TF32, 3 = 3xTF32 (hi/lo split operands)
     uint32_t m, n, k;
     int* error_flag;
 };
@@ -184,7 +185,8 @@ __device__ __forceinline__ float rn_tf32(float x) {
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, KernelArgs args) {
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_a_lo, const __grid_constant__ CUtensorMap tm_b_lo, KernelArgs args) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: align the ring to that.
@@ -203,6 +205,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (args.k + BK - 1) / BK;
+    // 3xTF32: with a = a_hi + a_lo and b = b_hi + b_lo (each part exact in TF32), the accumulator receives
+    // a_lo.b_hi, then a_hi.b_lo, then a_hi.b_hi: three sweeps over K into the same tensor-memory tile.
+    const uint32_t total_kb = num_kb * (uint32_t)args.passes;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -243,33 +248,36 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t tm, tn;
                 tile_coords(tile, tm, tn);
                 const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t vkb = 0; vkb < total_kb; ++vkb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); ok = false; break; }
                     const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
-                    const int k0 = (int)(kb * BK);
+                    const uint32_t pass = vkb / num_kb;
+                    const int k0 = (int)((vkb - pass * num_kb) * BK);
+                    const CUtensorMap* pa = (args.passes == 3 && pass == 0) ? &tm_a_lo : &tm_a;
+                    const CUtensorMap* pb = (args.passes == 3 && pass == 1) ? &tm_b_lo : &tm_b;
                     mbar_expect_tx(full_bar(stage), C::kStageBytes);
                     // An MN-major tile is BM/32 (BN/32) boxes of 32 columns x 32 k-rows.  When the row length is a
                     // multiple of 32 the matrix is also described as [column group][k][32] and one 3-D copy brings
                     // all boxes of the tile; otherwise one 2-D copy per box.
                     if (A_MN) {
                         if (args.a_grouped) {
-                            tma_load_3d(sa, &tm_a, full_bar(stage), 0, k0, m0 / 32);
+                            tma_load_3d(sa, pa, full_bar(stage), 0, k0, m0 / 32);
                         } else {
 #pragma unroll
-                            for (int b = 0; b < BM / 32; ++b) tma_load_2d(sa + b * 4096, &tm_a, full_bar(stage), m0 + 32 * b, k0);
+                            for (int b = 0; b < BM / 32; ++b) tma_load_2d(sa + b * 4096, pa, full_bar(stage), m0 + 32 * b, k0);
                         }
                     } else {
-                        tma_load_2d(sa, &tm_a, full_bar(stage), k0, m0);
+                        tma_load_2d(sa, pa, full_bar(stage), k0, m0);
                     }
                     if (B_MN) {
                         if (args.b_grouped) {
-                            tma_load_3d(sb, &tm_b, full_bar(stage), 0, k0, n0 / 32);
+                            tma_load_3d(sb, pb, full_bar(stage), 0, k0, n0 / 32);
                         } else {
 #pragma unroll
-                            for (int b = 0; b < BN / 32; ++b) tma_load_2d(sb + b * 4096, &tm_b, full_bar(stage), n0 + 32 * b, k0);
+                            for (int b = 0; b < BN / 32; ++b) tma_load_2d(sb + b * 4096, pb, full_bar(stage), n0 + 32 * b, k0);
                         }
                     } else {
-                        tma_load_2d(sb, &tm_b, full_bar(stage), k0, n0);
+                        tma_load_2d(sb, pb, full_bar(stage), k0, n0);
                     }
 #pragma unroll
                     for (int s = 0; s < C::kStages; ++s)
@@ -302,7 +310,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = 0; kb < total_kb; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrFullWait); ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
@@ -446,18 +454,28 @@ bool make_map_grouped(CUtensorMap* tm, const float* ptr, size_t rows, size_t col
 template <int BN, bool A_MN, bool B_MN>
 bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     using Cf = Cfg<BN>;
-    CUtensorMap tm_a, tm_b;
+    CUtensorMap tm_a, tm_b, tm_a_lo, tm_b_lo;
     // the grouped description is an optimisation: if the driver refuses it, the per-box maps still work
     bool a_grouped = A_MN && g.m % 32 == 0 && make_map_grouped(&tm_a, g.a, g.k, g.m, BK, BM / 32);
     bool b_grouped = B_MN && g.n % 32 == 0 && make_map_grouped(&tm_b, g.b, g.k, g.n, BK, BN / 32);
-    // A: stored [k][m] when transposed (MN-major) else [m][k]
-    if (a_grouped) {}
-    else if (A_MN) { if (!make_map(&tm_a, g.a, g.k, g.m, 32, 32, true)) return false; }
-    else { if (!make_map(&tm_a, g.a, g.m, g.k, BK, BM, false)) return false; }
-    // B: stored [k][n] when not transposed (MN-major) else [n][k]
-    if (b_grouped) {}
-    else if (B_MN) { if (!make_map(&tm_b, g.b, g.k, g.n, 32, 32, true)) return false; }
-    else { if (!make_map(&tm_b, g.b, g.n, g.k, BK, BN, false)) return false; }
+    // A: stored [k][m] when transposed (MN-major) else [m][k];  B: stored [k][n] when not transposed (MN-major) else [n][k]
+    auto map_a = [&](CUtensorMap* tm, const float* p) {
+        if (a_grouped) return make_map_grouped(tm, p, g.k, g.m, BK, BM / 32);
+        return A_MN ? make_map(tm, p, g.k, g.m, 32, 32, true) : make_map(tm, p, g.m, g.k, BK, BM, false);
+    };
+    auto map_b = [&](CUtensorMap* tm, const float* p) {
+        if (b_grouped) return make_map_grouped(tm, p, g.k, g.n, BK, BN / 32);
+        return B_MN ? make_map(tm, p, g.k, g.n, 32, 32, true) : make_map(tm, p, g.n, g.k, BK, BN, false);
+    };
+    if (!a_grouped && !map_a(&tm_a, g.a)) return false;
+    if (!b_grouped && !map_b(&tm_b, g.b)) return false;
+    const bool split3 = g.a_lo && g.b_lo;
+    if (split3) {
+        if (!map_a(&tm_a_lo, g.a_lo) || !map_b(&tm_b_lo, g.b_lo)) return false;
+    } else {
+        tm_a_lo = tm_a;
+        tm_b_lo = tm_b;
+    }
     auto kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
     static bool attr_set[64] = {false};   // the attribute is per device
     if (!attr_set[c->device]) {
@@ -466,9 +484,10 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     }
     size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN);
     int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
-    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
-    ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
-    kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, ka);
+    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+    ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
+    kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
 }
 
@@ -496,8 +515,22 @@ bool gemm_tc_supported(const GemmArgs& g) {
 }
 
 bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
-    (void)split3;
     if (!gemm_tc_supported(g)) { set_error("gemm: shape or alignment not supported by the tensor-core kernel"); return false; }
+    if (split3 && !(g.a_lo && g.b_lo)) {
+        // The caller passed plain FP32 operands: split them into TF32-exact high and low parts in scratch memory.
+        const size_t na = g.m * g.k, nb = g.k * g.n;
+        float* buf = c->alloc.alloc(2 * (na + nb) * sizeof(float) + 4 * 256);
+        if (!buf) return false;
+        auto up = [](size_t x) { return (x + 63) & ~size_t(63); };   // keep every part 256-byte aligned
+        float *a_hi = buf, *a_lo = a_hi + up(na), *b_hi = a_lo + up(na), *b_lo = b_hi + up(nb);
+        GemmArgs h = g;
+        h.a = a_hi; h.a_lo = a_lo; h.b = b_hi; h.b_lo = b_lo;
+        bool ok = split_tf32(g.a, a_hi, a_lo, na, s) && split_tf32(g.b, b_hi, b_lo, nb, s) && gemm_tc(h, true, c, s);
+        if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
+        c->alloc.free(buf);
+        return ok;
+    }
+    if (!split3 && (g.a_lo || g.b_lo)) { set_error("gemm: low parts given without the 3xTF32 mode"); return false; }
     size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
     if (g.n <= 128 || tiles256 < (size_t)c->sm_count) return launch_tc_bn<128>(g, c, s);
     return launch_tc_bn<256>(g, c, s);
