@@ -59,6 +59,24 @@ def test_tf32_gemm_exact_on_small_integers(gpu):
         assert np.array_equal(got, exact), (ta, tb, int((got != exact).sum()))
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 96), (2308, 8196, 132)])
+def test_two_cta_kernel_exact_on_small_integers(gpu, ora, m, n, k):
+    """Problems with at least 74 tiles of 256 x 256 run on CTA pairs (cta_group::2): every layout, edge tiles, epilogues."""
+    rng = np.random.default_rng(m + k)
+    a = rng.integers(-4, 5, (m, k)).astype(np.float32)
+    b = rng.integers(-4, 5, (k, n)).astype(np.float32)
+    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    for ta, tb in ((0, 0), (0, 1), (1, 0), (1, 1)):
+        got = _run(gpu, np.ascontiguousarray(a.T) if ta else a, np.ascontiguousarray(b.T) if tb else b, m, n, k, ta, tb)
+        assert np.array_equal(got, exact), (ta, tb, int((got != exact).sum()))
+    bias = rng.integers(-50, 50, n).astype(np.float32)
+    mask = rng.standard_normal((m, n), dtype=np.float32)
+    assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, bias=bias, relu=1), ora.relu(ora.add_row(exact, bias)), "bias+relu")
+    assert_bit_equal(_run(gpu, a, b, m, n, k, 0, 0, mask=mask), ora.relu_bwd(mask, exact), "mask")
+    got3 = _run(gpu, a, b, m, n, k, 0, 0, precision=2)
+    assert np.array_equal(got3, exact), "3xTF32 on integers"
+
+
 def test_tf32_gemm_epilogues(gpu, ora):
     rng = np.random.default_rng(5)
     m, n, k = 300, 384, 200

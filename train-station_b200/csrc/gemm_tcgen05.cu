@@ -398,6 +398,294 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
+// =====================================================================================================
+// Two-CTA variant: a cluster of two CTAs on the two SMs of a TPC computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its 128 rows of A and ITS HALF of the B tile (128 columns),
+// so per SM the shared-memory traffic per flop drops by a third and a stage is 32 KiB instead of 48 KiB:
+// six stages fit, which is what hides the TMA latency for 4-byte operands.
+//   * the leader CTA (cluster rank 0) issues every MMA; the tensor cores of both SMs read A from their own
+//     shared memory and B from both; each SM accumulates its 128 rows in its own tensor memory;
+//   * both producers signal the LEADER's full barrier (TMA copies of the peer carry .cta_group::2 so that
+//     their completion may land on the other CTA's mbarrier); the leader arms it with the bytes of both;
+//   * the leader's commits arrive on the stage-empty and accumulator-full barriers of BOTH CTAs (one
+//     commit per CTA, addressed through mapa);
+//   * both epilogues arrive on the leader's accumulator-empty barrier (the peer's with a cluster-scope
+//     remote arrive).
+// No copy uses cluster multicast.  All waits are bounded exactly as in the one-CTA kernel; the two cluster
+// barriers (after set-up, before exit) complete because every thread of both CTAs reaches them.
+constexpr int kBN2 = 256, kStages2 = 6;
+constexpr int kHalfBytes = BM * BK * 4;               // 16 KiB: 128 rows (or columns) x 32 k
+constexpr int kStageBytes2 = 2 * kHalfBytes;          // A half-tile + B half-tile
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 256 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA copies whose completion is signalled on an mbarrier that may live in the other CTA of the pair
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_commit(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tmem2_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem2_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc2(bool a_mn, bool b_mn) {   // M = 256 across the pair, N = 256
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(kBN2 >> 3) << 17) |
+           ((uint32_t)(256 >> 4) << 24);
+}
+
+// one 32-column chunk of one output row: bias, ReLU, mask, rounding, store
+__device__ __forceinline__ void store_chunk(const KernelArgs& args, const uint32_t (&r)[32], float* crow, const float* mrow, uint32_t col0) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const uint32_t col = col0 + q * 4;
+        if (col < args.n) {
+            float4 v = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                   __uint_as_float(r[q * 4 + 3]));
+            if (args.bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+            }
+            if (args.relu) {
+                v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f; v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
+            }
+            if (mrow) {
+                const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
+                v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
+            }
+            if (args.round_out) { v.x = rn_tf32(v.x); v.y = rn_tf32(v.y); v.z = rn_tf32(v.z); v.w = rn_tf32(v.w); }
+            *reinterpret_cast<float4*>(crow + col) = v;
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const __grid_constant__ CUtensorMap tm_a_lo, const __grid_constant__ CUtensorMap tm_b_lo, KernelArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // same offset in both CTAs of the pair
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kStages2 * kStageBytes2;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages2 + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages2 + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages2 + 2 + a); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * kStages2 + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages2 * kStageBytes2 + 8 * (2 * kStages2 + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t rank = cluster_ctarank();                 // 0 = leader
+    const uint32_t pair = blockIdx.x / 2, num_pairs = gridDim.x / 2;
+    const uint32_t tiles_m = (args.m + 255) / 256, tiles_n = (args.n + kBN2 - 1) / kBN2;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (args.k + BK - 1) / BK;
+    const uint32_t total_kb = num_kb * (uint32_t)args.passes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 2 * kEpiThreads); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem2_alloc(smem_u32(tmem_slot), 512);     // both CTAs, same warp, same slot offset
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                        // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    constexpr uint32_t kGroup = 8;                             // 8 row-tiles of 256 share their B panels in L2
+    auto tile_coords = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
+        const uint32_t per_group = kGroup * tiles_n;
+        const uint32_t g = tile / per_group, r = tile % per_group;
+        const uint32_t first = g * kGroup;
+        const uint32_t gsz = (tiles_m - first) < kGroup ? (tiles_m - first) : kGroup;
+        tm = first + r % gsz;
+        tn = r / gsz;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int armed_parity[kStages2];
+#pragma unroll
+            for (int s = 0; s < kStages2; ++s) armed_parity[s] = -1;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                uint32_t tm, tn;
+                tile_coords(tile, tm, tn);
+                const int m0 = (int)(tm * 256 + rank * 128);          // this CTA's rows of A
+                const int n0 = (int)(tn * kBN2 + rank * 128);         // this CTA's columns of B
+                for (uint32_t vkb = 0; vkb < total_kb; ++vkb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); ok = false; break; }
+                    const uint32_t sa = smem_base + stage * kStageBytes2, sb = sa + kHalfBytes;
+                    const uint32_t pass = vkb / num_kb;
+                    const int k0 = (int)((vkb - pass * num_kb) * BK);
+                    const CUtensorMap* pa = (args.passes == 3 && pass == 0) ? &tm_a_lo : &tm_a;
+                    const CUtensorMap* pb = (args.passes == 3 && pass == 1) ? &tm_b_lo : &tm_b;
+                    const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kStageBytes2);   // the bytes of both CTAs
+                    if (A_MN) {
+                        if (args.a_grouped) {
+                            tma2_load_3d(sa, pa, lead_full, 0, k0, m0 / 32);
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) tma2_load_2d(sa + b * 4096, pa, lead_full, m0 + 32 * b, k0);
+                        }
+                    } else {
+                        tma2_load_2d(sa, pa, lead_full, k0, m0);
+                    }
+                    if (B_MN) {
+                        if (args.b_grouped) {
+                            tma2_load_3d(sb, pb, lead_full, 0, k0, n0 / 32);
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) tma2_load_2d(sb + b * 4096, pb, lead_full, n0 + 32 * b, k0);
+                        }
+                    } else {
+                        tma2_load_2d(sb, pb, lead_full, k0, n0);
+                    }
+#pragma unroll
+                    for (int s = 0; s < kStages2; ++s)
+                        if (s == (int)stage) armed_parity[s] = (int)phase;
+                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if ((!ok || *abort_flag) && rank == 0) {
+                // Bounded drain before the pair retires: the leader's full barriers count the bytes of both CTAs'
+                // copies, so waiting on them here covers the peer's outstanding copies too.
+#pragma unroll
+                for (int s = 0; s < kStages2; ++s) {
+                    if (armed_parity[s] >= 0) {
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(full_bar(s), (uint32_t)armed_parity[s])) {
+                            if (clock64() - t0 > kWaitCycles) { atomicCAS(args.error_flag, 0, kErrDrain); break; }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc2(A_MN, B_MN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+                const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN2;
+                for (uint32_t kb = 0; kb < total_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrFullWait); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * kStageBytes2, sb = sa + kHalfBytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t da = A_MN ? smem_desc(sa + kk * 1024, 4096, 512, kLayoutSw128Base32)
+                                                 : smem_desc(sa + kk * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t db = B_MN ? smem_desc(sb + kk * 1024, 4096, 512, kLayoutSw128Base32)
+                                                 : smem_desc(sb + kk * 32, 16, 1024, kLayoutSw128);
+                        umma2_tf32(d_tmem, da, db, idesc, (kb | (uint32_t)kk) != 0u ? 1u : 0u);
+                    }
+                    umma2_commit(map_to_cta(empty_bar(stage), 0));   // the stage is free in both CTAs once these MMAs have read it
+                    umma2_commit(map_to_cta(empty_bar(stage), 1));
+                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma2_commit(map_to_cta(acc_full_bar(acc), 0));      // accumulators complete in both CTAs
+                umma2_commit(map_to_cta(acc_full_bar(acc), 1));
+            }
+            if (!ok || *abort_flag) {
+                umma2_commit(map_to_cta(drain_bar, 0));
+                const long long t0 = clock64();
+                while (!mbar_try_wait(drain_bar, 0)) {
+                    if (clock64() - t0 > kWaitCycles) { atomicCAS(args.error_flag, 0, kErrDrain); break; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const uint32_t lane_group = (uint32_t)(warp & 3);
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+            uint32_t tm, tn;
+            tile_coords(tile, tm, tn);
+            const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+            if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccFullWait); ok = false; break; }
+            tc_fence_after();
+            const uint32_t row = tm * 256 + rank * 128 + lane_group * 32 + lane;
+            const bool row_ok = row < args.m;
+            float* crow = args.c + (size_t)row * args.n;
+            const float* mrow = args.mask ? args.mask + (size_t)row * args.n : nullptr;
+#pragma unroll 1
+            for (int ch = 0; ch < kBN2 / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((lane_group * 32u) << 16) + acc * kBN2 + ch * 32, r);
+                tmem_ld_wait();
+                if (row_ok) store_chunk(args, r, crow, mrow, tn * kBN2 + ch * 32);
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));   // the leader's MMA thread owns the accumulators' reuse
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still touch it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem2_dealloc(tmem_base, 512);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -491,6 +779,58 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
 }
 
+// Two-CTA kernel: 256 x 256 tiles, each CTA of the pair loads 128 rows of A and 128 columns of B per stage.
+template <bool A_MN, bool B_MN>
+bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+    CUtensorMap tm_a, tm_b, tm_a_lo, tm_b_lo;
+    bool a_grouped = A_MN && g.m % 32 == 0 && make_map_grouped(&tm_a, g.a, g.k, g.m, BK, 4);
+    bool b_grouped = B_MN && g.n % 32 == 0 && make_map_grouped(&tm_b, g.b, g.k, g.n, BK, 4);
+    auto map_a = [&](CUtensorMap* tm, const float* p) {
+        if (a_grouped) return make_map_grouped(tm, p, g.k, g.m, BK, 4);
+        return A_MN ? make_map(tm, p, g.k, g.m, 32, 32, true) : make_map(tm, p, g.m, g.k, BK, 128, false);
+    };
+    auto map_b = [&](CUtensorMap* tm, const float* p) {
+        if (b_grouped) return make_map_grouped(tm, p, g.k, g.n, BK, 4);
+        return B_MN ? make_map(tm, p, g.k, g.n, 32, 32, true) : make_map(tm, p, g.n, g.k, BK, 128, false);
+    };
+    if (!a_grouped && !map_a(&tm_a, g.a)) return false;
+    if (!b_grouped && !map_b(&tm_b, g.b)) return false;
+    const bool split3 = g.a_lo && g.b_lo;
+    if (split3) {
+        if (!map_a(&tm_a_lo, g.a_lo) || !map_b(&tm_b_lo, g.b_lo)) return false;
+    } else {
+        tm_a_lo = tm_a;
+        tm_b_lo = tm_b;
+    }
+    auto kern = gemm_tf32_2cta_kernel<A_MN, B_MN>;
+    static bool attr_set[64] = {false};
+    if (!attr_set[c->device]) {
+        TS_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
+        attr_set[c->device] = true;
+    }
+    size_t tiles = ((g.m + 255) / 256) * ((g.n + kBN2 - 1) / kBN2);
+    size_t pairs = (size_t)c->sm_count / 2;
+    int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+    KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+    ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
+    kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
+    return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
+}
+
+bool launch_tc2_any(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+    const bool a_mn = g.trans_a, b_mn = !g.trans_b;
+    if (a_mn) return b_mn ? launch_tc2<true, true>(g, c, s) : launch_tc2<true, false>(g, c, s);
+    return b_mn ? launch_tc2<false, true>(g, c, s) : launch_tc2<false, false>(g, c, s);
+}
+
+// TS_GEMM_2CTA=0 keeps every GEMM on the one-CTA kernel (for A/B measurements).
+bool two_cta_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TS_GEMM_2CTA"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v == 1;
+}
+
 template <int BN>
 bool launch_tc_bn(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     const bool a_mn = g.trans_a, b_mn = !g.trans_b;
@@ -531,6 +871,9 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
         return ok;
     }
     if (!split3 && (g.a_lo || g.b_lo)) { set_error("gemm: low parts given without the 3xTF32 mode"); return false; }
+    // Large problems: pairs of CTAs on 256 x 256 tiles, as long as every pair gets at least one tile.
+    size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
+    if (two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)c->sm_count / 2) return launch_tc2_any(g, c, s);
     size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
     if (g.n <= 128 || tiles256 < (size_t)c->sm_count) return launch_tc_bn<128>(g, c, s);
     return launch_tc_bn<256>(g, c, s);
