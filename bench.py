@@ -158,7 +158,7 @@ class Dist:
 
 
 # ------------------------------------------------------------------------ CPU arm
-def cpu_baseline(sample_rows: int = 32):
+def cpu_baseline(sample_rows: int = 128):
     """Times the CPU oracle on `sample_rows` batch rows of the workload (all three layers, forward,
     backward) plus one full-size Adam update, single thread as the reference is, and extrapolates the
     row-proportional part to the global batch."""
@@ -206,7 +206,7 @@ def run_gpu(args, d: Dist):
     ts = entry.load_package()
     lib = ts._ffi.lib()
     ts.set_default_device(d.local_rank)
-    prec = {"tf32": ts.TF32, "fp32": ts.FP32}[args.precision]
+    prec = {"tf32": ts.TF32, "fp32": ts.FP32, "tf32x3": ts.TF32X3}[args.precision]
     ts.set_matmul_precision(prec)
     if d.world > 1:
         ids = [ts.distributed.get_unique_id() if d.rank == 0 else None]
@@ -283,10 +283,11 @@ def run_gpu(args, d: Dist):
         return int(n.value), float(t.value), float(w.value)
 
     peaks = measured_peaks()
-    cls = 0 if prec == ts.TF32 else 1
+    cls = 1 if prec == ts.FP32 else 0
     gl, gms, gwork = prof(cls)
-    tf32_peak = peaks["bf16_sustained"] / 2.0   # no TF32 entry is measured: half the measured sustained bf16 rate
-    roof = {"bound": "tensor", "kernel": "gemm_tf32_kernel (tcgen05)" if cls == 0 else "sgemm_kernel (FFMA)",
+    # no TF32 entry is measured: half the measured sustained bf16 rate (a sixth for the three sweeps of 3xTF32)
+    tf32_peak = peaks["bf16_sustained"] / (6.0 if prec == ts.TF32X3 else 2.0)
+    roof = {"bound": "tensor", "kernel": "gemm_tf32_2cta_kernel / gemm_tf32_kernel (tcgen05)" if cls == 0 else "sgemm_kernel (FFMA)",
             "achieved": (gwork / (gms * 1e-3) / 1e12) if gms > 0 else None, "peak": tf32_peak, "unit": "TFLOP/s",
             "frac": None, "traffic": None, "launches": gl, "avg_launch_ms": gms / gl if gl else None,
             "peak_source": f"{peaks['source']}: bf16_tflops_sustained / 2 (derived; TF32 runs at half the bf16 rate)",
@@ -326,7 +327,7 @@ def run_gpu(args, d: Dist):
     stats = ts.allocator_stats()
     line = {"metric": METRIC, "value": value, "unit": "steps/s", "n_gpus": d.world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "tf32" if prec == ts.TF32 else "f32", "data": "synthetic",
+            "dtype": args.precision if prec != ts.FP32 else "f32", "data": "synthetic",
             "config": {"workload": "C5 data-parallel wide MLP 4096-8192-8192-4096 f32, Kaiming-uniform init, ReLU, MSE, Adam(1e-3)",
                        "global_batch": GLOBAL_BATCH, "rows_per_gpu": local, "parallelism": f"dp{d.world}", "seed": SEED,
                        "gemm_precision": args.precision, "l2": "inputs and activations (>= 1 GiB each) are larger than the 126 MB L2",
@@ -341,6 +342,177 @@ def run_gpu(args, d: Dist):
         print(json.dumps(line), flush=True)
     if d.world > 1:
         ts.distributed.finalize()
+
+
+# ------------------------------------------------------------------------ the smaller BASELINE configurations
+CONFIGS = {
+    # name: (layer dims, batch, loss, relu after last layer, input requires grad, description)
+    "c1": ([784, 128], 32, "sum", True, False, "C1 README step: y = relu(x.w + b), loss = sum(y), Adam; x[32,784], w[784,128]; seed 0"),
+    "c3": ([8192, 8192], 8192, "mean", True, True, "C3 dense layer 8192^3: Y = relu(X.W + b), loss = mean(Y), dX dW db, Adam; seed 2"),
+    "c4": ([784, 1024, 1024, 10], 4096, "mse", False, False, "C4 MLP 784-1024-1024-10, batch 4096, one-hot targets, MSE, Adam; seed 3"),
+}
+
+
+def run_config(args):
+    """One of the single-GPU configurations C1, C3, C4 through the public API: steps/s, GEMM rate, CPU port beside it."""
+    dims, batch, loss_kind, relu_last, x_grad, desc = CONFIGS[args.config]
+    seed = {"c1": 0, "c3": 2, "c4": 3}[args.config]
+    ts = entry.load_package()
+    lib = ts._ffi.lib()
+    ts.set_default_device(0)
+    prec = {"tf32": ts.TF32, "fp32": ts.FP32, "tf32x3": ts.TF32X3}[args.precision]
+    ts.set_matmul_precision(prec)
+    rng = np.random.default_rng(seed)
+    L = len(dims) - 1
+    if args.config == "c1":
+        ws = [rng.standard_normal((dims[0], dims[1]), dtype=np.float32)]
+    elif args.config == "c3":
+        ws = [(rng.standard_normal((dims[0], dims[1])) * np.sqrt(1.0 / dims[0])).astype(np.float32)]   # variance 1/8192
+    else:
+        ws = [rng.uniform(-np.sqrt(6 / dims[i]), np.sqrt(6 / dims[i]), (dims[i], dims[i + 1])).astype(np.float32) for i in range(L)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(L)]
+    x = rng.standard_normal((batch, dims[0]), dtype=np.float32)
+    t = np.eye(dims[-1], dtype=np.float32)[rng.integers(0, dims[-1], batch)] if loss_kind == "mse" else None
+
+    W = [ts.Tensor.from_slice(w, w.shape).with_requires_grad() for w in ws]
+    B = [ts.Tensor.from_slice(b, b.shape).with_requires_grad() for b in bs]
+    params = [p for pair in zip(W, B) for p in pair]
+    opt = ts.Adam.with_learning_rate(1e-3)
+    opt.add_parameters(params)
+    pin_x = ts.PinnedBuffer(x.size); pin_x.array[:] = x.reshape(-1)
+    pin_t = None
+    if t is not None:
+        pin_t = ts.PinnedBuffer(t.size); pin_t.array[:] = t.reshape(-1)
+
+    def upload():
+        X = ts.Tensor.from_pinned_async(pin_x, x.shape)
+        if x_grad:
+            X = X.with_requires_grad()
+        return X, (ts.Tensor.from_pinned_async(pin_t, t.shape) if pin_t else None)
+
+    def step(X, T):
+        h = X
+        for i in range(L):
+            h = h.matmul(W[i]).add_tensor(B[i])
+            if i + 1 < L or relu_last:
+                h = h.relu()
+        loss = h.sum() if loss_kind == "sum" else h.mean() if loss_kind == "mean" else h.sub_tensor(T).pow_scalar(2.0).mean()
+        loss.backward(None)
+        opt.step(params)
+        opt.zero_grad(params)
+        return loss
+
+    X, T = upload()
+    for _ in range(args.warmup):
+        loss = step(X, T)
+    ts.synchronize()
+    ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
+    lib.ts_profile_reset(); lib.ts_profile_enable(1)
+    sampler = ClockSampler(0); sampler.start()
+    launches0 = int(lib.ts_launch_count())
+    lib.ts_event_record(ev0, None)
+    for _ in range(args.steps):
+        loss = step(X, T)
+    lib.ts_event_record(ev1, None)
+    ts.synchronize()
+    ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps
+    launches = int(lib.ts_launch_count()) - launches0
+    clocks = sampler.stop()
+    lib.ts_profile_enable(0)
+    ts._ffi.check(lib.ts_profile_collect(), "profile")
+    lib.ts_event_record(ev0, None)
+    for _ in range(args.steps):
+        l = step(*upload())
+        _ = l.value()
+    lib.ts_event_record(ev1, None)
+    ts.synchronize()
+    e2e_ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps
+
+    flop = 0.0
+    for i in range(L):
+        mnk = 2.0 * batch * dims[i] * dims[i + 1]
+        flop += 2 * mnk + (mnk if (i > 0 or x_grad) else 0.0)
+    n, tms, w = C.c_ulonglong(), C.c_double(), C.c_double()
+    cls = 1 if prec == ts.FP32 else 0
+    lib.ts_profile_get(cls, C.byref(n), C.byref(tms), C.byref(w))
+    peaks = measured_peaks()
+    peak = {ts.TF32: peaks["bf16_sustained"] / 2, ts.TF32X3: peaks["bf16_sustained"] / 6, ts.FP32: None}[prec]
+    ach = w.value / (tms.value * 1e-3) / 1e12 if tms.value > 0 else None
+    roof = {"bound": "tensor" if cls == 0 else "fp32 pipe", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+            "frac": (ach / peak) if (ach and peak) else None, "traffic": None, "launches": int(n.value),
+            "share_of_step": tms.value / (ms * args.steps) if ms > 0 else None,
+            "note": "small GEMMs that do not fit the tensor-core kernel's alignment run on the FP32 kernel (class 1)"}
+
+    # CPU port: full step where that takes seconds, a row slice scaled by rows for the 8192^3 layer
+    ora = entry.load_oracle()
+    rows = batch if args.config != "c3" else 64
+    st = ora.MlpState(ws, bs)
+    kind = {"sum": ora.LOSS_SUM, "mean": ora.LOSS_MEAN, "mse": ora.LOSS_MSE}[loss_kind]
+    t0 = time.perf_counter()
+    ora.mlp_step(st, x[:rows], None if t is None else t[:rows], loss_kind=kind, relu_last=relu_last, do_adam=False,
+                 want_gx=x_grad, as_written=True)
+    t_rows = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for l_ in range(L):
+        ora.adam_update(st.w[l_].reshape(-1), st.gw[l_].reshape(-1), st.mw[l_].reshape(-1), st.vw[l_].reshape(-1), 1)
+        ora.adam_update(st.b[l_], st.gb[l_], st.mb[l_], st.vb[l_], 1)
+    t_adam = time.perf_counter() - t0
+    cpu_s = t_rows * (batch / rows) + t_adam
+    line = {"metric": f"fwd+bwd+Adam steps/s ({args.config.upper()})", "value": 1000.0 / ms, "unit": "steps/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "none",
+            "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
+            "config": {"workload": desc, "gemm_precision": args.precision, "seed": seed},
+            "tflops": flop / (ms * 1e-3) / 1e12, "loss": loss.value(), "roofline": roof,
+            "e2e": {"value": 1000.0 / e2e_ms, "unit": "steps/s", "h2d_bytes_per_step": 4 * (x.size + (t.size if t is not None else 0)),
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "launches_per_step": launches / args.steps, "clocks": clocks,
+            "cpu_baseline": {"value": 1.0 / cpu_s, "unit": "steps/s", "cores": 1, "kind": "port",
+                             "sample": f"{rows} of {batch} rows fwd+bwd ({t_rows:.2f} s" + (", scaled by rows" if rows != batch else "")
+                                       + f") + Adam ({t_adam:.3f} s)"}}
+    print(json.dumps(line), flush=True)
+
+
+def run_c2(args):
+    """C2: add/sub/mul/div of two f32 tensors (a ~ N(0,1), b ~ U[0.5,2)), loss = sum(out), backward to both operands.
+    Reports achieved GB/s of the whole forward+backward sequence per op and size against its algorithmic bytes."""
+    ts = entry.load_package()
+    lib = ts._ffi.lib()
+    ts.set_default_device(0)
+    peaks = measured_peaks()
+    rng = np.random.default_rng(1)
+    out = []
+    for logn in (20, 24, 28):
+        n = 1 << logn
+        a = ts.Tensor.from_slice(rng.standard_normal(n, dtype=np.float32), [n]).with_requires_grad()
+        b = ts.Tensor.from_slice((rng.random(n, dtype=np.float32) * 1.5 + 0.5).astype(np.float32), [n]).with_requires_grad()
+        for op, bwd_bytes in (("add", 0), ("sub", 8), ("mul", 20), ("div", 20)):
+            # forward 12 B/elem, sum 4, seed fill 4 (written once, then read by the op's backward where it has one)
+            algo = (12 + 4 + 4 + bwd_bytes) * n
+
+            def once():
+                o = getattr(a, f"{op}_tensor")(b)
+                o.sum().backward(None)
+                ts.clear_gradients()
+            for _ in range(args.warmup):
+                once()
+            ts.synchronize()
+            ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
+            lib.ts_event_record(ev0, None)
+            for _ in range(args.steps):
+                once()
+            lib.ts_event_record(ev1, None)
+            ts.synchronize()
+            ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps
+            out.append({"op": op, "n": n, "ms": ms, "GBps": algo / (ms * 1e-3) / 1e9, "frac_of_hbm": algo / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+        del a, b
+        ts.release_cached_memory()
+    big = [r for r in out if r["n"] == 1 << 28]
+    print(json.dumps({"metric": "elementwise fwd+bwd HBM GB/s (C2)", "value": float(np.mean([r["GBps"] for r in big])), "unit": "GB/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "C2 elementwise sweep 2^20/2^24/2^28, out = op(a,b), loss = sum(out), backward; seed 1",
+                                 "bytes": "algorithmic: forward 12 B/elem, sum 4, seed fill 4, backward 0 (add: gradients alias), 8 (sub), 20 (mul, div)"},
+                      "roofline": {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "peak_source": peaks["source"]},
+                      "results": out}), flush=True)
 
 
 # ------------------------------------------------------------------------ single-kernel cases
@@ -439,11 +611,19 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32", "tf32x3"])
+    ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="BASELINE configuration; c5 (default) is the headline data-parallel MLP, the others run on one GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.micro:
         run_micro(args)
+        return
+    if args.config == "c2":
+        run_c2(args)
+        return
+    if args.config in CONFIGS:
+        run_config(args)
         return
     d = Dist(args.gpus)
     try:

@@ -289,6 +289,37 @@ def test_async_upload_overlaps_and_is_ordered(gpu, ora):
     assert_bit_equal(t.add_tensor(t).data(), ora.add(a, a))
 
 
+def test_host_running_ahead_of_the_gpu_changes_nothing(gpu):
+    """Every call only enqueues work, so the host may be many steps ahead of the GPU.  Whatever a queued launch
+    needs (the Adam pointer table in particular) must be captured when it is enqueued: a run that synchronises
+    after every step and a run that never does must end with identical bits, also when gradient buffers change
+    address from step to step."""
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((8192, 2048), dtype=np.float32)
+    w0 = (rng.standard_normal((2048, 2048)) / np.sqrt(2048)).astype(np.float32)
+
+    def run(sync_each_step):
+        gpu.clear_gradients()
+        X = gpu.Tensor.from_slice(x, x.shape)
+        W = gpu.Tensor.from_slice(w0, w0.shape).with_requires_grad()
+        opt = gpu.Adam.with_learning_rate(1e-3)
+        opt.add_parameter(W)
+        held = None
+        for s in range(10):
+            if s % 2:
+                held = gpu.Tensor.new(w0.shape)     # occupies the block the last gradient used: the next one lands elsewhere
+            X.matmul(W).relu().sum().backward(None)
+            opt.step([W])
+            opt.zero_grad([W])
+            if s % 2 == 0:
+                held = None
+            if sync_each_step:
+                gpu.synchronize()
+        return W.data()
+
+    assert_bit_equal(run(False), run(True), "weights after 10 steps")
+
+
 def test_storage_is_recycled_across_steps(gpu):
     rng = np.random.default_rng(0)
     ws, bs, x = _config1(rng)

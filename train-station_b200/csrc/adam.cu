@@ -40,10 +40,16 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
     p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, mh), __fadd_rn(__fsqrt_rn(vh), sc.eps)));
 }
 
-__global__ void __launch_bounds__(kThreads) adam_kernel(const AdamTensor* __restrict__ tensors, const ChunkEntry* __restrict__ chunks,
-                                                        Scalars sc) {
-    const ChunkEntry ce = chunks[blockIdx.x];
-    const AdamTensor t = tensors[ce.tensor];
+// The tensor table travels in the kernel's parameters: the pointers are captured when the launch is
+// enqueued, so a host that runs steps ahead of the GPU cannot overwrite a table that a queued launch
+// has yet to read (a table staged in reused pinned memory did exactly that).
+constexpr int kMaxTensorsPerLaunch = 48;
+struct AdamTable { AdamTensor t[kMaxTensorsPerLaunch]; };
+
+__global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ AdamTable tab, const ChunkEntry* __restrict__ chunks,
+                                                        int chunk_base, int tensor_base, Scalars sc) {
+    const ChunkEntry ce = chunks[chunk_base + blockIdx.x];
+    const AdamTensor t = tab.t[ce.tensor - tensor_base];
     const unsigned long long body = t.n / 8 * 8;
     unsigned long long end = ce.offset + kChunk;
     if (end > t.n) end = t.n;
@@ -109,13 +115,31 @@ void adam_build_chunks(const unsigned long long* sizes, int n, void* host_out) {
         for (unsigned long long off = 0; off < sizes[i]; off += kChunk) ce[c++] = ChunkEntry{i, 0, off};
 }
 
-bool adam_launch(const AdamTensor* tensors_dev, const void* chunks_dev, int n_chunks, double total_elems, float lr, float beta1,
-                 float beta2, float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s) {
-    if (n_chunks == 0) return true;
+// tensors: HOST array of n records; chunks_dev: device chunk map built by adam_build_chunks for the same sizes.
+// One launch per 48 tensors (a single launch for any MLP of the path).
+bool adam_launch(const AdamTensor* tensors, int n, const void* chunks_dev, float lr, float beta1, float beta2, float eps, float wd,
+                 float f1, float f2, float grad_scale, cudaStream_t s) {
     Scalars sc{lr, beta1, beta2, eps, wd, f1, f2, grad_scale, 1.0f - beta1, 1.0f - beta2};
-    ProfScope prof(kProfAdam, s, 28.0 * total_elems);
-    adam_kernel<<<n_chunks, kThreads, 0, s>>>(tensors_dev, (const ChunkEntry*)chunks_dev, sc);
-    return cuda_ok(cudaGetLastError(), "adam launch");
+    int chunk_base = 0;
+    for (int t0 = 0; t0 < n; t0 += kMaxTensorsPerLaunch) {
+        const int cnt = n - t0 < kMaxTensorsPerLaunch ? n - t0 : kMaxTensorsPerLaunch;
+        AdamTable tab;
+        memset(&tab, 0, sizeof(tab));
+        int n_chunks = 0;
+        double elems = 0;
+        for (int i = 0; i < cnt; ++i) {
+            tab.t[i] = tensors[t0 + i];
+            n_chunks += (int)((tensors[t0 + i].n + kChunk - 1) / kChunk);
+            elems += (double)tensors[t0 + i].n;
+        }
+        if (n_chunks > 0) {
+            ProfScope prof(kProfAdam, s, 28.0 * elems);
+            adam_kernel<<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
+            if (!cuda_ok(cudaGetLastError(), "adam launch")) return false;
+        }
+        chunk_base += n_chunks;
+    }
+    return true;
 }
 
 }  // namespace k
@@ -139,19 +163,15 @@ TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* c
     }
     std::vector<unsigned long long> sz(sizes, sizes + n_tensors);
     int n_chunks = k::adam_chunk_count(sz.data(), n_tensors);
-    size_t tbytes = (((size_t)n_tensors * sizeof(k::AdamTensor)) + 255) & ~size_t(255);
-    size_t bytes = tbytes + k::adam_chunk_bytes(n_chunks);
+    if (n_chunks == 0) return true;
+    size_t bytes = k::adam_chunk_bytes(n_chunks);
     std::vector<char> host(bytes);
-    memcpy(host.data(), t.data(), (size_t)n_tensors * sizeof(k::AdamTensor));
-    k::adam_build_chunks(sz.data(), n_tensors, host.data() + tbytes);
+    k::adam_build_chunks(sz.data(), n_tensors, host.data());
     float* dev = c->alloc.alloc(bytes);
     if (!dev) return false;
-    bool ok = cuda_ok(cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, s), "adam table upload");
-    // a pageable source has been staged by the time cudaMemcpyAsync returns
-    double total = 0;
-    for (int i = 0; i < n_tensors; ++i) total += (double)sizes[i];
-    ok = ok && k::adam_launch((const k::AdamTensor*)dev, (const char*)dev + tbytes, n_chunks, total, lr, beta1, beta2, eps,
-                              weight_decay, f1, f2, grad_scale, s);
+    // the pageable source is staged before cudaMemcpyAsync returns, so `host` may go out of scope
+    bool ok = cuda_ok(cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, s), "adam chunk map upload");
+    ok = ok && k::adam_launch(t.data(), n_tensors, dev, lr, beta1, beta2, eps, weight_decay, f1, f2, grad_scale, s);
     // Freed blocks are only reused by later work, which is ordered after this kernel when it runs on
     // the compute stream; a caller-supplied stream is drained first.
     if (s != c->compute) cudaStreamSynchronize(s);

@@ -46,7 +46,8 @@ struct Storage {
     float* tf32_lo = nullptr;          // 3xTF32 mode: rn_tf32(data - tf32_copy)
     uint64_t tf32_lo_version = 0;
     ~Storage() {
-        if (ready) cudaEventDestroy(ready);
+        // an upload nobody waited for must land before the block goes back to the allocator
+        if (ready) { cudaEventSynchronize(ready); cudaEventDestroy(ready); }
         if (c && tf32_copy) c->alloc.free(tf32_copy);
         if (c && tf32_lo) c->alloc.free(tf32_lo);
         if (c && ptr) c->alloc.free(ptr);
@@ -613,9 +614,6 @@ struct ts_adam {
     std::vector<unsigned long long> cached_sizes;
     float* chunks_dev = nullptr;
     int n_chunks = 0;
-    float* tensors_dev = nullptr;
-    ts::k::AdamTensor* tensors_host = nullptr;   // pinned
-    size_t tensors_cap = 0;
     ts::DeviceCtx* c = nullptr;
 };
 
@@ -922,11 +920,7 @@ TS_API ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float
 }
 TS_API void ts_adam_free(ts_adam* o) {
     if (!o) return;
-    if (o->c) {
-        o->c->alloc.free(o->chunks_dev);
-        o->c->alloc.free(o->tensors_dev);
-    }
-    if (o->tensors_host) cudaFreeHost(o->tensors_host);
+    if (o->c) o->c->alloc.free(o->chunks_dev);
     delete o;
 }
 TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
@@ -990,27 +984,15 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
             o->n_chunks = nc;
             o->cached_sizes = sizes;
         }
-        if (tab.size() > o->tensors_cap) {
-            if (o->tensors_host) cudaFreeHost(o->tensors_host);
-            c->alloc.free(o->tensors_dev);
-            o->tensors_cap = tab.size() + 8;
-            TS_CHECK(cudaMallocHost(&o->tensors_host, 2 * o->tensors_cap * sizeof(k::AdamTensor)));
-            o->tensors_dev = c->alloc.alloc(o->tensors_cap * sizeof(k::AdamTensor));
-            if (!o->tensors_dev) return false;
-        }
-        // Two pinned slots used alternately: the copy of step t may still be in flight when step t+1 fills its table.
-        k::AdamTensor* slot = o->tensors_host + (o->step_count & 1) * o->tensors_cap;
-        memcpy(slot, tab.data(), tab.size() * sizeof(k::AdamTensor));
-        TS_CHECK(cudaMemcpyAsync(o->tensors_dev, slot, tab.size() * sizeof(k::AdamTensor), cudaMemcpyHostToDevice, c->compute));
+        // The pointer table goes to the kernel by value: the host may be several steps ahead of the GPU, and a
+        // table staged in reused host memory would be overwritten before the queued copy reads it.
         // bias corrections in f64 from the f32-rounded betas, then to f32: adam/mod.rs:526-531, :793
         const float stepf = (float)o->step_count;
         const float bc1 = (float)(1.0 - std::pow((double)o->beta1, (double)stepf));
         const float bc2 = (float)(1.0 - std::pow((double)o->beta2, (double)stepf));
         const float f1 = 1.0f / bc1, f2 = 1.0f / bc2;
-        double total = 0;
-        for (unsigned long long sz : sizes) total += (double)sz;
-        if (!k::adam_launch((const k::AdamTensor*)o->tensors_dev, o->chunks_dev, o->n_chunks, total, o->lr, o->beta1, o->beta2, o->eps,
-                            o->wd, f1, f2, grad_scale, c->compute))
+        if (!k::adam_launch(tab.data(), (int)tab.size(), o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
+                            c->compute))
             return false;
         for (auto& s : touched) { s->version++; s->tf32_clean = false; }
     }
