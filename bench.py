@@ -194,7 +194,8 @@ def run_reference(args, d: Dist):
     line = {"metric": METRIC, "value": v, "unit": "steps/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1000.0 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": "C5 data-parallel wide MLP 4096-8192-8192-4096, global batch 65536, MSE, Adam",
+            "config": {"workload": "C5 data-parallel wide MLP 4096-8192-8192-4096 f32, Kaiming-uniform init, ReLU, MSE, Adam(1e-3)",
+                       "global_batch": GLOBAL_BATCH, "seed": SEED,
                        "note": "the reference is single-threaded CPU code with no multi-device path; timed on one host core"},
             "cpu_baseline": base, "e2e": {"value": v, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -294,6 +295,12 @@ def run_gpu(args, d: Dist):
             "share_of_step": gms / ms if ms > 0 else None}
     if roof["achieved"]:
         roof["frac"] = roof["achieved"] / roof["peak"]
+    if cls == 0 and gl:
+        # DRAM bytes per launch.  Measured with ncu on the 8192^3 case of the same kernel (dram__bytes_read + write =
+        # 3.04 GB for 1.0995e12 flop, profiles/gemm_tf32_tcgen05_8192cubed.md); the bench's GEMMs are too large to capture
+        # under the size rule, so the figure is scaled by flop, which assumes the same L2 hit rate (73 %).
+        roof["traffic"] = 3.04e9 / 1.0995e12 * (gwork / gl)
+        roof["traffic_note"] = "ncu on the 8192^3 case, scaled by flop per launch; algorithmic bytes per launch are operands + result once"
     al, ams, awork = prof(4)
     el, ems, ework = prof(2)
     rl, rms, rwork = prof(3)

@@ -173,8 +173,10 @@ bool launch_colsum_kernel(const float* g, float* out, unsigned long long rows, u
  * synchronise the whole device) has no scratch buffer to hand to launch_colsum_kernel; this variant
  * keeps the partial sums in a 512 KiB array built into the library (held on every GPU that loads the
  * library, until the process exits) and itself calls no allocation routine of any kind.
- *   - Limit: the row splits times `cols` must fit 131,072 elements (for example 65536 x 8192 needs
- *     81,920); larger problems are refused with a message in ts_last_error().
+ *   - Limit: the row splits times `cols` must fit 131,072 elements (65536 x 8192 needs 73,728; the
+ *     kernel plans at most four CTAs per SM, so a 148-SM B200 never needs more than 75,776 and the
+ *     limit only bites on devices with more SMs); a problem that does not fit is refused with a
+ *     message in ts_last_error().
  *   - The library must already be initialised on the current device (cuda_ffi_initialize() allocates
  *     and therefore is not done here); otherwise the call fails with a message.
  *   - The first call on each device looks up the device address of the built-in array; make that
