@@ -76,18 +76,30 @@ class ClockSampler:
 
     def __init__(self, device: int):
         self.device, self.proc, self.path = device, None, None
+        self.t_begin = self.t_end = None
 
     def start(self):
+        """Started before the warm-up (nvidia-smi needs a few hundred ms to come up); the samples used are those whose
+        timestamps fall between mark_begin() and mark_end(), i.e. inside the timed region."""
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.device)], stdout=f, stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu=timestamp,{self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "20", "-i", str(self.device)], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        import datetime
+        self.t_begin = datetime.datetime.now()
+
+    def mark_end(self):
+        import datetime
+        self.t_end = datetime.datetime.now()
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": None}
         if not self.proc:
             return out
         self.proc.terminate()   # the exact process started above
@@ -95,24 +107,27 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         try:
             for line in open(self.path):
                 c = [x.strip() for x in line.split(",")]
-                if len(c) < 9:
+                if len(c) < 10:
                     continue
                 try:
-                    sm.append(float(c[1])); mx.append(float(c[2]))
+                    when = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f")
+                    rows.append((when, float(c[2]), float(c[3]), [v.lower() == "active" for v in c[6:10]]))
                 except ValueError:
                     continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
-                    if v.lower() == "active":
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        inside = [r for r in rows if self.t_begin and self.t_end and self.t_begin <= r[0] <= self.t_end]
+        use, out["window"] = (inside, "timed region") if inside else (rows[-25:], "last samples before the end of the timed region")
+        if use:
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            reasons = sorted({n for r in use for n, a in zip(names, r[3]) if a})
+            out.update(sm_mhz=float(np.median([r[1] for r in use])), sm_max_mhz=float(max(r[2] for r in use)),
+                       reasons=reasons, samples=len(use))
         return out
 
 
@@ -251,6 +266,8 @@ def run_gpu(args, d: Dist):
     X = ts.Tensor.from_pinned_async(pins_x[0], [local, DIMS[0]])
     T = ts.Tensor.from_pinned_async(pins_t[0], [local, DIMS[-1]])
 
+    sampler = ClockSampler(d.local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         loss = step(X, T)
     ts.synchronize()
@@ -259,15 +276,15 @@ def run_gpu(args, d: Dist):
     ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
     lib.ts_profile_reset()
     lib.ts_profile_enable(1)
-    sampler = ClockSampler(d.local_rank)
     d.barrier(); ts.synchronize()
-    sampler.start()
+    sampler.mark_begin()
     launches0 = int(lib.ts_launch_count())
     lib.ts_event_record(ev0, None)
     for _ in range(args.steps):
         loss = step(X, T)
     lib.ts_event_record(ev1, None)
     ts.synchronize(); d.barrier()
+    sampler.mark_end()
     ms = float(lib.ts_event_elapsed_ms(ev0, ev1))
     launches = int(lib.ts_launch_count()) - launches0
     clocks = sampler.stop()
@@ -316,6 +333,7 @@ def run_gpu(args, d: Dist):
     d.barrier(); ts.synchronize()
     nxt = (ts.Tensor.from_pinned_async(pins_x[1], [local, DIMS[0]]), ts.Tensor.from_pinned_async(pins_t[1], [local, DIMS[-1]]))
     t0 = time.perf_counter()
+    prev = None
     lib.ts_event_record(ev0, None)
     for s in range(args.steps):
         cur = nxt
@@ -324,7 +342,12 @@ def run_gpu(args, d: Dist):
             nxt = (ts.Tensor.from_pinned_async(pins_x[slot], [local, DIMS[0]]),
                    ts.Tensor.from_pinned_async(pins_t[slot], [local, DIMS[-1]]))
         l = step(*cur)
-        _ = l.value()       # device -> host read of the step's result
+        # device -> host read of every step's loss, one step behind: the next step is already queued while the host
+        # waits for this value, so the GPU never idles on the read-back
+        if prev is not None:
+            _ = prev.value()
+        prev = l
+    _ = prev.value()
     lib.ts_event_record(ev1, None)
     ts.synchronize(); d.barrier()
     e2e_ms = d.max(float(lib.ts_event_elapsed_ms(ev0, ev1)))
@@ -410,18 +433,20 @@ def run_config(args):
         return loss
 
     X, T = upload()
+    sampler = ClockSampler(0); sampler.start()
     for _ in range(args.warmup):
         loss = step(X, T)
     ts.synchronize()
     ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
     lib.ts_profile_reset(); lib.ts_profile_enable(1)
-    sampler = ClockSampler(0); sampler.start()
+    sampler.mark_begin()
     launches0 = int(lib.ts_launch_count())
     lib.ts_event_record(ev0, None)
     for _ in range(args.steps):
         loss = step(X, T)
     lib.ts_event_record(ev1, None)
     ts.synchronize()
+    sampler.mark_end()
     ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps
     launches = int(lib.ts_launch_count()) - launches0
     clocks = sampler.stop()
