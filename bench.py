@@ -453,9 +453,13 @@ def run_config(args):
     lib.ts_profile_enable(0)
     ts._ffi.check(lib.ts_profile_collect(), "profile")
     lib.ts_event_record(ev0, None)
+    prev = None
     for _ in range(args.steps):
         l = step(*upload())
-        _ = l.value()
+        if prev is not None:
+            _ = prev.value()     # every step's loss is read back, one step behind the queue
+        prev = l
+    _ = prev.value()
     lib.ts_event_record(ev1, None)
     ts.synchronize()
     e2e_ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / args.steps

@@ -149,6 +149,79 @@ void launch(const GemmArgs& g, dim3 grid, cudaStream_t s) {
     else sgemm_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
 }
 
+// The same arithmetic on 32 x 32 tiles (2 x 2 outputs per thread, 32 k per stage) for results that would fill only a
+// few 128 x 128 tiles: a [1024 x 10] bias-layer weight gradient reduced over 4096 rows is 8 CTAs of the big kernel,
+// each walking all of K alone, but 32 CTAs here.  Per output element the chain over p is unchanged.
+constexpr int SM_T = 32;
+
+template <bool TA, bool TB, bool HAS_TAIL>
+__global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
+    __shared__ float As[SM_T][SM_T + 1];   // [k][m]
+    __shared__ float Bs[SM_T][SM_T + 1];   // [k][n]
+    const int t = threadIdx.x, ty = t / 16, tx = t % 16;
+    const size_t m0 = (size_t)blockIdx.y * SM_T, n0 = (size_t)blockIdx.x * SM_T;
+    const size_t M = g.m, N = g.n, K = g.k;
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    bool tailc[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) tailc[j] = HAS_TAIL && (n0 + tx * 2 + j) >= N / 8 * 8;
+
+    for (size_t k0 = 0; k0 < K; k0 += SM_T) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int e = t + kThreads * q, lo = e % SM_T, hi = e / SM_T;
+            {   // A: stored [K][M] (TA, contiguous along m) or [M][K] (contiguous along k)
+                const int kk = TA ? hi : lo, mm = TA ? lo : hi;
+                const size_t p = k0 + kk, i = m0 + mm;
+                As[kk][mm] = (p < K && i < M) ? (TA ? g.a[p * M + i] : g.a[i * K + p]) : 0.0f;
+            }
+            {   // B: stored [N][K] (TB, contiguous along k) or [K][N] (contiguous along n)
+                const int kk = TB ? lo : hi, nn = TB ? hi : lo;
+                const size_t p = k0 + kk, j = n0 + nn;
+                Bs[kk][nn] = (p < K && j < N) ? (TB ? g.b[j * K + p] : g.b[p * N + j]) : 0.0f;
+            }
+        }
+        __syncthreads();
+        const int pmax = (K - k0) < (size_t)SM_T ? (int)(K - k0) : SM_T;   // no padded terms enter the chain
+        for (int p = 0; p < pmax; ++p) {
+            const float a0 = As[p][ty * 2], a1 = As[p][ty * 2 + 1];
+            const float b[2] = {Bs[p][tx * 2], Bs[p][tx * 2 + 1]};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (HAS_TAIL && tailc[j]) {
+                    acc[0][j] = __fadd_rn(acc[0][j], __fmul_rn(a0, b[j]));
+                    acc[1][j] = __fadd_rn(acc[1][j], __fmul_rn(a1, b[j]));
+                } else {
+                    acc[0][j] = fmaf(a0, b[j], acc[0][j]);
+                    acc[1][j] = fmaf(a1, b[j], acc[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const size_t row = m0 + ty * 2 + i;
+        if (row >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const size_t col = n0 + tx * 2 + j;
+            if (col >= N) continue;
+            float v = acc[i][j];
+            if (g.bias) v = __fadd_rn(v, __ldg(g.bias + col));
+            if (g.relu) v = v > 0.0f ? v : 0.0f;
+            if (g.mask) v = g.mask[row * N + col] > 0.0f ? v : 0.0f;
+            g.c[row * N + col] = v;
+        }
+    }
+}
+
+template <bool TA, bool TB>
+void launch_small(const GemmArgs& g, dim3 grid, cudaStream_t s) {
+    if (g.n % 8 != 0) sgemm_small_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
+    else sgemm_small_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+}
+
 }  // namespace
 
 bool sgemm(const GemmArgs& g, cudaStream_t s) {
@@ -161,6 +234,15 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
     if (gy > 65535) { set_error("gemm: m = %zu too large for the FP32 kernel's grid", g.m); return false; }
     dim3 grid((unsigned)gx, (unsigned)gy);
     ProfScope prof(kProfGemmFp32, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
+    DeviceCtx* c = ctx();
+    const size_t sgy = (g.m + SM_T - 1) / SM_T;
+    if (c && gx * gy < (size_t)c->sm_count / 2 && sgy <= 65535) {
+        // too few 128 x 128 tiles to occupy the GPU: 32 x 32 tiles, sixteen times as many CTAs
+        dim3 sgrid((unsigned)((g.n + SM_T - 1) / SM_T), (unsigned)sgy);
+        if (g.trans_a) { if (g.trans_b) launch_small<true, true>(g, sgrid, s); else launch_small<true, false>(g, sgrid, s); }
+        else { if (g.trans_b) launch_small<false, true>(g, sgrid, s); else launch_small<false, false>(g, sgrid, s); }
+        return cuda_ok(cudaGetLastError(), "sgemm (small tiles) launch");
+    }
     if (g.trans_a) { if (g.trans_b) launch<true, true>(g, grid, s); else launch<true, false>(g, grid, s); }
     else { if (g.trans_b) launch<false, true>(g, grid, s); else launch<false, false>(g, grid, s); }
     return cuda_ok(cudaGetLastError(), "sgemm launch");
