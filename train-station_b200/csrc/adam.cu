@@ -119,9 +119,18 @@ void adam_build_chunks(const unsigned long long* sizes, int n, void* host_out) {
 // One launch per 48 tensors (a single launch for any MLP of the path).
 bool adam_launch(const AdamTensor* tensors, int n, const void* chunks_dev, float lr, float beta1, float beta2, float eps, float wd,
                  float f1, float f2, float grad_scale, cudaStream_t s) {
+    return adam_launch_range(tensors, 0, n, chunks_dev, lr, beta1, beta2, eps, wd, f1, f2, grad_scale, s);
+}
+
+// Updates tensors [first, last) of the table only; chunks_dev is still the map of the WHOLE table, so the range's
+// chunks start after those of the tensors before it.  Used to update each tensor as soon as its gradient is ready.
+bool adam_launch_range(const AdamTensor* tensors, int first, int last, const void* chunks_dev, float lr, float beta1, float beta2,
+                       float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s) {
     Scalars sc{lr, beta1, beta2, eps, wd, f1, f2, grad_scale, 1.0f - beta1, 1.0f - beta2};
     int chunk_base = 0;
-    for (int t0 = 0; t0 < n; t0 += kMaxTensorsPerLaunch) {
+    for (int i = 0; i < first; ++i) chunk_base += (int)((tensors[i].n + kChunk - 1) / kChunk);
+    const int n = last;
+    for (int t0 = first; t0 < n; t0 += kMaxTensorsPerLaunch) {
         const int cnt = n - t0 < kMaxTensorsPerLaunch ? n - t0 : kMaxTensorsPerLaunch;
         AdamTable tab;
         memset(&tab, 0, sizeof(tab));

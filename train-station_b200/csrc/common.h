@@ -117,6 +117,8 @@ struct AdamTensor {
 int adam_chunk_count(const unsigned long long* sizes, int n);
 size_t adam_chunk_bytes(int n_chunks);
 void adam_build_chunks(const unsigned long long* sizes, int n, void* host_out);
+bool adam_launch_range(const AdamTensor* tensors, int first, int last, const void* chunks_dev, float lr, float beta1, float beta2,
+                       float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s);
 // tensors is a HOST array: the records are passed to the kernel by value (captured at enqueue time).
 bool adam_launch(const AdamTensor* tensors, int n, const void* chunks_dev, float lr, float beta1, float beta2, float eps, float wd,
                  float f1, float f2, float grad_scale, cudaStream_t s);

@@ -277,10 +277,14 @@ struct DpState {
     std::unordered_set<uint64_t> params;
     cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
     bool comm_outstanding = false;
+    // per-parameter completion of the gradient all-reduce, so that Adam can update each tensor as soon as its
+    // own sum has landed instead of waiting for the last one
+    std::unordered_map<uint64_t, cudaEvent_t> done_event;
+    std::vector<uint64_t> pending_order;   // parameter ids in the order their all-reduces were enqueued
 };
 static thread_local DpState g_dp;
 
-static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n) {
+static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n, uint64_t param_id = 0) {
     if (!g_dp.comm || g_dp.world <= 1) return true;
     if (!g_dp.ev_compute) {
         TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_compute, cudaEventDisableTiming));
@@ -293,13 +297,21 @@ static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n) {
     ncclResult_t r = nc->AllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm);
     if (r != ncclSuccess) { set_error("ncclAllReduce failed: %s", nc->GetErrorString(r)); return false; }
     g_dp.comm_outstanding = true;
+    if (param_id) {
+        cudaEvent_t& ev = g_dp.done_event[param_id];
+        if (!ev) TS_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        TS_CHECK(cudaEventRecord(ev, c->comm));
+        g_dp.pending_order.push_back(param_id);
+    }
     return true;
 }
+// The compute stream waits for every all-reduce enqueued so far.
 static bool dp_join(DeviceCtx* c) {
     if (!g_dp.comm_outstanding) return true;
     TS_CHECK(cudaEventRecord(g_dp.ev_comm, c->comm));
     TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.ev_comm, 0));
     g_dp.comm_outstanding = false;
+    g_dp.pending_order.clear();
     return true;
 }
 
@@ -531,12 +543,13 @@ static bool finalize_leaf(DeviceCtx* c, uint64_t id, std::unordered_set<uint64_t
         lg = priv;
     }
     reduced.insert(id);
-    return dp_all_reduce_async(c, lg->st->ptr, lg->size);
+    return dp_all_reduce_async(c, lg->st->ptr, lg->size, id);
 }
 
 static bool backward(const TensorP& root, const TensorP& grad_output) {
     DeviceCtx* c = ctx();
     if (!c) return false;
+    if (g_dp.comm_outstanding && !dp_join(c)) return false;   // earlier gradients may be accumulated into below
     // seed: gradtrack/engine.rs:964-978
     TensorP seed = grad_output;
     if (!seed) {
@@ -597,7 +610,9 @@ static bool backward(const TensorP& root, const TensorP& grad_output) {
         for (uint64_t id : g_dp.params)
             if (!reduced.count(id) && g_graph.grads.count(id) && !finalize_leaf(c, id, reduced)) return false;
     g_graph.bias_grad_ready.clear();
-    return dp_join(c);   // the compute stream continues only after every all-reduce has landed
+    // The all-reduces may still be running on the communication stream.  Whoever reads a gradient next waits for
+    // them: grad_by_value() for all, Adam::step per parameter, so that early layers' sums overlap late layers' updates.
+    return true;
 }
 
 // ------------------------------------------------------------------ Adam
@@ -897,9 +912,17 @@ TS_API ts_tensor* ts_tensor_grad_by_value(const ts_tensor* t) {
     TensorP g = grad_lookup(t->t->id);
     if (!g) return nullptr;
     if (!materialize(g)) return nullptr;
+    if (g_dp.comm_outstanding) {   // a gradient handed to the caller must be the all-reduced one
+        DeviceCtx* c = ctx();
+        if (!c || !dp_join(c)) return nullptr;
+    }
     return wrap(reshaped_alias(g, t->t->dims));
 }
 TS_API void ts_clear_gradients(void) {
+    if (g_dp.comm_outstanding) {   // gradient buffers go back to the allocator below: no all-reduce may still write them
+        DeviceCtx* c = ctx();
+        if (c) dp_join(c);
+    }
     g_graph.ops.clear();
     g_graph.grads.clear();
     g_graph.bias_grad_ready.clear();
@@ -946,6 +969,7 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
     std::vector<k::AdamTensor> tab;
     std::vector<unsigned long long> sizes;
     std::vector<StorageP> touched;
+    std::vector<uint64_t> tab_ids;
     std::string skipped;
     for (int i = 0; i < n; ++i) {
         if (!params[i]) { set_error("adam step: null parameter at index %d", i); return false; }
@@ -968,8 +992,9 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size});
         sizes.push_back(p->size);
         touched.push_back(p->st);
+        tab_ids.push_back(p->id);
     }
-    if (!dp_join(c)) return false;   // gradient all-reduces must have landed
+    if (tab.empty() && !dp_join(c)) return false;
     if (!tab.empty()) {
         if (sizes != o->cached_sizes) {
             int nc = k::adam_chunk_count(sizes.data(), (int)sizes.size());
@@ -991,9 +1016,33 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         const float bc1 = (float)(1.0 - std::pow((double)o->beta1, (double)stepf));
         const float bc2 = (float)(1.0 - std::pow((double)o->beta2, (double)stepf));
         const float f1 = 1.0f / bc1, f2 = 1.0f / bc2;
-        if (!k::adam_launch(tab.data(), (int)tab.size(), o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
-                            c->compute))
-            return false;
+        if (g_dp.comm_outstanding && !g_dp.pending_order.empty()) {
+            // Data parallel: gradients are summed on the communication stream in the order backward produced them
+            // (last layer first).  Update each tensor as soon as its own sum has landed; the all-reduce of the first
+            // layer's gradient, which is enqueued last, then overlaps the updates of the other layers.
+            std::vector<char> launched(tab.size(), 0);
+            const std::vector<uint64_t> order = g_dp.pending_order;
+            for (uint64_t id : order) {
+                for (size_t i = 0; i < tab.size(); ++i) {
+                    if (tab_ids[i] != id || launched[i]) continue;
+                    TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.done_event[id], 0));
+                    if (!k::adam_launch_range(tab.data(), (int)i, (int)i + 1, o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd,
+                                              f1, f2, grad_scale, c->compute))
+                        return false;
+                    launched[i] = 1;
+                }
+            }
+            if (!dp_join(c)) return false;   // anything else that was outstanding
+            for (size_t i = 0; i < tab.size(); ++i)
+                if (!launched[i] && !k::adam_launch_range(tab.data(), (int)i, (int)i + 1, o->chunks_dev, o->lr, o->beta1, o->beta2,
+                                                          o->eps, o->wd, f1, f2, grad_scale, c->compute))
+                    return false;
+        } else {
+            if (!dp_join(c)) return false;
+            if (!k::adam_launch(tab.data(), (int)tab.size(), o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
+                                c->compute))
+                return false;
+        }
         for (auto& s : touched) { s->version++; s->tf32_clean = false; }
     }
     if (!skipped.empty()) {
@@ -1055,6 +1104,9 @@ TS_API void ts_dp_finalize(void) {
     if (c) { cudaStreamSynchronize(c->comm); cudaStreamSynchronize(c->compute); }
     if (g_dp.comm) { if (NcclApi* nc = nccl_api()) nc->CommDestroy(g_dp.comm); g_dp.comm = nullptr; }
     if (g_dp.ev_compute) { cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); g_dp.ev_compute = g_dp.ev_comm = nullptr; }
+    for (auto& kv : g_dp.done_event) cudaEventDestroy(kv.second);
+    g_dp.done_event.clear();
+    g_dp.pending_order.clear();
     g_dp.params.clear();
     g_dp.rank = 0; g_dp.world = 1; g_dp.comm_outstanding = false;
 }
