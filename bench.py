@@ -553,7 +553,8 @@ def run_c2(args):
 
 # ------------------------------------------------------------------------ single-kernel cases
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
-               "colsum", "sum")
+               "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
+               "softmax_inner")
 
 
 def run_micro(args):
@@ -579,6 +580,35 @@ def run_micro(args):
         return p
 
     name, n = args.micro, args.micro_size
+    if name == "library_tf32":
+        # Yardstick, not the product path: the vendor library's TF32 GEMM on the same 8192^3 case, timed the same way,
+        # as a measured stand-in for the TF32 tensor-pipe peak (the driver-written peaks file holds bf16 only).
+        import torch
+        m = n or 8192
+        torch.backends.cuda.matmul.allow_tf32 = True
+        a = torch.randn(m, m, device="cuda:0")
+        b = torch.randn(m, m, device="cuda:0")
+        c = torch.empty(m, m, device="cuda:0")
+        for _ in range(args.warmup):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = float("inf")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(args.steps):      # burst: best single launch
+            e0.record(); torch.matmul(a, b, out=c); e1.record(); torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(args.steps, 200)      # sustained: back to back for a few seconds
+        e0.record()
+        for _ in range(reps):
+            torch.matmul(a, b, out=c)
+        e1.record(); torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / reps
+        flop = 2.0 * m * m * m
+        print(json.dumps({"micro": name, "size": m, "library": "torch.matmul f32 with allow_tf32 (cuBLAS)",
+                          "burst_tflops": flop / (best * 1e-3) / 1e12, "sustained_tflops": flop / (sustained_ms * 1e-3) / 1e12,
+                          "sustained_launches": reps, "derived_peak_burst": peaks["bf16_burst"] / 2.0,
+                          "derived_peak_sustained": peaks["bf16_sustained"] / 2.0}), flush=True)
+        return
     if name.startswith("gemm"):
         m = nn = k = n or 8192
         a, b, c = dev(rng.standard_normal((m, k), dtype=np.float32)), dev(rng.standard_normal((k, nn), dtype=np.float32)), empty(m * nn)
@@ -607,6 +637,25 @@ def run_micro(args):
             launch = lambda: chk(lib.launch_mul_backward_kernel(x, y, g, o1, o2, n, None), name)
             work = 20.0 * n
         unit, peak = "GB/s", peaks["hbm_gbs"]
+    elif name in ("exp", "tanh", "sigmoid", "sigmoid_backward"):
+        n = n or (1 << 26)
+        x, g, o1 = dev(rng.standard_normal(n, dtype=np.float32)), dev(rng.standard_normal(n, dtype=np.float32)), empty(n)
+        code = {"exp": 0, "tanh": 3, "sigmoid": 4, "sigmoid_backward": 4}[name]     # enum ts_unary_op
+        if name.endswith("backward"):
+            launch = lambda: chk(lib.launch_unary_backward_kernel(code, x, g, o1, n, 0.0, None), name)
+            work = 12.0 * n
+        else:
+            launch = lambda: chk(lib.launch_unary_kernel(code, x, o1, n, 0.0, None), name)
+            work = 8.0 * n
+        unit, peak = "GB/s", peaks["hbm_gbs"]
+    elif name in ("softmax_rows", "softmax_classes", "softmax_inner"):
+        # long rows (one warp per row), 10-class rows (one thread per row), and a middle axis (one thread per line)
+        outer, reduce, inner = {"softmax_rows": (16384, 4096, 1), "softmax_classes": (1 << 22, 10, 1),
+                                "softmax_inner": (64, 256, 4096)}[name]
+        n = outer * reduce * inner
+        x, o1 = dev(rng.standard_normal(n, dtype=np.float32)), empty(n)
+        launch = lambda: chk(lib.launch_softmax_kernel(x, o1, outer, reduce, inner, None), name)
+        work, unit, peak = 8.0 * n, "GB/s", peaks["hbm_gbs"]
     elif name in ("colsum", "relu_backward_colsum"):
         rows, cols = (n or 16384), 8192
         g, ref = dev(rng.standard_normal((rows, cols), dtype=np.float32)), dev(rng.standard_normal((rows, cols), dtype=np.float32))

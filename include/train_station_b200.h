@@ -156,6 +156,34 @@ bool launch_fill_kernel(float* out, float value, unsigned long long size, void* 
  * (grad_fn/reductions/sum.rs:4-16, mean.rs:4-30: scale = 1 or 1/numel as f32). */
 bool launch_fill_from_scalar_kernel(float* out, const float* scalar, float scale,
                                     unsigned long long size, void* stream);
+/* Unary and scalar elementwise ops next to the MLP path, forward and backward, one launcher each.
+ *   forward:  out = f(x [, param])
+ *   backward: grad_in = grad_out * f'(saved [, param]); `saved` is what the reference's GradFn keeps:
+ *             the op's OUTPUT for exp, sqrt, tanh, sigmoid; its INPUT for log, leaky_relu, pow_scalar;
+ *             ignored (may be NULL) for the four scalar ops.
+ * Reference: tensor/ops/{exp.rs:148-163, log.rs:68-107, sqrt.rs:136-280, tanh.rs:174-190, sigmoid.rs:90-110,
+ * leaky_relu.rs:124-330 (param = negative slope), add.rs:450 ff., sub.rs:504 ff., mul.rs:495 ff., div.rs:511-575
+ * (param = the scalar), pow.rs:125-160 (param = exponent; 2 -> x*x, 0.5 -> sqrt, else powf)} and
+ * gradtrack/grad_fn/ops/{exp,log,sqrt,tanh,sigmoid,leaky_relu,pow,add,sub,mul,div}.rs.
+ * Where the reference panics: a zero divisor scalar makes the call return false before any launch;
+ * log of x <= 0 (or NaN) still stores the IEEE result and raises the device error word
+ * TS_DEVICE_ERROR_LOG_DOMAIN, which the next ts_sync_stream reports as a failure. */
+enum ts_unary_op {
+    TS_UNARY_EXP = 0, TS_UNARY_LOG = 1, TS_UNARY_SQRT = 2, TS_UNARY_TANH = 3, TS_UNARY_SIGMOID = 4,
+    TS_UNARY_LEAKY_RELU = 5, TS_UNARY_ADD_SCALAR = 6, TS_UNARY_SUB_SCALAR = 7, TS_UNARY_MUL_SCALAR = 8,
+    TS_UNARY_DIV_SCALAR = 9, TS_UNARY_POW_SCALAR = 10
+};
+#define TS_DEVICE_ERROR_LOG_DOMAIN 100
+bool launch_unary_kernel(int op, const float* x, float* out, unsigned long long size, float param, void* stream);
+bool launch_unary_backward_kernel(int op, const float* saved, const float* grad_out, float* grad_in,
+                                  unsigned long long size, float param, void* stream);
+/* softmax over the middle axis of a contiguous [outer, reduce, inner] tensor (tensor/ops/softmax.rs:110-158:
+ * subtract the maximum, exponentiate, multiply by the reciprocal of the sum) and its backward
+ * (grad_fn/ops/softmax.rs:4-35: grad_in = y * (grad_out - sum_j grad_out*y)). */
+bool launch_softmax_kernel(const float* x, float* out, unsigned long long outer, unsigned long long reduce,
+                           unsigned long long inner, void* stream);
+bool launch_softmax_backward_kernel(const float* y, const float* grad_out, float* grad_in, unsigned long long outer,
+                                    unsigned long long reduce, unsigned long long inner, void* stream);
 /* reductions/sum.rs:80-143 and mean.rs:48-110: out[0] = sum(x) or sum(x)/(f32)size.
  * Deterministic two-level tree (the reference adds sequentially).  `scratch` needs
  * ts_reduce_scratch_elems() f32 elements of device memory. */
@@ -257,7 +285,24 @@ ts_tensor* ts_tensor_sub_tensor(ts_tensor* a, ts_tensor* b);   /* sub.rs:121-160
 ts_tensor* ts_tensor_mul_tensor(ts_tensor* a, ts_tensor* b);   /* mul.rs:94-135 */
 ts_tensor* ts_tensor_div_tensor(ts_tensor* a, ts_tensor* b);   /* div.rs:109-150 */
 ts_tensor* ts_tensor_relu(ts_tensor* x);                       /* relu.rs:77-90 */
-ts_tensor* ts_tensor_pow_scalar(ts_tensor* x, float exponent); /* pow.rs:79-130; exponent 2 only */
+ts_tensor* ts_tensor_pow_scalar(ts_tensor* x, float exponent); /* pow.rs:79-160 */
+/* The unary and scalar ops of the reference's example networks; each records the GradFn the reference records
+ * (what it saves is listed at launch_unary_backward_kernel). */
+ts_tensor* ts_tensor_exp(ts_tensor* x);                         /* exp.rs:96-110 */
+ts_tensor* ts_tensor_log(ts_tensor* x);                         /* log.rs:68-140; x <= 0 fails, see ts_set_domain_checks */
+ts_tensor* ts_tensor_sqrt(ts_tensor* x);                        /* sqrt.rs:99-214 */
+ts_tensor* ts_tensor_tanh(ts_tensor* x);                        /* tanh.rs:140-190 */
+ts_tensor* ts_tensor_sigmoid(ts_tensor* x);                     /* sigmoid.rs:90-125 */
+ts_tensor* ts_tensor_leaky_relu(ts_tensor* x, float negative_slope); /* leaky_relu.rs:80-330 */
+ts_tensor* ts_tensor_softmax(ts_tensor* x, unsigned long long dim);  /* softmax.rs:110-175 */
+ts_tensor* ts_tensor_add_scalar(ts_tensor* x, float scalar);    /* add.rs:236-250 */
+ts_tensor* ts_tensor_sub_scalar(ts_tensor* x, float scalar);    /* sub.rs:264-278 */
+ts_tensor* ts_tensor_mul_scalar(ts_tensor* x, float scalar);    /* mul.rs:239-255 */
+ts_tensor* ts_tensor_div_scalar(ts_tensor* x, float scalar);    /* div.rs:247-265; a zero scalar fails */
+/* The reference panics inside log() when an element is <= 0.  1 (default): ts_tensor_log waits for its kernel and
+ * fails at the call, like the panic.  0: no wait; the failure is reported by the next ts_sync_stream. */
+void ts_set_domain_checks(int at_the_call);
+int ts_get_domain_checks(void);
 ts_tensor* ts_tensor_sum(ts_tensor* x);                        /* reductions/sum.rs:80-143 */
 ts_tensor* ts_tensor_mean(ts_tensor* x);                       /* reductions/mean.rs:48-110 */
 

@@ -23,8 +23,8 @@ _f = C.POINTER(C.c_float)
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside it (gcc, a second or two)."""
-    src = os.path.join(_HERE, "ts_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("ts_oracle.c", "ts_oracle_unary.c", "Makefile"))
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < newest:
         subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
     return _SO
 
@@ -72,6 +72,12 @@ def lib():
                                       C.c_float, C.c_float, C.c_uint64]
         L.ora_mlp_step.argtypes = [C.POINTER(_MlpArgs)]
         L.ora_mlp_step.restype = C.c_float
+        L.ora_unary.argtypes = [C.c_int, _f, _f, sz, C.c_float]
+        L.ora_unary.restype = C.c_int
+        L.ora_unary_backward.argtypes = [C.c_int, _f, _f, _f, sz, C.c_float]
+        L.ora_unary_backward.restype = C.c_int
+        L.ora_softmax.argtypes = [_f, _f, sz, sz, sz]
+        L.ora_softmax_backward.argtypes = [_f, _f, _f, sz, sz, sz]
         _lib = L
     return _lib
 
@@ -165,6 +171,61 @@ def neg(x):
     o = np.empty_like(x)
     lib().ora_neg(_p(x), _p(o), x.size)
     return o
+
+
+# operation codes of ora_unary / ora_unary_backward (ts_oracle_unary.c); the device library uses the same numbers
+UNARY = {"exp": 0, "log": 1, "sqrt": 2, "tanh": 3, "sigmoid": 4, "leaky_relu": 5, "add_scalar": 6, "sub_scalar": 7,
+         "mul_scalar": 8, "div_scalar": 9, "pow_scalar": 10}
+# what the reference's GradFn saves for each op: "out", "in" or None
+UNARY_SAVES = {"exp": "out", "log": "in", "sqrt": "out", "tanh": "out", "sigmoid": "out", "leaky_relu": "in",
+               "add_scalar": None, "sub_scalar": None, "mul_scalar": None, "div_scalar": None, "pow_scalar": "in"}
+
+
+class DomainError(ArithmeticError):
+    """Where the reference panics: log of x <= 0, division by a zero scalar."""
+
+
+def unary(name, x, param=0.0, check=True):
+    x = _c(x)
+    o = np.empty_like(x)
+    st = lib().ora_unary(UNARY[name], _p(x), _p(o), x.size, float(param))
+    if st == -2:
+        raise ValueError(name)
+    if st == -1 and check:
+        raise DomainError(name)
+    return o
+
+
+def unary_backward(name, saved, go, param=0.0):
+    go = _c(go)
+    gi = np.empty_like(go)
+    sp = _p(_c(saved)) if saved is not None else None
+    st = lib().ora_unary_backward(UNARY[name], sp, _p(go), _p(gi), go.size, float(param))
+    if st != 0:
+        raise ValueError(name)
+    return gi
+
+
+def _softmax_axes(shape, dim):
+    outer = int(np.prod(shape[:dim], dtype=np.int64))
+    inner = int(np.prod(shape[dim + 1:], dtype=np.int64))
+    return outer, int(shape[dim]), inner
+
+
+def softmax(x, dim):
+    x = _c(x)
+    y = np.empty_like(x)
+    o, r, i = _softmax_axes(x.shape, dim)
+    lib().ora_softmax(_p(x), _p(y), o, r, i)
+    return y
+
+
+def softmax_backward(y, go, dim):
+    y, go = _c(y), _c(go)
+    gi = np.empty_like(y)
+    o, r, i = _softmax_axes(y.shape, dim)
+    lib().ora_softmax_backward(_p(y), _p(go), _p(gi), o, r, i)
+    return gi
 
 
 def total(x) -> np.float32:

@@ -99,6 +99,16 @@ class OracleGraph:
             n = x.data.size
             return self._mk(np.array([o.mean(x.data)], np.float32), [x],
                             lambda g: [np.full(x.data.shape, np.float32(1.0) / np.float32(n) * g.reshape(-1)[0], np.float32)])
+        if name in o.UNARY:   # exp, log, sqrt, tanh, sigmoid, leaky_relu, *_scalar, pow_scalar: [x, param?]
+            x, *params = args
+            p = float(params[0]) if params else 0.0
+            y = o.unary(name, x.data, p)
+            saved = {"out": y, "in": x.data, None: None}[o.UNARY_SAVES[name]]
+            return self._mk(y, [x], lambda g: [o.unary_backward(name, saved, g, p)])
+        if name == "softmax":
+            x, dim = args
+            y = o.softmax(x.data, int(dim))
+            return self._mk(y, [x], lambda g: [o.softmax_backward(y, g, int(dim))])
         raise KeyError(name)
 
     def backward(self, root, grad_output=None):
@@ -128,7 +138,8 @@ def run_case_oracle(ora, case):
     G = OracleGraph(ora)
     env = {k: G.leaf(v["data"], v["dims"], v.get("rg", False)) for k, v in case["inputs"].items()}
     for out, opname, *args in case["program"]:
-        env[out] = G.op("pow2" if opname == "pow_scalar2" else opname, *[env[a] for a in args])
+        # string arguments name tensors; numbers are the op's own parameter (slope, scalar, exponent, axis)
+        env[out] = G.op("pow2" if opname == "pow_scalar2" else opname, *[env[a] if isinstance(a, str) else a for a in args])
     if "backward" in case:
         go = case["backward"]["grad_output"]
         G.backward(env[case["backward"]["of"]], env[go] if go else None)
@@ -143,7 +154,7 @@ def run_case_device(ts, case):
         t = ts.Tensor.from_slice(v["data"], v["dims"])
         env[k] = t.with_requires_grad() if v.get("rg", False) else t
     for out, opname, *args in case["program"]:
-        a = [env[x] for x in args]
+        a = [env[x] if isinstance(x, str) else x for x in args]
         env[out] = a[0].pow_scalar(2.0) if opname == "pow_scalar2" else getattr(a[0], opname)(*a[1:])
     if "backward" in case:
         go = case["backward"]["grad_output"]

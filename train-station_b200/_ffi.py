@@ -75,6 +75,10 @@ SIGNATURES = {
     "launch_scale_kernel": (C.c_bool, [vp, C.c_float, vp, u64, vp]),
     "launch_fill_kernel": (C.c_bool, [vp, C.c_float, u64, vp]),
     "launch_fill_from_scalar_kernel": (C.c_bool, [vp, vp, C.c_float, u64, vp]),
+    "launch_unary_kernel": (C.c_bool, [C.c_int, vp, vp, u64, C.c_float, vp]),
+    "launch_unary_backward_kernel": (C.c_bool, [C.c_int, vp, vp, vp, u64, C.c_float, vp]),
+    "launch_softmax_kernel": (C.c_bool, [vp, vp, u64, u64, u64, vp]),
+    "launch_softmax_backward_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, vp]),
     "ts_reduce_scratch_elems": (u64, []),
     "launch_sum_kernel": (C.c_bool, [vp, vp, u64, C.c_int, vp, vp]),
     "ts_colsum_scratch_elems": (u64, [u64, u64]),
@@ -109,6 +113,19 @@ SIGNATURES = {
     "ts_tensor_div_tensor": (vp, [vp, vp]),
     "ts_tensor_relu": (vp, [vp]),
     "ts_tensor_pow_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_exp": (vp, [vp]),
+    "ts_tensor_log": (vp, [vp]),
+    "ts_tensor_sqrt": (vp, [vp]),
+    "ts_tensor_tanh": (vp, [vp]),
+    "ts_tensor_sigmoid": (vp, [vp]),
+    "ts_tensor_leaky_relu": (vp, [vp, C.c_float]),
+    "ts_tensor_softmax": (vp, [vp, u64]),
+    "ts_tensor_add_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_sub_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_mul_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_div_scalar": (vp, [vp, C.c_float]),
+    "ts_set_domain_checks": (None, [C.c_int]),
+    "ts_get_domain_checks": (C.c_int, []),
     "ts_tensor_sum": (vp, [vp]),
     "ts_tensor_mean": (vp, [vp]),
     "ts_tensor_backward": (C.c_bool, [vp, vp]),

@@ -99,6 +99,11 @@ bool fill(float* o, float v, size_t n, cudaStream_t s);
 bool fill_from_scalar(float* o, const float* scalar, float scale, size_t n, cudaStream_t s);
 // gy = ((inv_n) * (*upstream)) * (2 * (y - t)): ReduceMean -> PowScalar(2) -> Sub in one pass.
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s);
+// op codes: enum ts_unary_op of the public header; p is the slope, scalar or exponent
+bool unary(int op, const float* x, float* o, size_t n, float p, cudaStream_t s);
+bool unary_bwd(int op, const float* saved, const float* go, float* gi, size_t n, float p, cudaStream_t s);
+bool softmax(const float* x, float* y, size_t outer, size_t reduce, size_t inner, cudaStream_t s);
+bool softmax_bwd(const float* y, const float* go, float* gi, size_t outer, size_t reduce, size_t inner, cudaStream_t s);
 bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaStream_t s);
 // loss[0] = mean((y-t)^2) without materialising the difference.
 bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s);

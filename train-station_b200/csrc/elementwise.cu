@@ -177,6 +177,51 @@ struct MseGradF {
     }
 };
 
+// ---- unary and scalar ops beside the MLP path (tensor/ops/{exp,log,sqrt,tanh,sigmoid,leaky_relu,pow}.rs and
+// the *_scalar variants of add/sub/mul/div).  The transcendental functions are CUDA's full-precision expf, logf,
+// tanhf and powf (1-4 ulp from the host libm the reference calls); every other step is one rounded operation.
+struct ExpF { __device__ void apply(const float* x, float* o) const { o[0] = expf(x[0]); } };
+// log.rs:68-107 panics on x <= 0 (NaN included): the kernel still stores the IEEE result and raises the device word.
+struct LogF {
+    int* flag;
+    __device__ void apply(const float* x, float* o) const {
+        if (!(x[0] > 0.0f)) atomicCAS(flag, 0, TS_DEVICE_ERROR_LOG_DOMAIN);
+        o[0] = logf(x[0]);
+    }
+};
+struct SqrtF { __device__ void apply(const float* x, float* o) const { o[0] = __fsqrt_rn(x[0]); } };
+struct TanhF { __device__ void apply(const float* x, float* o) const { o[0] = tanhf(x[0]); } };
+// sigmoid.rs:90-110, the two-branch stable form: x >= 0 -> 1/(1+exp(-x)), else exp(x)/(1+exp(x)).  Both branches
+// exponentiate -|x|, so one expf and one division serve both without divergence (a NaN takes the second branch
+// in the reference and stays a NaN here).
+struct SigmoidF {
+    __device__ void apply(const float* x, float* o) const {
+        const float z = expf(-fabsf(x[0]));
+        const float num = x[0] >= 0.0f ? 1.0f : z;
+        o[0] = __fdiv_rn(num, __fadd_rn(1.0f, z));
+    }
+};
+struct LeakyReluF { float slope; __device__ void apply(const float* x, float* o) const { o[0] = x[0] > 0.0f ? x[0] : __fmul_rn(slope, x[0]); } };
+struct AddScalarF { float v; __device__ void apply(const float* x, float* o) const { o[0] = __fadd_rn(x[0], v); } };
+struct SubScalarF { float v; __device__ void apply(const float* x, float* o) const { o[0] = __fsub_rn(x[0], v); } };
+struct DivScalarF { float v; __device__ void apply(const float* x, float* o) const { o[0] = __fdiv_rn(x[0], v); } };
+struct PowF { float e; __device__ void apply(const float* x, float* o) const { o[0] = powf(x[0], e); } };
+// backward functors: inputs (saved, go)
+struct ExpBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[1], x[0]); } };
+struct LogBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[1], __fdiv_rn(1.0f, x[0])); } };
+struct SqrtBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[1], __fmul_rn(__fdiv_rn(1.0f, x[0]), 0.5f)); } };
+struct TanhBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(x[1], __fsub_rn(1.0f, __fmul_rn(x[0], x[0]))); } };
+struct SigmoidBwdF { __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(__fmul_rn(x[1], x[0]), __fsub_rn(1.0f, x[0])); } };
+struct LeakyReluBwdF { float slope; __device__ void apply(const float* x, float* o) const { o[0] = x[0] > 0.0f ? x[1] : __fmul_rn(slope, x[1]); } };
+// go * (e * x^(e-1)), zero when e == 0 (grad_fn/ops/pow.rs:5-27)
+struct PowBwdF {
+    float e;
+    __device__ void apply(const float* x, float* o) const {
+        float local = e == 0.0f ? 0.0f : __fmul_rn(e, powf(x[0], __fsub_rn(e, 1.0f)));
+        o[0] = __fmul_rn(x[1], local);
+    }
+};
+
 // out[i,j] = act(z[i,j] + bias[j]); cols % 4 == 0 and aligned pointers take the vector path.
 template <bool RELU>
 __global__ void __launch_bounds__(kThreads) bias_act_vec_kernel(const float4* __restrict__ z, const float4* __restrict__ bias,
@@ -251,6 +296,60 @@ bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s) { return 
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {
     if (!upstream) { set_error("mse_grad: null upstream"); return false; }
     return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n}, s);
+}
+
+bool unary(int op, const float* x, float* o, size_t n, float p, cudaStream_t s) {
+    Ptrs<1, 1> ptrs{{x}, {o}};
+    switch (op) {
+        case TS_UNARY_EXP: return launch_ew(ptrs, n, ExpF{}, s);
+        case TS_UNARY_LOG: {
+            DeviceCtx* c = ctx();
+            return c && launch_ew(ptrs, n, LogF{c->error_flag}, s);
+        }
+        case TS_UNARY_SQRT: return launch_ew(ptrs, n, SqrtF{}, s);
+        case TS_UNARY_TANH: return launch_ew(ptrs, n, TanhF{}, s);
+        case TS_UNARY_SIGMOID: return launch_ew(ptrs, n, SigmoidF{}, s);
+        case TS_UNARY_LEAKY_RELU: return launch_ew(ptrs, n, LeakyReluF{p}, s);
+        case TS_UNARY_ADD_SCALAR: return launch_ew(ptrs, n, AddScalarF{p}, s);
+        case TS_UNARY_SUB_SCALAR: return launch_ew(ptrs, n, SubScalarF{p}, s);
+        case TS_UNARY_MUL_SCALAR: return launch_ew(ptrs, n, ScaleF{p}, s);
+        case TS_UNARY_DIV_SCALAR:
+            // div.rs:511-514 panics before touching the data
+            if (p == 0.0f) { set_error("Division by zero: cannot divide tensor by zero scalar"); return false; }
+            return launch_ew(ptrs, n, DivScalarF{p}, s);
+        case TS_UNARY_POW_SCALAR:
+            // pow.rs:125-160: exponent 2 is x*x, 0.5 is sqrt, anything else powf
+            if (p == 2.0f) return launch_ew(ptrs, n, SquareF{}, s);
+            if (p == 0.5f) return launch_ew(ptrs, n, SqrtF{}, s);
+            return launch_ew(ptrs, n, PowF{p}, s);
+    }
+    set_error("unary: unknown op %d", op);
+    return false;
+}
+
+bool unary_bwd(int op, const float* saved, const float* go, float* gi, size_t n, float p, cudaStream_t s) {
+    const bool needs_saved = op == TS_UNARY_EXP || op == TS_UNARY_LOG || op == TS_UNARY_SQRT || op == TS_UNARY_TANH ||
+                             op == TS_UNARY_SIGMOID || op == TS_UNARY_LEAKY_RELU || op == TS_UNARY_POW_SCALAR;
+    if (needs_saved && !saved && n) { set_error("unary backward: op %d needs the saved tensor", op); return false; }
+    Ptrs<2, 1> two{{saved, go}, {gi}};
+    Ptrs<1, 1> one{{go}, {gi}};
+    switch (op) {
+        case TS_UNARY_EXP: return launch_ew(two, n, ExpBwdF{}, s);
+        case TS_UNARY_LOG: return launch_ew(two, n, LogBwdF{}, s);
+        case TS_UNARY_SQRT: return launch_ew(two, n, SqrtBwdF{}, s);
+        case TS_UNARY_TANH: return launch_ew(two, n, TanhBwdF{}, s);
+        case TS_UNARY_SIGMOID: return launch_ew(two, n, SigmoidBwdF{}, s);
+        case TS_UNARY_LEAKY_RELU: return launch_ew(two, n, LeakyReluBwdF{p}, s);
+        case TS_UNARY_POW_SCALAR: return launch_ew(two, n, PowBwdF{p}, s);
+        case TS_UNARY_ADD_SCALAR:
+        case TS_UNARY_SUB_SCALAR: return launch_ew(one, n, ScaleF{1.0f}, s);   // the gradient itself (a copy)
+        case TS_UNARY_MUL_SCALAR: return launch_ew(one, n, ScaleF{p}, s);
+        case TS_UNARY_DIV_SCALAR:
+            if (p == 0.0f) { set_error("Division by zero: cannot divide tensor by zero scalar"); return false; }
+            return launch_ew(one, n, DivScalarF{p}, s);
+    }
+    set_error("unary backward: unknown op %d", op);
+    return false;
 }
 
 bool bias_act(const float* z, const float* bias, float* o, size_t rows, size_t cols, bool relu_on, cudaStream_t s) {
@@ -347,4 +446,15 @@ TS_API bool launch_fill_kernel(float* out, float value, unsigned long long n, vo
 TS_API bool launch_fill_from_scalar_kernel(float* out, const float* scalar, float scale, unsigned long long n, void* stream) {
     TS_STREAM_OR_FAIL(s);
     return k::fill_from_scalar(out, scalar, scale, n, s);
+}
+TS_API bool launch_unary_kernel(int op, const float* x, float* out, unsigned long long n, float param, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!x || !out) { if (n == 0) return true; set_error("launch_unary_kernel: null pointer"); return false; }
+    return k::unary(op, x, out, n, param, s);
+}
+TS_API bool launch_unary_backward_kernel(int op, const float* saved, const float* go, float* gi, unsigned long long n, float param,
+                                         void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    if (!go || !gi) { if (n == 0) return true; set_error("launch_unary_backward_kernel: null pointer"); return false; }
+    return k::unary_bwd(op, saved, go, gi, n, param, s);
 }

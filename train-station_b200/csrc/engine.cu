@@ -179,7 +179,7 @@ static bool materialize(const TensorP& t, bool for_gemm) {
 }
 
 // ------------------------------------------------------------------ tape
-enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean };
+enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax };
 
 struct Saved {
     TensorP t;
@@ -203,6 +203,7 @@ struct Node {
     Saved s0, s1;                       // saved tensors (meaning depends on op)
     std::vector<size_t> dims0, dims1;   // operand shapes
     float scalar = 0.0f;
+    int code = 0;                       // Unary: the ts_unary_op; Softmax: the axis
 };
 
 struct Graph {
@@ -508,6 +509,36 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             const float *x = rptr(nd.s0.t), *gp = rptr(go);
             TensorP r = (x && gp) ? new_tensor(c, go->dims) : nullptr;
             if (!r || !k::square_bwd(x, gp, r->st->ptr, r->size, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::Unary: {
+            // grad_fn/ops/{exp,log,sqrt,tanh,sigmoid,leaky_relu,pow}.rs and the scalar branches of add/sub/mul/div.rs
+            if (!nd.needs[0]) return true;
+            if (nd.code == TS_UNARY_ADD_SCALAR || nd.code == TS_UNARY_SUB_SCALAR) { gin[0] = go; return true; }
+            const float* saved = nullptr;
+            if (nd.s0.t) {
+                if (!nd.s0.check("a unary op")) return false;
+                saved = rptr(nd.s0.t);
+                if (!saved) return false;
+            }
+            const float* gp = rptr(go);
+            TensorP r = gp ? new_tensor(c, go->dims) : nullptr;
+            if (!r || !k::unary_bwd(nd.code, saved, gp, r->st->ptr, r->size, nd.scalar, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::Softmax: {
+            // grad_fn/ops/softmax.rs:4-35
+            if (!nd.needs[0]) return true;
+            if (!nd.s0.check("softmax")) return false;
+            const float *y = rptr(nd.s0.t), *gp = rptr(go);
+            TensorP r = (y && gp) ? new_tensor(c, nd.dims0) : nullptr;
+            if (!r) return false;
+            size_t outer = 1, inner = 1;
+            for (int d = 0; d < nd.code; ++d) outer *= nd.dims0[d];
+            for (size_t d = nd.code + 1; d < nd.dims0.size(); ++d) inner *= nd.dims0[d];
+            if (!k::softmax_bwd(y, gp, r->st->ptr, outer, nd.dims0[nd.code], inner, s)) return false;
             gin[0] = r;
             return true;
         }
@@ -858,9 +889,82 @@ TS_API ts_tensor* ts_tensor_relu(ts_tensor* hx) {
     return wrap(out);
 }
 
+// ---- unary and scalar ops: one kernel forward, one backward, the tensor the reference's GradFn saves kept by reference
+static std::atomic<int> g_domain_checks{1};
+TS_API void ts_set_domain_checks(int at_the_call) { g_domain_checks.store(at_the_call ? 1 : 0); }
+TS_API int ts_get_domain_checks(void) { return g_domain_checks.load(); }
+
+static ts_tensor* unary_op(ts_tensor* hx, int code, float param, const char* name) {
+    if (!hx) { set_error("%s: null tensor", name); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+    if (!out || !k::unary(code, px, out->st->ptr, out->size, param, c->compute)) return nullptr;
+    if (code == TS_UNARY_LOG && g_domain_checks.load() && out->size) {
+        // log.rs:68-107 panics at the call; here the kernel raises a device word, read back now
+        if (!ts_sync_stream(nullptr)) return nullptr;
+    }
+    if (grad_on() && x->requires_grad) {
+        Node nd;
+        nd.op = Op::Unary;
+        nd.code = code;
+        nd.scalar = param;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        switch (code) {
+            case TS_UNARY_EXP: case TS_UNARY_SQRT: case TS_UNARY_TANH: case TS_UNARY_SIGMOID: nd.s0.set(out); break;
+            case TS_UNARY_LOG: case TS_UNARY_LEAKY_RELU: case TS_UNARY_POW_SCALAR: nd.s0.set(x); break;
+            default: break;
+        }
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+TS_API ts_tensor* ts_tensor_exp(ts_tensor* x) { return unary_op(x, TS_UNARY_EXP, 0.0f, "exp"); }
+TS_API ts_tensor* ts_tensor_log(ts_tensor* x) { return unary_op(x, TS_UNARY_LOG, 0.0f, "log"); }
+TS_API ts_tensor* ts_tensor_sqrt(ts_tensor* x) { return unary_op(x, TS_UNARY_SQRT, 0.0f, "sqrt"); }
+TS_API ts_tensor* ts_tensor_tanh(ts_tensor* x) { return unary_op(x, TS_UNARY_TANH, 0.0f, "tanh"); }
+TS_API ts_tensor* ts_tensor_sigmoid(ts_tensor* x) { return unary_op(x, TS_UNARY_SIGMOID, 0.0f, "sigmoid"); }
+TS_API ts_tensor* ts_tensor_leaky_relu(ts_tensor* x, float negative_slope) { return unary_op(x, TS_UNARY_LEAKY_RELU, negative_slope, "leaky_relu"); }
+TS_API ts_tensor* ts_tensor_add_scalar(ts_tensor* x, float v) { return unary_op(x, TS_UNARY_ADD_SCALAR, v, "add_scalar"); }
+TS_API ts_tensor* ts_tensor_sub_scalar(ts_tensor* x, float v) { return unary_op(x, TS_UNARY_SUB_SCALAR, v, "sub_scalar"); }
+TS_API ts_tensor* ts_tensor_mul_scalar(ts_tensor* x, float v) { return unary_op(x, TS_UNARY_MUL_SCALAR, v, "mul_scalar"); }
+TS_API ts_tensor* ts_tensor_div_scalar(ts_tensor* x, float v) { return unary_op(x, TS_UNARY_DIV_SCALAR, v, "div_scalar"); }
+
+TS_API ts_tensor* ts_tensor_softmax(ts_tensor* hx, unsigned long long dim) {
+    if (!hx) { set_error("softmax: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    if (dim >= x->dims.size()) {   // softmax.rs:112-117
+        set_error("softmax dim %llu out of bounds for rank %zu", dim, x->dims.size());
+        return nullptr;
+    }
+    size_t outer = 1, inner = 1;
+    for (size_t d = 0; d < dim; ++d) outer *= x->dims[d];
+    for (size_t d = dim + 1; d < x->dims.size(); ++d) inner *= x->dims[d];
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+    if (!out || !k::softmax(px, out->st->ptr, outer, x->dims[dim], inner, c->compute)) return nullptr;
+    if (grad_on() && x->requires_grad) {
+        Node nd;
+        nd.op = Op::Softmax;
+        nd.code = (int)dim;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.s0.set(out);
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
 TS_API ts_tensor* ts_tensor_pow_scalar(ts_tensor* hx, float exponent) {
     if (!hx) { set_error("pow_scalar: null tensor"); return nullptr; }
-    if (exponent != 2.0f) { set_error("pow_scalar: only exponent 2.0 is implemented on this path (got %g)", (double)exponent); return nullptr; }
+    if (exponent != 2.0f) return unary_op(hx, TS_UNARY_POW_SCALAR, exponent, "pow_scalar");
     DeviceCtx* c = ctx();
     if (!c) return nullptr;
     TensorP x = hx->t;

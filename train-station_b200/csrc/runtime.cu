@@ -370,7 +370,8 @@ TS_API bool ts_sync_stream(void* stream) {
         *c->error_flag_host = 0;
         cudaMemsetAsync(c->error_flag, 0, sizeof(int), s);
         cudaStreamSynchronize(s);
-        set_error("a kernel reported device-side error code %d (a bounded wait gave up); results of the last launches are invalid", code);
+        if (code == TS_DEVICE_ERROR_LOG_DOMAIN) set_error("log domain error: x <= 0");   // the reference's panic text, log.rs:80-83
+        else set_error("a kernel reported device-side error code %d (a bounded wait gave up); results of the last launches are invalid", code);
         return false;
     }
     return true;

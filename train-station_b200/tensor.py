@@ -178,11 +178,84 @@ class Tensor:
     def mean(self) -> "Tensor":
         return Tensor(_ffi.lib().ts_tensor_mean(self._h))
 
-    # operator sugar, as tensor/core/operators.rs:120-185 forwards to the *_tensor methods
-    __add__ = add_tensor
-    __sub__ = sub_tensor
-    __mul__ = mul_tensor
-    __truediv__ = div_tensor
+    # unary and scalar ops (tensor/ops/{exp,log,sqrt,tanh,sigmoid,leaky_relu,softmax}.rs, *_scalar of add/sub/mul/div.rs)
+    def exp(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_exp(self._h))
+
+    def log(self) -> "Tensor":
+        """Raises where the reference panics: an element <= 0 (log.rs:68-107)."""
+        return Tensor(_ffi.lib().ts_tensor_log(self._h))
+
+    def sqrt(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_sqrt(self._h))
+
+    def tanh(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_tanh(self._h))
+
+    def sigmoid(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_sigmoid(self._h))
+
+    def leaky_relu(self, negative_slope: float) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_leaky_relu(self._h, float(negative_slope)))
+
+    def softmax(self, dim: int) -> "Tensor":
+        if dim < 0:
+            raise ValueError("softmax dim is an unsigned axis index (softmax.rs:110)")
+        return Tensor(_ffi.lib().ts_tensor_softmax(self._h, int(dim)))
+
+    def add_scalar(self, scalar: float) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_add_scalar(self._h, float(scalar)))
+
+    def sub_scalar(self, scalar: float) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_sub_scalar(self._h, float(scalar)))
+
+    def mul_scalar(self, scalar: float) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_mul_scalar(self._h, float(scalar)))
+
+    def div_scalar(self, scalar: float) -> "Tensor":
+        """Raises where the reference panics: a zero scalar (div.rs:511-514)."""
+        return Tensor(_ffi.lib().ts_tensor_div_scalar(self._h, float(scalar)))
+
+    # operator sugar: tensor/core/operators.rs forwards Tensor (op) Tensor to the *_tensor methods (:120-410),
+    # Tensor (op) f32 to the *_scalar methods (:418-660) and -Tensor to mul_scalar(-1.0) (:690-705)
+    @staticmethod
+    def _is_scalar(v) -> bool:
+        return isinstance(v, (int, float, np.floating, np.integer))
+
+    def __add__(self, other):
+        return self.add_scalar(other) if Tensor._is_scalar(other) else self.add_tensor(other)
+
+    def __sub__(self, other):
+        return self.sub_scalar(other) if Tensor._is_scalar(other) else self.sub_tensor(other)
+
+    def __mul__(self, other):
+        return self.mul_scalar(other) if Tensor._is_scalar(other) else self.mul_tensor(other)
+
+    def __truediv__(self, other):
+        return self.div_scalar(other) if Tensor._is_scalar(other) else self.div_tensor(other)
+
+    def __radd__(self, scalar):      # f32 + &Tensor -> add_scalar (operators.rs:448-472)
+        return self.add_scalar(scalar)
+
+    def __rmul__(self, scalar):      # f32 * &Tensor -> mul_scalar (operators.rs:595-620)
+        return self.mul_scalar(scalar)
+
+    def __rsub__(self, scalar):
+        """f32 - &Tensor (operators.rs:535-547): the reference negates a detached clone and adds the scalar,
+        so the result carries no gradient history; the same holds here."""
+        lib = _ffi.lib()
+        lib.ts_no_grad_push()
+        try:
+            return self.mul_scalar(-1.0).add_scalar(scalar)
+        finally:
+            lib.ts_no_grad_pop()
+
+    def __rtruediv__(self, scalar):  # f32 / &Tensor -> pow_scalar(-1.0).mul_scalar(s) (operators.rs:665-685)
+        return self.pow_scalar(-1.0).mul_scalar(scalar)
+
+    def __neg__(self):
+        return self.mul_scalar(-1.0)
+
     __matmul__ = matmul
 
     # ------------------------------------------------------------------ gradtrack
