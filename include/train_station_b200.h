@@ -244,6 +244,15 @@ bool launch_adam_multi_tensor_kernel(float* const* params, const float* const* g
                                      float* const* v, const unsigned long long* sizes, int n_tensors,
                                      float lr, float beta1, float beta2, float eps, float weight_decay,
                                      float f1, float f2, float grad_scale, void* stream);
+/* The AMSGrad branch (adam/mod.rs:534-541, 846-900): v_hat_max[i] = max(v_hat_max[i], v[i]*f2), i.e. the running
+ * maximum of the BIAS-CORRECTED second moment, and the update divides by sqrt(v_hat_max) + eps.  The reference
+ * creates v_hat_max as a copy of the first v_hat; a zero-filled buffer gives the same values since v_hat >= 0.
+ * 36 bytes per parameter. */
+bool launch_adam_amsgrad_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m,
+                                             float* const* v, float* const* v_hat_max,
+                                             const unsigned long long* sizes, int n_tensors, float lr, float beta1,
+                                             float beta2, float eps, float weight_decay, float f1, float f2,
+                                             float grad_scale, void* stream);
 
 /* ===================================================================================
  * 4. Tensor, gradtrack and Adam engine: what the reference's Rust API maps onto
@@ -261,6 +270,12 @@ ts_tensor* ts_tensor_from_slice(const float* host, const unsigned long long* dim
 /* Upload queued on the copy stream; `host` must be pinned and stay valid until the tensor is
  * first used (the compute stream then waits for the copy). */
 ts_tensor* ts_tensor_from_pinned_async(const float* host, const unsigned long long* dims, int rank);
+/* Tensor::randn(dims, seed) (tensor/init/random.rs:231-236): the reference's own generator, value for value —
+ * xorshift64 (13, 7, 17) from state = seed, draws in [0.5, 1), Box-Muller with the host libm (random.rs:473-616) —
+ * produced on the host and uploaded.  has_seed == 0 is randn(dims, None): a clock-derived seed, not reproducible. */
+ts_tensor* ts_tensor_randn(const unsigned long long* dims, int rank, unsigned long long seed, int has_seed);
+/* The same generator into a host buffer; needs no device. */
+bool ts_randn_host(float* out, unsigned long long size, unsigned long long seed);
 void ts_tensor_free(ts_tensor* t);
 
 unsigned long long ts_tensor_id(const ts_tensor* t);
@@ -317,6 +332,8 @@ unsigned long long ts_tape_len(void);                          /* recorded opera
 
 /* Adam (optimizers/adam/mod.rs:91-117 config defaults 1e-3, 0.9, 0.999, 1e-8, 0, false). */
 ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float weight_decay);
+/* The same with AdamConfig::amsgrad (adam/mod.rs:103): each parameter also gets a v_hat_max state. */
+ts_adam* ts_adam_new_amsgrad(float lr, float beta1, float beta2, float eps, float weight_decay, int amsgrad);
 void ts_adam_free(ts_adam* opt);
 bool ts_adam_add_parameter(ts_adam* opt, const ts_tensor* p);  /* adam/mod.rs:287-320 */
 /* Optimizer::step (adam/mod.rs:1036-1044): parameters without a gradient are skipped with
@@ -330,6 +347,7 @@ unsigned long long ts_adam_step_count(const ts_adam* opt);
 /* Device copies of the moment estimates, for parity checks (NULL if p is not linked). */
 ts_tensor* ts_adam_state_m(const ts_adam* opt, const ts_tensor* p);
 ts_tensor* ts_adam_state_v(const ts_adam* opt, const ts_tensor* p);
+ts_tensor* ts_adam_state_v_hat_max(const ts_adam* opt, const ts_tensor* p);   /* NULL unless amsgrad */
 
 /* ===================================================================================
  * 5. Data parallelism: batch rows sharded over GPUs, one NCCL all-reduce of the parameter

@@ -23,10 +23,30 @@ _f = C.POINTER(C.c_float)
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside it (gcc, a second or two)."""
-    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("ts_oracle.c", "ts_oracle_unary.c", "Makefile"))
+    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("ts_oracle.c", "ts_oracle_unary.c", "ts_oracle_variants.c", "Makefile"))
     if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < newest:
         subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
     return _SO
+
+
+def adam_update_amsgrad(p, g, m, v, vmax, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+    """In place on p, m, v, vmax (float32 arrays; vmax starts at zero); step is the global step after increment."""
+    g = _c(g)
+    for a in (p, m, v, vmax):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().ora_adam_update_amsgrad(_p(p), _p(g), _p(m), _p(v), _p(vmax), p.size, lr, beta1, beta2, eps, weight_decay, int(step))
+
+
+def xorshift_u64(seed, n):
+    out = np.empty(n, np.uint64)
+    lib().ora_xorshift_u64(int(seed), out.ctypes.data_as(C.POINTER(C.c_uint64)), n)
+    return out
+
+
+def randn(shape, seed):
+    out = np.empty(int(np.prod(shape, dtype=np.int64)), np.float32)
+    lib().ora_randn(_p(out), out.size, int(seed))
+    return out.reshape(shape)
 
 
 class _MlpArgs(C.Structure):
@@ -78,6 +98,10 @@ def lib():
         L.ora_unary_backward.restype = C.c_int
         L.ora_softmax.argtypes = [_f, _f, sz, sz, sz]
         L.ora_softmax_backward.argtypes = [_f, _f, _f, sz, sz, sz]
+        L.ora_adam_update_amsgrad.argtypes = [_f, _f, _f, _f, _f, sz, C.c_float, C.c_float, C.c_float,
+                                              C.c_float, C.c_float, C.c_uint64]
+        L.ora_xorshift_u64.argtypes = [C.c_uint64, C.POINTER(C.c_uint64), sz]
+        L.ora_randn.argtypes = [_f, sz, C.c_uint64]
         _lib = L
     return _lib
 

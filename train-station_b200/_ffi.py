@@ -89,12 +89,17 @@ SIGNATURES = {
     "launch_adam_multi_tensor_kernel": (C.c_bool, [C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u64p,
                                                    C.c_int, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float,
                                                    C.c_float, C.c_float, C.c_float, vp]),
+    "launch_adam_amsgrad_multi_tensor_kernel": (C.c_bool, [C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                                           u64p, C.c_int, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float,
+                                                           C.c_float, C.c_float, C.c_float, vp]),
     # 4. tensor / gradtrack / Adam engine
     "ts_tensor_new": (vp, [u64p, C.c_int]),
     "ts_tensor_zeros": (vp, [u64p, C.c_int]),
     "ts_tensor_ones": (vp, [u64p, C.c_int]),
     "ts_tensor_from_slice": (vp, [vp, u64p, C.c_int]),
     "ts_tensor_from_pinned_async": (vp, [vp, u64p, C.c_int]),
+    "ts_tensor_randn": (vp, [u64p, C.c_int, u64, C.c_int]),
+    "ts_randn_host": (C.c_bool, [vp, u64, u64]),
     "ts_tensor_free": (None, [vp]),
     "ts_tensor_id": (u64, [vp]),
     "ts_tensor_rank": (C.c_int, [vp]),
@@ -136,6 +141,8 @@ SIGNATURES = {
     "ts_is_grad_enabled": (C.c_bool, []),
     "ts_tape_len": (u64, []),
     "ts_adam_new": (vp, [C.c_float, C.c_float, C.c_float, C.c_float, C.c_float]),
+    "ts_adam_new_amsgrad": (vp, [C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]),
+    "ts_adam_state_v_hat_max": (vp, [vp, vp]),
     "ts_adam_free": (None, [vp]),
     "ts_adam_add_parameter": (C.c_bool, [vp, vp]),
     "ts_adam_step": (C.c_bool, [vp, C.POINTER(vp), C.c_int, C.c_float]),

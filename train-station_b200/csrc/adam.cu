@@ -30,13 +30,17 @@ struct ChunkEntry {
 
 struct Scalars { float lr, beta1, beta2, eps, wd, f1, f2, grad_scale, c1, c2; };
 
-__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, bool body, const Scalars& sc) {
+// AMS: v_hat_max = max(v_hat_max, v_hat) on the bias-corrected second moment (`if a > b { a } else { b }`,
+// adam/mod.rs:534-541, :846-900), and the update divides by sqrt(v_hat_max) + eps.
+template <bool AMS>
+__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, float& vmx, bool body, const Scalars& sc) {
     if (sc.grad_scale != 1.0f) g = __fmul_rn(g, sc.grad_scale);
     if (sc.wd > 0.0f) g = __fadd_rn(g, __fmul_rn(sc.wd, p));
     m = __fadd_rn(__fmul_rn(sc.beta1, m), __fmul_rn(sc.c1, g));
     float gg = body ? __fmul_rn(sc.c2, __fmul_rn(g, g)) : __fmul_rn(__fmul_rn(sc.c2, g), g);
     v = __fadd_rn(__fmul_rn(sc.beta2, v), gg);
     float mh = __fmul_rn(m, sc.f1), vh = __fmul_rn(v, sc.f2);
+    if (AMS) { vmx = vmx > vh ? vmx : vh; vh = vmx; }
     p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, mh), __fadd_rn(__fsqrt_rn(vh), sc.eps)));
 }
 
@@ -46,6 +50,7 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 constexpr int kMaxTensorsPerLaunch = 48;
 struct AdamTable { AdamTensor t[kMaxTensorsPerLaunch]; };
 
+template <bool AMS>
 __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ AdamTable tab, const ChunkEntry* __restrict__ chunks,
                                                         int chunk_base, int tensor_base, Scalars sc) {
     const ChunkEntry ce = chunks[chunk_base + blockIdx.x];
@@ -53,8 +58,11 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
     const unsigned long long body = t.n / 8 * 8;
     unsigned long long end = ce.offset + kChunk;
     if (end > t.n) end = t.n;
-    const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
-                       reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
+                     reinterpret_cast<uintptr_t>(t.v);
+    if (AMS) bits |= reinterpret_cast<uintptr_t>(t.vmax);
+    const bool vec = (bits & 15) == 0;
+    float unused = 0.0f;
     if (vec) {
         // ce.offset is a multiple of kChunk, hence of 4
         const unsigned long long v0 = ce.offset / 4, v1 = end / 4;
@@ -62,38 +70,45 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
         const float4* gp = reinterpret_cast<const float4*>(t.g);
         float4* mp = reinterpret_cast<float4*>(t.m);
         float4* vp = reinterpret_cast<float4*>(t.v);
+        float4* xp = reinterpret_cast<float4*>(t.vmax);
         for (unsigned long long i = v0 + threadIdx.x; i < v1; i += 2 * kThreads) {
             // two float4 per array in flight
             unsigned long long j = i + kThreads;
             bool has2 = j < v1;
             float4 p0 = pp[i], g0 = __ldcs(gp + i), m0 = mp[i], w0 = vp[i];
+            float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+            if (AMS) x0 = xp[i];
             float4 p1, g1, m1, w1;
-            if (has2) { p1 = pp[j]; g1 = __ldcs(gp + j); m1 = mp[j]; w1 = vp[j]; }
+            if (has2) { p1 = pp[j]; g1 = __ldcs(gp + j); m1 = mp[j]; w1 = vp[j]; if (AMS) x1 = xp[j]; }
             unsigned long long e = i * 4;
-            adam_one(p0.x, g0.x, m0.x, w0.x, e < body, sc);
-            adam_one(p0.y, g0.y, m0.y, w0.y, e + 1 < body, sc);
-            adam_one(p0.z, g0.z, m0.z, w0.z, e + 2 < body, sc);
-            adam_one(p0.w, g0.w, m0.w, w0.w, e + 3 < body, sc);
+            adam_one<AMS>(p0.x, g0.x, m0.x, w0.x, x0.x, e < body, sc);
+            adam_one<AMS>(p0.y, g0.y, m0.y, w0.y, x0.y, e + 1 < body, sc);
+            adam_one<AMS>(p0.z, g0.z, m0.z, w0.z, x0.z, e + 2 < body, sc);
+            adam_one<AMS>(p0.w, g0.w, m0.w, w0.w, x0.w, e + 3 < body, sc);
             pp[i] = p0; mp[i] = m0; vp[i] = w0;
+            if (AMS) xp[i] = x0;
             if (has2) {
                 e = j * 4;
-                adam_one(p1.x, g1.x, m1.x, w1.x, e < body, sc);
-                adam_one(p1.y, g1.y, m1.y, w1.y, e + 1 < body, sc);
-                adam_one(p1.z, g1.z, m1.z, w1.z, e + 2 < body, sc);
-                adam_one(p1.w, g1.w, m1.w, w1.w, e + 3 < body, sc);
+                adam_one<AMS>(p1.x, g1.x, m1.x, w1.x, x1.x, e < body, sc);
+                adam_one<AMS>(p1.y, g1.y, m1.y, w1.y, x1.y, e + 1 < body, sc);
+                adam_one<AMS>(p1.z, g1.z, m1.z, w1.z, x1.z, e + 2 < body, sc);
+                adam_one<AMS>(p1.w, g1.w, m1.w, w1.w, x1.w, e + 3 < body, sc);
                 pp[j] = p1; mp[j] = m1; vp[j] = w1;
+                if (AMS) xp[j] = x1;
             }
         }
         for (unsigned long long i = v1 * 4 + threadIdx.x; i < end; i += kThreads) {
-            float p = t.p[i], m = t.m[i], v = t.v[i];
-            adam_one(p, t.g[i], m, v, i < body, sc);
+            float p = t.p[i], m = t.m[i], v = t.v[i], x = AMS ? t.vmax[i] : unused;
+            adam_one<AMS>(p, t.g[i], m, v, x, i < body, sc);
             t.p[i] = p; t.m[i] = m; t.v[i] = v;
+            if (AMS) t.vmax[i] = x;
         }
     } else {
         for (unsigned long long i = ce.offset + threadIdx.x; i < end; i += kThreads) {
-            float p = t.p[i], m = t.m[i], v = t.v[i];
-            adam_one(p, t.g[i], m, v, i < body, sc);
+            float p = t.p[i], m = t.m[i], v = t.v[i], x = AMS ? t.vmax[i] : unused;
+            adam_one<AMS>(p, t.g[i], m, v, x, i < body, sc);
             t.p[i] = p; t.m[i] = m; t.v[i] = v;
+            if (AMS) t.vmax[i] = x;
         }
     }
 }
@@ -142,8 +157,11 @@ bool adam_launch_range(const AdamTensor* tensors, int first, int last, const voi
             elems += (double)tensors[t0 + i].n;
         }
         if (n_chunks > 0) {
-            ProfScope prof(kProfAdam, s, 28.0 * elems);
-            adam_kernel<<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
+            // every tensor of one optimizer has a running maximum, or none has
+            const bool ams = tab.t[0].vmax != nullptr;
+            ProfScope prof(kProfAdam, s, (ams ? 36.0 : 28.0) * elems);
+            if (ams) adam_kernel<true><<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
+            else adam_kernel<false><<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
             if (!cuda_ok(cudaGetLastError(), "adam launch")) return false;
         }
         chunk_base += n_chunks;
@@ -157,9 +175,10 @@ bool adam_launch_range(const AdamTensor* tensors, int first, int last, const voi
 // ====================================================================== C ABI
 using namespace ts;
 
-TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m, float* const* v,
-                                            const unsigned long long* sizes, int n_tensors, float lr, float beta1, float beta2,
-                                            float eps, float weight_decay, float f1, float f2, float grad_scale, void* stream) {
+// vmax == nullptr: plain Adam; otherwise a table of running maxima (AMSGrad)
+static bool adam_tables_launch(float* const* params, const float* const* grads, float* const* m, float* const* v, float* const* vmax,
+                               const unsigned long long* sizes, int n_tensors, float lr, float beta1, float beta2, float eps,
+                               float weight_decay, float f1, float f2, float grad_scale, void* stream) {
     cudaStream_t s = pick_stream(stream);
     DeviceCtx* c = ctx();
     if (!s || !c) return false;
@@ -167,8 +186,11 @@ TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* c
     if (!params || !grads || !m || !v || !sizes) { set_error("launch_adam_multi_tensor_kernel: null table"); return false; }
     std::vector<k::AdamTensor> t((size_t)n_tensors);
     for (int i = 0; i < n_tensors; ++i) {
-        if (sizes[i] && (!params[i] || !grads[i] || !m[i] || !v[i])) { set_error("launch_adam_multi_tensor_kernel: null tensor pointer at index %d", i); return false; }
-        t[i] = k::AdamTensor{params[i], grads[i], m[i], v[i], sizes[i]};
+        if (sizes[i] && (!params[i] || !grads[i] || !m[i] || !v[i] || (vmax && !vmax[i]))) {
+            set_error("launch_adam_multi_tensor_kernel: null tensor pointer at index %d", i);
+            return false;
+        }
+        t[i] = k::AdamTensor{params[i], grads[i], m[i], v[i], sizes[i], vmax ? vmax[i] : nullptr};
     }
     std::vector<unsigned long long> sz(sizes, sizes + n_tensors);
     int n_chunks = k::adam_chunk_count(sz.data(), n_tensors);
@@ -186,4 +208,18 @@ TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* c
     if (s != c->compute) cudaStreamSynchronize(s);
     c->alloc.free(dev);
     return ok;
+}
+
+TS_API bool launch_adam_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m, float* const* v,
+                                            const unsigned long long* sizes, int n_tensors, float lr, float beta1, float beta2,
+                                            float eps, float weight_decay, float f1, float f2, float grad_scale, void* stream) {
+    return adam_tables_launch(params, grads, m, v, nullptr, sizes, n_tensors, lr, beta1, beta2, eps, weight_decay, f1, f2, grad_scale, stream);
+}
+
+TS_API bool launch_adam_amsgrad_multi_tensor_kernel(float* const* params, const float* const* grads, float* const* m, float* const* v,
+                                                    float* const* v_hat_max, const unsigned long long* sizes, int n_tensors, float lr,
+                                                    float beta1, float beta2, float eps, float weight_decay, float f1, float f2,
+                                                    float grad_scale, void* stream) {
+    if (n_tensors > 0 && !v_hat_max) { set_error("launch_adam_amsgrad_multi_tensor_kernel: null table"); return false; }
+    return adam_tables_launch(params, grads, m, v, v_hat_max, sizes, n_tensors, lr, beta1, beta2, eps, weight_decay, f1, f2, grad_scale, stream);
 }

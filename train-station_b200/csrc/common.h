@@ -118,6 +118,7 @@ struct AdamTensor {
     float* m;
     float* v;
     unsigned long long n;
+    float* vmax = nullptr;   // AMSGrad: running maximum of the bias-corrected second moment; null = plain Adam
 };
 int adam_chunk_count(const unsigned long long* sizes, int n);
 size_t adam_chunk_bytes(int n_chunks);

@@ -22,6 +22,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstring>
+#include <ctime>
 #include <memory>
 #include <unordered_set>
 
@@ -647,12 +648,13 @@ static bool backward(const TensorP& root, const TensorP& grad_output) {
 }
 
 // ------------------------------------------------------------------ Adam
-struct AdamState { StorageP m, v; uint64_t step = 0; size_t n = 0; };
+struct AdamState { StorageP m, v, vmax; uint64_t step = 0; size_t n = 0; };   // vmax only under amsgrad
 
 }  // namespace ts
 
 struct ts_adam {
     float lr, beta1, beta2, eps, wd;
+    bool amsgrad = false;
     uint64_t step_count = 0;
     std::unordered_map<uint64_t, ts::AdamState> states;
     std::vector<uint64_t> order;                 // insertion order, adam/mod.rs:201-206
@@ -703,6 +705,62 @@ TS_API ts_tensor* ts_tensor_from_slice(const float* host, const unsigned long lo
         if (!cuda_ok(cudaMemcpyAsync(h->t->st->ptr, host, h->t->size * sizeof(float), cudaMemcpyHostToDevice, c->compute), "upload") ||
             !cuda_ok(cudaStreamSynchronize(c->compute), "upload sync")) { delete h; return nullptr; }
     }
+    return h;
+}
+
+// Tensor::randn (tensor/init/random.rs:231-236, 270-300, 473-616): a host-side generator, because the reference's
+// stream is one serial xorshift64 chain (shifts 13, 7, 17 from state = seed) and a seeded tensor must reproduce it
+// value for value.  next_f32 puts the low 23 bits under exponent field 126, i.e. in [0.5, 1); a sample is
+// sqrt(-2 ln u1) * cos(2 pi u2) from two consecutive draws, NaN or infinity replaced by 0.  logf / sqrtf / cosf are
+// the host libm's, which is what Rust's f32::ln / sqrt / cos call.
+static inline uint64_t xorshift64(uint64_t& s) {
+    s ^= s << 13;
+    s ^= s >> 7;
+    s ^= s << 17;
+    return s;
+}
+static inline float half_open_unit(uint64_t& s) {
+    const uint32_t bits = (uint32_t)(xorshift64(s) & 0x7FFFFFu) | (126u << 23);
+    float f;
+    std::memcpy(&f, &bits, sizeof f);
+    return f;
+}
+static void fill_randn_host(float* out, size_t n, uint64_t seed) {
+    uint64_t s = seed;
+    for (size_t i = 0; i < n; ++i) {
+        float u1 = half_open_unit(s);
+        const float u2 = half_open_unit(s);
+        if (u1 <= 0.0f) u1 = 1e-7f;                    // random.rs:598-604, unreachable for values in [0.5, 1)
+        else if (u1 >= 1.0f) u1 = 1.0f - 1e-7f;
+        const float z = sqrtf(-2.0f * logf(u1)) * cosf((2.0f * 3.14159265358979323846f) * u2);
+        out[i] = (std::isnan(z) || std::isinf(z)) ? 0.0f : z;
+    }
+}
+// The generator alone, into host memory: needs no device (fill_randn on a host buffer, random.rs:270-300).
+TS_API bool ts_randn_host(float* out, unsigned long long n, unsigned long long seed) {
+    if (!out && n) { set_error("ts_randn_host: null buffer"); return false; }
+    fill_randn_host(out, (size_t)n, (uint64_t)seed);
+    return true;
+}
+// has_seed == 0 mirrors randn(dims, None): the reference hashes the wall clock (random.rs:492-497); here the seed
+// mixes the clock with a per-process counter.  Such tensors are not reproducible in either library.
+TS_API ts_tensor* ts_tensor_randn(const unsigned long long* dims, int rank, unsigned long long seed, int has_seed) {
+    ts_tensor* h = ts_tensor_new(dims, rank);
+    if (!h) return nullptr;
+    const size_t n = h->t->size;
+    if (n == 0) return h;
+    if (!has_seed) {
+        static std::atomic<uint64_t> counter{0x9E3779B97F4A7C15ull};
+        timespec tp;
+        clock_gettime(CLOCK_REALTIME, &tp);
+        seed = ((uint64_t)tp.tv_sec * 1000000000ull + (uint64_t)tp.tv_nsec) ^ counter.fetch_add(0x9E3779B97F4A7C15ull);
+        if (seed == 0) seed = 1;
+    }
+    std::vector<float> host(n);
+    fill_randn_host(host.data(), n, (uint64_t)seed);
+    DeviceCtx* c = h->t->st->c;
+    if (!cuda_ok(cudaMemcpyAsync(h->t->st->ptr, host.data(), n * sizeof(float), cudaMemcpyHostToDevice, c->compute), "randn upload") ||
+        !cuda_ok(cudaStreamSynchronize(c->compute), "randn upload sync")) { delete h; return nullptr; }
     return h;
 }
 
@@ -1045,6 +1103,11 @@ TS_API ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float
     o->c = c;
     return o;
 }
+TS_API ts_adam* ts_adam_new_amsgrad(float lr, float beta1, float beta2, float eps, float weight_decay, int amsgrad) {
+    ts_adam* o = ts_adam_new(lr, beta1, beta2, eps, weight_decay);
+    if (o) o->amsgrad = amsgrad != 0;
+    return o;
+}
 TS_API void ts_adam_free(ts_adam* o) {
     if (!o) return;
     if (o->c) o->c->alloc.free(o->chunks_dev);
@@ -1060,6 +1123,11 @@ TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
     st.v = new_storage(o->c, st.n);
     if (!st.m || !st.v) return false;
     if (!k::fill(st.m->ptr, 0.0f, st.n, o->c->compute) || !k::fill(st.v->ptr, 0.0f, st.n, o->c->compute)) return false;
+    if (o->amsgrad) {
+        // the reference starts v_hat_max as a copy of the first v_hat (adam/mod.rs:535-537); zero gives the same maxima
+        st.vmax = new_storage(o->c, st.n);
+        if (!st.vmax || !k::fill(st.vmax->ptr, 0.0f, st.n, o->c->compute)) return false;
+    }
     o->states[p->t->id] = st;
     o->order.push_back(p->t->id);
     return true;
@@ -1093,7 +1161,8 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         if (!gp || !pp) return false;
         if (g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
         it->second.step += 1;
-        tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size});
+        tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size,
+                                    o->amsgrad ? it->second.vmax->ptr : nullptr});
         sizes.push_back(p->size);
         touched.push_back(p->st);
         tab_ids.push_back(p->id);
@@ -1165,16 +1234,19 @@ TS_API float ts_adam_learning_rate(const ts_adam* o) { return o ? o->lr : 0.0f; 
 TS_API void ts_adam_set_learning_rate(ts_adam* o, float lr) { if (o) o->lr = lr; }
 TS_API unsigned long long ts_adam_step_count(const ts_adam* o) { return o ? o->step_count : 0; }
 
-static ts_tensor* state_view(const ts_adam* o, const ts_tensor* p, bool second) {
+static ts_tensor* state_view(const ts_adam* o, const ts_tensor* p, int which) {
     if (!o || !p) return nullptr;
     auto it = o->states.find(p->t->id);
     if (it == o->states.end()) return nullptr;
+    StorageP st = which == 0 ? it->second.m : which == 1 ? it->second.v : it->second.vmax;
+    if (!st) return nullptr;
     auto t = std::make_shared<TensorImpl>(p->t->dims);
-    t->st = second ? it->second.v : it->second.m;
+    t->st = st;
     return wrap(t);
 }
-TS_API ts_tensor* ts_adam_state_m(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, false); }
-TS_API ts_tensor* ts_adam_state_v(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, true); }
+TS_API ts_tensor* ts_adam_state_m(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 0); }
+TS_API ts_tensor* ts_adam_state_v(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 1); }
+TS_API ts_tensor* ts_adam_state_v_hat_max(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 2); }
 
 // ====================================================================== C ABI: data parallel
 TS_API bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]) {

@@ -34,10 +34,8 @@ class Optimizer:
 class Adam(Optimizer):
     def __init__(self, config: AdamConfig | None = None):
         self.config = config or AdamConfig()
-        if self.config.amsgrad:
-            raise TrainStationError("AMSGrad is not implemented on this path")
         c = self.config
-        h = _ffi.lib().ts_adam_new(c.learning_rate, c.beta1, c.beta2, c.eps, c.weight_decay)
+        h = _ffi.lib().ts_adam_new_amsgrad(c.learning_rate, c.beta1, c.beta2, c.eps, c.weight_decay, 1 if c.amsgrad else 0)
         check(h, "Adam::new")
         self._h = vp(h)
         self.grad_scale = 1.0      # 1/world after a data-parallel gradient all-reduce
@@ -100,4 +98,7 @@ class Adam(Optimizer):
         v = _ffi.lib().ts_adam_state_v(self._h, p._h)
         if not m or not v:
             raise TrainStationError("parameter is not linked to this optimizer")
-        return [Tensor(m), Tensor(v)]
+        out = [Tensor(m), Tensor(v)]
+        if self.config.amsgrad:   # v_hat_max (adam/mod.rs:130-150 ParameterState)
+            out.append(Tensor(_ffi.lib().ts_adam_state_v_hat_max(self._h, p._h)))
+        return out

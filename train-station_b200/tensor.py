@@ -84,6 +84,15 @@ class Tensor:
         return Tensor(_ffi.lib().ts_tensor_from_slice(a.ctypes.data_as(vp), d, r))
 
     @staticmethod
+    def randn(shape_dims: Sequence[int], seed: Optional[int] = None) -> "Tensor":
+        """init/random.rs:231-236: with a seed, the reference's own stream value for value (xorshift64 and
+        Box-Muller, generated on the host); without one, a clock-derived seed."""
+        d, r = _dims(shape_dims)
+        if seed is None:
+            return Tensor(_ffi.lib().ts_tensor_randn(d, r, 0, 0))
+        return Tensor(_ffi.lib().ts_tensor_randn(d, r, int(seed) & 0xFFFFFFFFFFFFFFFF, 1))
+
+    @staticmethod
     def from_pinned_async(pinned: "PinnedBuffer", shape_dims: Sequence[int]) -> "Tensor":
         """Upload from page-locked memory on the copy stream; overlaps kernels already queued."""
         d, r = _dims(shape_dims)
