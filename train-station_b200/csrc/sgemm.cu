@@ -16,10 +16,58 @@ namespace k {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 8, kThreads = 256;
+constexpr int BM = 128, BN = 128, BK = 16, kThreads = 256;
+
+// One operand tile (128 rows or columns x 16 k) from global memory into 8 registers per thread, and from there into
+// shared memory as [k][128].  K_CONTIG: the operand is stored with k contiguous (A not transposed, B transposed):
+// a thread takes 4 consecutive k of one row and scatters them; otherwise the 128-wide dimension is contiguous and a
+// thread takes 4 consecutive elements of one k row.  The vector path needs an aligned base, a leading dimension that
+// is a multiple of 4 and a tile that lies inside the matrix; edge tiles and odd pitches take scalar guarded loads.
+template <bool K_CONTIG>
+__device__ __forceinline__ void tile_load(float (&r)[8], const float* __restrict__ base, size_t ld, size_t x0, size_t X, size_t k0, size_t K,
+                                          bool vec) {
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (K_CONTIG) {
+            const size_t x = x0 + t / 4 + 64 * h, p = k0 + (t % 4) * 4;
+            if (vec && x < X && p + 4 <= K) {
+                const float4 v = *reinterpret_cast<const float4*>(base + x * ld + p);
+                r[4 * h] = v.x; r[4 * h + 1] = v.y; r[4 * h + 2] = v.z; r[4 * h + 3] = v.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) r[4 * h + e] = (x < X && p + e < K) ? base[x * ld + p + e] : 0.0f;
+            }
+        } else {
+            const size_t p = k0 + t / 32 + 8 * h, x = x0 + (t % 32) * 4;
+            if (vec && p < K && x + 4 <= X) {
+                const float4 v = *reinterpret_cast<const float4*>(base + p * ld + x);
+                r[4 * h] = v.x; r[4 * h + 1] = v.y; r[4 * h + 2] = v.z; r[4 * h + 3] = v.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) r[4 * h + e] = (p < K && x + e < X) ? base[p * ld + x + e] : 0.0f;
+            }
+        }
+    }
+}
+template <bool K_CONTIG>
+__device__ __forceinline__ void tile_store(float (*sm)[BM], const float (&r)[8]) {
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (K_CONTIG) {
+            const int x = t / 4 + 64 * h, kc = (t % 4) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sm[kc + e][x] = r[4 * h + e];
+        } else {
+            const int kr = t / 32 + 8 * h, x = (t % 32) * 4;
+            *reinterpret_cast<float4*>(&sm[kr][x]) = make_float4(r[4 * h], r[4 * h + 1], r[4 * h + 2], r[4 * h + 3]);
+        }
+    }
+}
 
 template <bool TA, bool TB, bool HAS_TAIL>
-__global__ void __launch_bounds__(kThreads) sgemm_kernel(GemmArgs g) {
+__global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
     __shared__ __align__(16) float As[2][BK][BM];
     __shared__ __align__(16) float Bs[2][BK][BN];
     const int t = threadIdx.x;
@@ -34,66 +82,52 @@ __global__ void __launch_bounds__(kThreads) sgemm_kernel(GemmArgs g) {
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
     // which of this thread's 8 columns are reference "tail" columns (mul+add instead of fma)
-    bool tailc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        size_t col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
-        tailc[j] = HAS_TAIL && col >= N / 8 * 8;
-    }
+    // A thread's columns are two aligned groups of four, and the boundary N/8*8 is a multiple of 8: a group is tail or not as a whole.
+    const bool tail_lo = HAS_TAIL && n0 + tx * 4 >= N / 8 * 8;
+    const bool tail_hi = HAS_TAIL && n0 + 64 + tx * 4 >= N / 8 * 8;
 
-    float ra[4], rb[4];
+    // A is [M][K] (k contiguous) unless TA, then [K][M]; B is [K][N] unless TB, then [N][K] (k contiguous)
+    const size_t lda = TA ? M : K, ldb = TB ? K : N;
+    const bool vec_a = (reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && lda % 4 == 0;
+    const bool vec_b = (reinterpret_cast<uintptr_t>(g.b) & 15) == 0 && ldb % 4 == 0;
+    float ra[8], rb[8];
     auto load_tiles = [&](size_t k0) {
-        if (TA) {  // A stored [K][M]: M contiguous
-            int kr = t / 32, mc = (t % 32) * 4;
-            size_t p = k0 + kr;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                size_t i = m0 + mc + e;
-                ra[e] = (p < K && i < M) ? g.a[p * M + i] : 0.0f;
-            }
-        } else {   // A stored [M][K]: K contiguous
-            int mr = t / 2, kc = (t % 2) * 4;
-            size_t i = m0 + mr;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                size_t p = k0 + kc + e;
-                ra[e] = (p < K && i < M) ? g.a[i * K + p] : 0.0f;
-            }
-        }
-        if (TB) {  // B stored [N][K]: K contiguous
-            int nr = t / 2, kc = (t % 2) * 4;
-            size_t j = n0 + nr;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                size_t p = k0 + kc + e;
-                rb[e] = (p < K && j < N) ? g.b[j * K + p] : 0.0f;
-            }
-        } else {   // B stored [K][N]: N contiguous
-            int kr = t / 32, nc = (t % 32) * 4;
-            size_t p = k0 + kr;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                size_t j = n0 + nc + e;
-                rb[e] = (p < K && j < N) ? g.b[p * N + j] : 0.0f;
-            }
-        }
+        tile_load<!TA>(ra, g.a, lda, m0, M, k0, K, vec_a);
+        tile_load<TB>(rb, g.b, ldb, n0, N, k0, K, vec_b);
     };
     auto store_tiles = [&](int buf) {
-        if (TA) {
-            int kr = t / 32, mc = (t % 32) * 4;
-            *reinterpret_cast<float4*>(&As[buf][kr][mc]) = make_float4(ra[0], ra[1], ra[2], ra[3]);
-        } else {
-            int mr = t / 2, kc = (t % 2) * 4;
+        tile_store<!TA>(As[buf], ra);
+        tile_store<TB>(Bs[buf], rb);
+    };
+    auto k_step = [&](int buf, int p) {
+        float4 a0 = *reinterpret_cast<const float4*>(&As[buf][p][ty * 4]);
+        float4 a1 = *reinterpret_cast<const float4*>(&As[buf][p][64 + ty * 4]);
+        float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][p][tx * 4]);
+        float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][p][64 + tx * 4]);
+        float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        if (HAS_TAIL && (tail_lo || tail_hi)) {
+            // only threads of the last column block get here: a rounded multiply, then an add (kernels.rs:312-335)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) As[buf][kc + e][mr] = ra[e];
-        }
-        if (TB) {
-            int nr = t / 2, kc = (t % 2) * 4;
+            for (int half = 0; half < 2; ++half) {
+                if (half == 0 ? tail_lo : tail_hi) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) Bs[buf][kc + e][nr] = rb[e];
+                    for (int i = 0; i < 8; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            acc[i][half * 4 + j] = __fadd_rn(acc[i][half * 4 + j], __fmul_rn(av[i], bv[half * 4 + j]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[i][half * 4 + j] = fmaf(av[i], bv[half * 4 + j], acc[i][half * 4 + j]);
+                }
+            }
         } else {
-            int kr = t / 32, nc = (t % 32) * 4;
-            *reinterpret_cast<float4*>(&Bs[buf][kr][nc]) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
     };
 
@@ -104,23 +138,16 @@ __global__ void __launch_bounds__(kThreads) sgemm_kernel(GemmArgs g) {
     }
     __syncthreads();
     for (size_t kt = 0; kt < ktiles; ++kt) {
-        int buf = (int)(kt & 1);
+        const int buf = (int)(kt & 1);
+        // the next tile's loads are issued a whole tile (16 k steps, about a thousand instructions) ahead of their use
         if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+        if ((kt + 1) * BK <= K) {
 #pragma unroll
-        for (int p = 0; p < BK; ++p) {
-            float4 a0 = *reinterpret_cast<const float4*>(&As[buf][p][ty * 4]);
-            float4 a1 = *reinterpret_cast<const float4*>(&As[buf][p][64 + ty * 4]);
-            float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][p][tx * 4]);
-            float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][p][64 + tx * 4]);
-            float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (HAS_TAIL && tailc[j]) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
-                    else acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-                }
+            for (int p = 0; p < BK; ++p) k_step(buf, p);
+        } else {
+            // last, partial tile: only the k that exist enter the chain (a padded fma(0, 0, acc) would turn -0 into +0)
+            const int pmax = (int)(K - kt * BK);
+            for (int p = 0; p < pmax; ++p) k_step(buf, p);
         }
         if (kt + 1 < ktiles) store_tiles(buf ^ 1);
         __syncthreads();

@@ -231,17 +231,27 @@ __global__ void __launch_bounds__(kShortThreads) softmax_short_kernel(const floa
         __syncthreads();
         if (row0 + step < rows) Tile::fetch(nx, x + (row0 + step) * reduce, count(row0 + step));
         if ((int)threadIdx.x < nrows) {
+            // the row lives in registers between its one read and one write of the tile
             float* col = tile + threadIdx.x;
+            float v[RMAX];
             float mx = -INFINITY;
-            for (int j = 0; j < reduce; ++j) { float a = col[j * (TR + 1)]; if (a > mx) mx = a; }
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j) {
+                v[j] = j < reduce ? col[j * (TR + 1)] : -INFINITY;
+                if (v[j] > mx) mx = v[j];
+            }
             float sum = 0.0f;   // sequential, the reference's order
-            for (int j = 0; j < reduce; ++j) {
-                float e = expf(__fsub_rn(col[j * (TR + 1)], mx));
-                col[j * (TR + 1)] = e;
-                sum = __fadd_rn(sum, e);
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j) {
+                if (j < reduce) {
+                    v[j] = expf(__fsub_rn(v[j], mx));
+                    sum = __fadd_rn(sum, v[j]);
+                }
             }
             const float inv = __fdiv_rn(1.0f, sum);
-            for (int j = 0; j < reduce; ++j) col[j * (TR + 1)] = __fmul_rn(col[j * (TR + 1)], inv);
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j)
+                if (j < reduce) col[j * (TR + 1)] = __fmul_rn(v[j], inv);
         }
         __syncthreads();
         Tile::store(tile, y + row0 * reduce, nelem, reduce);
