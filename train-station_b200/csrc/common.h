@@ -97,6 +97,9 @@ bool div_bwd(const float* a, const float* b, const float* go, float* ga, float* 
 bool scale(const float* x, float alpha, float* o, size_t n, cudaStream_t s);
 bool fill(float* o, float v, size_t n, cudaStream_t s);
 bool fill_from_scalar(float* o, const float* scalar, float scale, size_t n, cudaStream_t s);
+bool sqdiff(const float* a, const float* b, float* o, size_t n, cudaStream_t s);   // (a - b)^2, both steps rounded
+// gi = (scale * (*upstream)) * (2 * x): ReduceMean / ReduceSum backward followed by PowScalar(2) backward.
+bool square_bwd_scalar(const float* x, const float* upstream, float scale, float* gi, size_t n, cudaStream_t s);
 // gy = ((inv_n) * (*upstream)) * (2 * (y - t)): ReduceMean -> PowScalar(2) -> Sub in one pass.
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s);
 // op codes: enum ts_unary_op of the public header; p is the slope, scalar or exponent

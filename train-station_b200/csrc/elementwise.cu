@@ -177,6 +177,13 @@ struct MseGradF {
     }
 };
 
+// (a - b)^2 with the difference and the square rounded separately, as sub_tensor followed by pow_scalar(2.0)
+struct SqDiffF { __device__ void apply(const float* x, float* o) const { float d = __fsub_rn(x[0], x[1]); o[0] = __fmul_rn(d, d); } };
+// (scale * upstream) * (2 * x): ReduceMean / ReduceSum backward followed by PowScalar(2) backward in one pass
+struct SquareBwdScalarF {
+    const float* upstream; float scale;
+    __device__ void apply(const float* x, float* o) const { o[0] = __fmul_rn(__fmul_rn(scale, __ldg(upstream)), __fmul_rn(2.0f, x[0])); }
+};
 // ---- unary and scalar ops beside the MLP path (tensor/ops/{exp,log,sqrt,tanh,sigmoid,leaky_relu,pow}.rs and
 // the *_scalar variants of add/sub/mul/div).  The transcendental functions are CUDA's full-precision expf, logf,
 // tanhf and powf (1-4 ulp from the host libm the reference calls); every other step is one rounded operation.
@@ -293,6 +300,11 @@ bool split_tf32(const float* x, float* hi, float* lo, size_t n, cudaStream_t s) 
     return launch_ew(Ptrs<1, 2>{{x}, {hi, lo}}, n, SplitTf32F{}, s);
 }
 bool round_to_tf32(const float* x, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, RoundTf32F{}, s); }
+bool sqdiff(const float* a, const float* b, float* o, size_t n, cudaStream_t s) { return launch_ew(Ptrs<2, 1>{{a, b}, {o}}, n, SqDiffF{}, s); }
+bool square_bwd_scalar(const float* x, const float* upstream, float scale, float* gi, size_t n, cudaStream_t s) {
+    if (!upstream) { set_error("square_bwd_scalar: null upstream"); return false; }
+    return launch_ew(Ptrs<1, 1>{{x}, {gi}}, n, SquareBwdScalarF{upstream, scale}, s);
+}
 bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {
     if (!upstream) { set_error("mse_grad: null upstream"); return false; }
     return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n}, s);

@@ -68,14 +68,27 @@ struct PendingGemm {
     bool relu = false;
 };
 
+// An elementwise result that has been requested but not launched, so that the MSE spelling
+// pred.sub_tensor(target).pow_scalar(2.0).mean() and its backward run as one pass each (the difference and its
+// square are only written to memory if something else reads them):
+//   Diff        a - b
+//   SqDiff      (a - b) * (a - b)
+//   ScalarFill  scale * a[0] in every element (the gradient ReduceMean / ReduceSum hand to their input)
+struct PendingEw {
+    enum Kind { Diff, SqDiff, ScalarFill } kind;
+    TensorP a, b;
+    float scale = 1.0f;
+};
+
 static std::atomic<uint64_t> g_next_id{1};
 
 struct TensorImpl {
     uint64_t id;
     std::vector<size_t> dims;
     size_t size = 1;
-    StorageP st;                          // null while `pending` is set
+    StorageP st;                          // null while `pending` or `pending_ew` is set
     std::unique_ptr<PendingGemm> pending;
+    std::unique_ptr<PendingEw> pending_ew;
     bool requires_grad = false;
     explicit TensorImpl(const std::vector<size_t>& d) : id(g_next_id.fetch_add(1)), dims(d) {
         for (size_t x : d) size *= x;
@@ -152,6 +165,26 @@ static bool tf32_split_operand(DeviceCtx* c, const TensorP& t, const float** hi,
 }
 
 static bool materialize(const TensorP& t, bool for_gemm) {
+    if (t->pending_ew) {
+        DeviceCtx* c = ctx();
+        if (!c) return false;
+        PendingEw& p = *t->pending_ew;
+        const float* a = rptr(p.a);
+        const float* b = p.b ? rptr(p.b) : nullptr;
+        if (!a || (p.b && !b)) return false;
+        StorageP st = new_storage(c, t->size);
+        if (!st) return false;
+        bool ok = false;
+        switch (p.kind) {
+            case PendingEw::Diff: ok = k::binary(1, a, b, st->ptr, t->size, c->compute); break;
+            case PendingEw::SqDiff: ok = k::sqdiff(a, b, st->ptr, t->size, c->compute); break;
+            case PendingEw::ScalarFill: ok = k::fill_from_scalar(st->ptr, a, p.scale, t->size, c->compute); break;
+        }
+        if (!ok) return false;
+        t->st = st;
+        t->pending_ew.reset();
+        return true;
+    }
     if (!t->pending) return t->st != nullptr;
     DeviceCtx* c = ctx();
     if (!c) return false;
@@ -222,18 +255,33 @@ static bool grad_on() { return g_no_grad_depth == 0; }
 static void register_pending(const TensorP& t) {
     if (g_pending_registry.size() > 4096) {
         auto& v = g_pending_registry;
-        v.erase(std::remove_if(v.begin(), v.end(), [](const std::weak_ptr<TensorImpl>& w) { auto s = w.lock(); return !s || !s->pending; }), v.end());
+        v.erase(std::remove_if(v.begin(), v.end(),
+                               [](const std::weak_ptr<TensorImpl>& w) { auto s = w.lock(); return !s || (!s->pending && !s->pending_ew); }),
+                v.end());
     }
     g_pending_registry.push_back(t);
 }
-// Before any in-place write: launch what still depends on the old contents.
-static bool flush_pending() {
+// Does the value of t depend on one of the storages in `written`?
+static bool reads_any(const TensorP& t, const std::unordered_set<const Storage*>& written) {
+    if (!t) return false;
+    if (t->pending) {
+        const PendingGemm& p = *t->pending;
+        return reads_any(p.a, written) || reads_any(p.b, written) || reads_any(p.bias, written) || reads_any(p.mask, written);
+    }
+    if (t->pending_ew) return reads_any(t->pending_ew->a, written) || reads_any(t->pending_ew->b, written);
+    return t->st && written.count(t->st.get()) != 0;
+}
+// Before an in-place write to the storages in `written`: launch every deferred operation that reads one of them,
+// so that it sees the old contents.  Deferred operations on other data stay deferred.
+static bool flush_pending(const std::unordered_set<const Storage*>& written) {
     auto reg = std::move(g_pending_registry);
     g_pending_registry.clear();
     bool ok = true;
     for (auto& w : reg) {
         TensorP t = w.lock();
-        if (t && t->pending) ok = materialize(t) && ok;
+        if (!t || (!t->pending && !t->pending_ew)) continue;
+        if (reads_any(t, written)) ok = materialize(t) && ok;
+        else g_pending_registry.push_back(w);
     }
     return ok;
 }
@@ -507,6 +555,25 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
         case Op::PowScalar: {
             if (!nd.needs[0]) return true;
             if (!nd.s0.check("pow_scalar")) return false;
+            if (fusion_enabled() && go->pending_ew && go->pending_ew->kind == PendingEw::ScalarFill) {
+                // The upstream gradient is scale * u in every element (it comes from mean() or sum()) and has not been
+                // written out: go * (2 * x) = (scale * u) * (2 * x) in one pass, and when x itself is a deferred
+                // difference a - b, straight from a and b.  Same operations, same order, same bits as the unfused chain.
+                const float* up = rptr(go->pending_ew->a);
+                const float scale = go->pending_ew->scale;
+                TensorP r = up ? new_tensor(c, go->dims) : nullptr;
+                if (!r) return false;
+                const TensorP& x = nd.s0.t;
+                if (x->pending_ew && x->pending_ew->kind == PendingEw::Diff) {
+                    const float *pa = rptr(x->pending_ew->a), *pb = rptr(x->pending_ew->b);
+                    if (!pa || !pb || !k::mse_grad(pa, pb, up, scale, r->st->ptr, r->size, s)) return false;
+                } else {
+                    const float* px = rptr(x);
+                    if (!px || !k::square_bwd_scalar(px, up, scale, r->st->ptr, r->size, s)) return false;
+                }
+                gin[0] = r;
+                return true;
+            }
             const float *x = rptr(nd.s0.t), *gp = rptr(go);
             TensorP r = (x && gp) ? new_tensor(c, go->dims) : nullptr;
             if (!r || !k::square_bwd(x, gp, r->st->ptr, r->size, s)) return false;
@@ -547,11 +614,21 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
         case Op::ReduceMean: {
             // grad_fn/reductions/sum.rs:4-16, mean.rs:4-30: fill with upstream, or (1/numel as f32) * upstream.
             if (!nd.needs[0]) return true;
+            size_t n_in = 1;
+            for (size_t d : nd.dims0) n_in *= d;
+            float scale = 1.0f;
+            if (nd.op == Op::ReduceMean) scale = n_in > 0 ? 1.0f / (float)n_in : 0.0f;
+            if (fusion_enabled() && n_in > 0) {
+                // deferred: whoever consumes this gradient either folds the constant in or has it written out
+                auto r = std::make_shared<TensorImpl>(nd.dims0);
+                r->pending_ew.reset(new PendingEw{PendingEw::ScalarFill, go, nullptr, scale});
+                register_pending(r);
+                gin[0] = r;
+                return true;
+            }
             const float* gp = rptr(go);
             TensorP r = gp ? new_tensor(c, nd.dims0) : nullptr;
             if (!r) return false;
-            float scale = 1.0f;
-            if (nd.op == Op::ReduceMean) scale = r->size > 0 ? 1.0f / (float)r->size : 0.0f;
             if (!k::fill_from_scalar(r->st->ptr, gp, scale, r->size, s)) return false;
             gin[0] = r;
             return true;
@@ -813,7 +890,7 @@ TS_API bool ts_tensor_to_host(ts_tensor* t, float* out) {
 }
 TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
     if (!t || (!host && t->t->size)) { set_error("ts_tensor_copy_from_host: null argument"); return false; }
-    if (!flush_pending() || !rptr(t->t)) return false;
+    if (!rptr(t->t) || !flush_pending({t->t->st.get()})) return false;
     Storage* st = t->t->st.get();
     TS_CHECK(cudaMemcpyAsync(st->ptr, host, t->t->size * sizeof(float), cudaMemcpyHostToDevice, st->c->compute));
     TS_CHECK(cudaStreamSynchronize(st->c->compute));
@@ -823,7 +900,7 @@ TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
 }
 TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
     if (!t) { set_error("ts_tensor_fill: null tensor"); return false; }
-    if (!flush_pending() || !rptr(t->t)) return false;
+    if (!rptr(t->t) || !flush_pending({t->t->st.get()})) return false;
     Storage* st = t->t->st.get();
     if (!k::fill(st->ptr, v, t->t->size, st->c->compute)) return false;
     st->version++;
@@ -844,7 +921,12 @@ static ts_tensor* binary_op(ts_tensor* ha, ts_tensor* hb, int op, const char* na
     TensorP a = ha->t, b = hb->t;
     TensorP out;
     bool track = grad_on() && (a->requires_grad || b->requires_grad);
-    if (same_dims(a->dims, b->dims)) {
+    if (same_dims(a->dims, b->dims) && op == 1 && fusion_enabled() && a->size > 0) {
+        // the difference is deferred: squared and averaged (the MSE spelling) it never has to be written out
+        out = std::make_shared<TensorImpl>(a->dims);
+        out->pending_ew.reset(new PendingEw{PendingEw::Diff, a, b});
+        register_pending(out);
+    } else if (same_dims(a->dims, b->dims)) {
         const float *pa = rptr(a), *pb = rptr(b);
         out = (pa && pb) ? new_tensor(c, a->dims) : nullptr;
         if (!out || !k::binary(op, pa, pb, out->st->ptr, out->size, c->compute)) return nullptr;
@@ -1026,9 +1108,16 @@ TS_API ts_tensor* ts_tensor_pow_scalar(ts_tensor* hx, float exponent) {
     DeviceCtx* c = ctx();
     if (!c) return nullptr;
     TensorP x = hx->t;
-    const float* px = rptr(x);
-    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
-    if (!out || !k::square(px, out->st->ptr, out->size, c->compute)) return nullptr;
+    TensorP out;
+    if (fusion_enabled() && x->pending_ew && x->pending_ew->kind == PendingEw::Diff) {
+        out = std::make_shared<TensorImpl>(x->dims);   // (a - b)^2, still deferred
+        out->pending_ew.reset(new PendingEw{PendingEw::SqDiff, x->pending_ew->a, x->pending_ew->b});
+        register_pending(out);
+    } else {
+        const float* px = rptr(x);
+        out = px ? new_tensor(c, x->dims) : nullptr;
+        if (!out || !k::square(px, out->st->ptr, out->size, c->compute)) return nullptr;
+    }
     if (grad_on() && x->requires_grad) {
         Node nd;
         nd.op = Op::PowScalar;
@@ -1047,9 +1136,17 @@ static ts_tensor* reduce_all(ts_tensor* hx, bool mean) {
     DeviceCtx* c = ctx();
     if (!c) return nullptr;
     TensorP x = hx->t;
-    const float* px = rptr(x);
-    TensorP out = px ? new_tensor(c, {1}) : nullptr;
-    if (!out || !k::sum(px, out->st->ptr, x->size, mean, c->reduce_scratch, c->compute)) return nullptr;
+    TensorP out;
+    if (mean && fusion_enabled() && x->pending_ew && x->pending_ew->kind == PendingEw::SqDiff) {
+        // mean((a - b)^2) straight from a and b: the same two-stage tree as sum() over the squared differences
+        const float *pa = rptr(x->pending_ew->a), *pb = rptr(x->pending_ew->b);
+        out = (pa && pb) ? new_tensor(c, {1}) : nullptr;
+        if (!out || !k::mse_loss(pa, pb, out->st->ptr, x->size, c->reduce_scratch, c->compute)) return nullptr;
+    } else {
+        const float* px = rptr(x);
+        out = px ? new_tensor(c, {1}) : nullptr;
+        if (!out || !k::sum(px, out->st->ptr, x->size, mean, c->reduce_scratch, c->compute)) return nullptr;
+    }
     // The reference registers these nodes even under NoGradTrack (reductions/sum.rs:131, mean.rs:99).
     if (x->requires_grad) {
         Node nd;
@@ -1136,7 +1233,6 @@ TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
 TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad_scale) {
     if (!o || (n > 0 && !params)) { set_error("adam step: null argument"); return false; }
     DeviceCtx* c = o->c;
-    if (!flush_pending()) return false;
     o->step_count += 1;   // adam/mod.rs:1037
     std::vector<k::AdamTensor> tab;
     std::vector<unsigned long long> sizes;
@@ -1169,6 +1265,11 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
     }
     if (tab.empty() && !dp_join(c)) return false;
     if (!tab.empty()) {
+        {   // deferred operations that read a parameter must see its value from before this step
+            std::unordered_set<const Storage*> written;
+            for (auto& s : touched) written.insert(s.get());
+            if (!flush_pending(written)) return false;
+        }
         if (sizes != o->cached_sizes) {
             int nc = k::adam_chunk_count(sizes.data(), (int)sizes.size());
             size_t bytes = k::adam_chunk_bytes(nc);
