@@ -554,7 +554,7 @@ def run_c2(args):
 # ------------------------------------------------------------------------ single-kernel cases
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
-               "softmax_inner")
+               "softmax_inner", "transpose", "permute_021", "permute_gather")
 
 
 def run_micro(args):
@@ -655,6 +655,16 @@ def run_micro(args):
         n = outer * reduce * inner
         x, o1 = dev(rng.standard_normal(n, dtype=np.float32)), empty(n)
         launch = lambda: chk(lib.launch_softmax_kernel(x, o1, outer, reduce, inner, None), name)
+        work, unit, peak = 8.0 * n, "GB/s", peaks["hbm_gbs"]
+    elif name in ("transpose", "permute_021", "permute_gather"):
+        # [8192, 8192] -> transposed; [64, 1024, 1024] with the last two axes swapped; [256, 512, 512] -> axes (2, 0, 1)
+        shape, perm = {"transpose": ((8192, 8192), (1, 0)), "permute_021": ((64, 1024, 1024), (0, 2, 1)),
+                       "permute_gather": ((256, 512, 512), (2, 0, 1))}[name]
+        n = int(np.prod(shape))
+        x, o1 = dev(rng.standard_normal(n, dtype=np.float32)), empty(n)
+        dims = (C.c_ulonglong * len(shape))(*shape)
+        pm = (C.c_int * len(shape))(*perm)
+        launch = lambda: chk(lib.launch_permute_kernel(x, o1, dims, pm, len(shape), None), name)
         work, unit, peak = 8.0 * n, "GB/s", peaks["hbm_gbs"]
     elif name in ("colsum", "relu_backward_colsum"):
         rows, cols = (n or 16384), 8192

@@ -184,6 +184,11 @@ bool launch_softmax_kernel(const float* x, float* out, unsigned long long outer,
                            unsigned long long inner, void* stream);
 bool launch_softmax_backward_kernel(const float* y, const float* grad_out, float* grad_in, unsigned long long outer,
                                     unsigned long long reduce, unsigned long long inner, void* stream);
+/* out = in with its axes permuted (output axis i is input axis perm[i]; `dims` are the input's, rank 1..8): the
+ * contiguous result of transform/permute.rs:147-190 or transpose.rs:156-200 followed by contiguous.rs:123-160.
+ * A batched swap of the last two merged axes runs as a tiled transpose, anything else as a gather. */
+bool launch_permute_kernel(const float* in, float* out, const unsigned long long* dims, const int* perm, int rank,
+                           void* stream);
 /* reductions/sum.rs:80-143 and mean.rs:48-110: out[0] = sum(x) or sum(x)/(f32)size.
  * Deterministic two-level tree (the reference adds sequentially).  `scratch` needs
  * ts_reduce_scratch_elems() f32 elements of device memory. */
@@ -314,6 +319,15 @@ ts_tensor* ts_tensor_add_scalar(ts_tensor* x, float scalar);    /* add.rs:236-25
 ts_tensor* ts_tensor_sub_scalar(ts_tensor* x, float scalar);    /* sub.rs:264-278 */
 ts_tensor* ts_tensor_mul_scalar(ts_tensor* x, float scalar);    /* mul.rs:239-255 */
 ts_tensor* ts_tensor_div_scalar(ts_tensor* x, float scalar);    /* div.rs:247-265; a zero scalar fails */
+/* Shape and layout.  reshape shares the storage (transform/reshape.rs:139-215; one -1 is inferred); flatten, squeeze
+ * and unsqueeze are reshapes in the reference too (flatten.rs:124, squeeze.rs:184, unsqueeze.rs:218).  permute and
+ * transpose (permute.rs:147-190, transpose.rs:156-200; t() swaps the last two axes, :283-291) return the permuted
+ * contiguous copy, since tensors here carry no strides; transpose(d, d) is a detached copy as in the reference.
+ * contiguous (contiguous.rs:123-137) is a copy connected to its source in the graph. */
+ts_tensor* ts_tensor_reshape(ts_tensor* x, const long long* new_shape, int rank);
+ts_tensor* ts_tensor_permute(ts_tensor* x, const unsigned long long* order, int n);
+ts_tensor* ts_tensor_transpose(ts_tensor* x, unsigned long long dim0, unsigned long long dim1);
+ts_tensor* ts_tensor_contiguous(ts_tensor* x);
 /* The reference panics inside log() when an element is <= 0.  1 (default): ts_tensor_log waits for its kernel and
  * fails at the call, like the panic.  0: no wait; the failure is reported by the next ts_sync_stream. */
 void ts_set_domain_checks(int at_the_call);

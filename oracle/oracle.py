@@ -252,6 +252,36 @@ def softmax_backward(y, go, dim):
     return gi
 
 
+def permute(x, dims):
+    """The contiguous result of tensor/transform/permute.rs:147-190 (a strided view: output axis i walks input axis
+    dims[i]) read out in order, as contiguous.rs:205-345 does.  Pure data movement: exact."""
+    return np.ascontiguousarray(np.transpose(_c(x), tuple(int(d) for d in dims)))
+
+
+def reshape_dims(size, new_shape):
+    """transform/reshape.rs:185-215: one -1 is inferred; other entries must be positive; sizes must agree."""
+    dims, infer, known = [], None, 1
+    for i, d in enumerate(new_shape):
+        d = int(d)
+        if d == -1:
+            if infer is not None:
+                raise ValueError("Only one dimension can be -1 for automatic inference")
+            infer = i
+            dims.append(0)
+        elif d <= 0:
+            raise ValueError(f"Dimension sizes must be positive, got {d}")
+        else:
+            dims.append(d)
+            known *= d
+    if infer is not None:
+        if known == 0 or size % known != 0:
+            raise ValueError("Cannot infer dimension size")
+        dims[infer] = size // known
+    if int(np.prod(dims, dtype=np.int64)) != size:
+        raise ValueError("Cannot reshape tensor")
+    return dims
+
+
 def total(x) -> np.float32:
     x = _c(x)
     return np.float32(lib().ora_sum(_p(x), x.size))

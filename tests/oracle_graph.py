@@ -105,6 +105,24 @@ class OracleGraph:
             y = o.unary(name, x.data, p)
             saved = {"out": y, "in": x.data, None: None}[o.UNARY_SAVES[name]]
             return self._mk(y, [x], lambda g: [o.unary_backward(name, saved, g, p)])
+        if name in ("permute", "transpose", "t", "reshape", "flatten", "contiguous"):
+            x, *params = args
+            shape = x.data.shape
+            if name == "reshape" or name == "flatten":
+                new = o.reshape_dims(x.data.size, params[0] if name == "reshape" else [-1])
+                return self._mk(x.data.reshape(new), [x], lambda g: [g.reshape(shape)])       # grad_fn/transforms/reshape.rs
+            if name == "contiguous":
+                return self._mk(x.data.copy(), [x], lambda g: [g])
+            if name == "permute":
+                perm = [int(d) for d in params[0]]
+            else:
+                d0, d1 = (len(shape) - 2, len(shape) - 1) if name == "t" else (int(params[0]), int(params[1]))
+                if d0 == d1:   # transpose.rs:169-171: a detached clone
+                    return OVal(x.data.copy(), False)
+                perm = list(range(len(shape)))
+                perm[d0], perm[d1] = perm[d1], perm[d0]
+            inv = [perm.index(i) for i in range(len(perm))]
+            return self._mk(o.permute(x.data, perm), [x], lambda g: [o.permute(g, inv)])      # grad_fn/transforms/permute.rs
         if name == "softmax":
             x, dim = args
             y = o.softmax(x.data, int(dim))

@@ -77,6 +77,7 @@ SIGNATURES = {
     "launch_fill_from_scalar_kernel": (C.c_bool, [vp, vp, C.c_float, u64, vp]),
     "launch_unary_kernel": (C.c_bool, [C.c_int, vp, vp, u64, C.c_float, vp]),
     "launch_unary_backward_kernel": (C.c_bool, [C.c_int, vp, vp, vp, u64, C.c_float, vp]),
+    "launch_permute_kernel": (C.c_bool, [vp, vp, u64p, C.POINTER(C.c_int), C.c_int, vp]),
     "launch_softmax_kernel": (C.c_bool, [vp, vp, u64, u64, u64, vp]),
     "launch_softmax_backward_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, vp]),
     "ts_reduce_scratch_elems": (u64, []),
@@ -129,6 +130,10 @@ SIGNATURES = {
     "ts_tensor_sub_scalar": (vp, [vp, C.c_float]),
     "ts_tensor_mul_scalar": (vp, [vp, C.c_float]),
     "ts_tensor_div_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_reshape": (vp, [vp, C.POINTER(C.c_longlong), C.c_int]),
+    "ts_tensor_permute": (vp, [vp, u64p, C.c_int]),
+    "ts_tensor_transpose": (vp, [vp, u64, u64]),
+    "ts_tensor_contiguous": (vp, [vp]),
     "ts_set_domain_checks": (None, [C.c_int]),
     "ts_get_domain_checks": (C.c_int, []),
     "ts_tensor_sum": (vp, [vp]),

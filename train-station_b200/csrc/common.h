@@ -107,6 +107,8 @@ bool unary(int op, const float* x, float* o, size_t n, float p, cudaStream_t s);
 bool unary_bwd(int op, const float* saved, const float* go, float* gi, size_t n, float p, cudaStream_t s);
 bool softmax(const float* x, float* y, size_t outer, size_t reduce, size_t inner, cudaStream_t s);
 bool softmax_bwd(const float* y, const float* go, float* gi, size_t outer, size_t reduce, size_t inner, cudaStream_t s);
+// out = in with its axes permuted: output axis i is input axis perm[i]; dims are the input's (rank <= 8)
+bool permute(const float* in, float* out, const size_t* dims, const int* perm, int rank, cudaStream_t s);
 bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaStream_t s);
 // loss[0] = mean((y-t)^2) without materialising the difference.
 bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s);

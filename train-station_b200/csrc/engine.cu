@@ -213,7 +213,7 @@ static bool materialize(const TensorP& t, bool for_gemm) {
 }
 
 // ------------------------------------------------------------------ tape
-enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax };
+enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax, Reshape, Permute };
 
 struct Saved {
     TensorP t;
@@ -238,6 +238,7 @@ struct Node {
     std::vector<size_t> dims0, dims1;   // operand shapes
     float scalar = 0.0f;
     int code = 0;                       // Unary: the ts_unary_op; Softmax: the axis
+    std::vector<int> perm;              // Permute: output axis i is input axis perm[i]
 };
 
 struct Graph {
@@ -593,6 +594,25 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             const float* gp = rptr(go);
             TensorP r = gp ? new_tensor(c, go->dims) : nullptr;
             if (!r || !k::unary_bwd(nd.code, saved, gp, r->st->ptr, r->size, nd.scalar, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::Reshape: {
+            // grad_fn/transforms/reshape.rs: the gradient with the input's shape (same data); Contiguous is the same
+            if (!nd.needs[0]) return true;
+            gin[0] = reshaped_alias(go, nd.dims0);
+            return gin[0] != nullptr;
+        }
+        case Op::Permute: {
+            // grad_fn/transforms/permute.rs, transpose.rs: the gradient through the inverse permutation
+            if (!nd.needs[0]) return true;
+            const int rank = (int)nd.perm.size();
+            std::vector<int> inv(rank);
+            std::vector<size_t> go_dims(rank);
+            for (int i = 0; i < rank; ++i) { inv[nd.perm[i]] = i; go_dims[i] = nd.dims0[nd.perm[i]]; }
+            const float* gp = rptr(go);
+            TensorP r = gp ? new_tensor(c, nd.dims0) : nullptr;
+            if (!r || !k::permute(gp, r->st->ptr, go_dims.data(), inv.data(), rank, s)) return false;
             gin[0] = r;
             return true;
         }
@@ -1097,6 +1117,134 @@ TS_API ts_tensor* ts_tensor_softmax(ts_tensor* hx, unsigned long long dim) {
         nd.needs = {true};
         nd.dims0 = x->dims;
         nd.s0.set(out);
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+// ---- shape and layout ops.  Tensors here are always contiguous: reshape shares the storage (as the reference's
+// view does), permute / transpose produce the permuted copy at once (the reference returns a strided view and
+// copies in contiguous()).
+TS_API ts_tensor* ts_tensor_reshape(ts_tensor* hx, const long long* new_shape, int rank) {
+    if (!hx || (rank > 0 && !new_shape)) { set_error("reshape: null argument"); return nullptr; }
+    TensorP x = hx->t;
+    // transform/reshape.rs:185-215: one -1 is inferred, everything else must be positive
+    std::vector<size_t> dims((size_t)rank);
+    int infer = -1;
+    size_t known = 1;
+    for (int i = 0; i < rank; ++i) {
+        if (new_shape[i] == -1) {
+            if (infer >= 0) { set_error("Only one dimension can be -1 for automatic inference"); return nullptr; }
+            infer = i;
+        } else if (new_shape[i] <= 0) {
+            set_error("Dimension sizes must be positive, got %lld", new_shape[i]);
+            return nullptr;
+        } else {
+            dims[i] = (size_t)new_shape[i];
+            known *= dims[i];
+        }
+    }
+    if (infer >= 0) {
+        if (known == 0 || x->size % known != 0) {
+            set_error("Cannot infer dimension size: total size %zu not divisible by known size %zu", x->size, known);
+            return nullptr;
+        }
+        dims[infer] = x->size / known;
+    }
+    if (dims.empty()) dims.push_back(1);
+    size_t n = 1;
+    for (size_t d : dims) n *= d;
+    if (n != x->size) { set_error("Cannot reshape tensor of size %zu to a shape of size %zu", x->size, n); return nullptr; }   // reshape.rs:142-150
+    if (!materialize(x)) return nullptr;
+    auto out = std::make_shared<TensorImpl>(dims);
+    out->st = x->st;
+    if (x->requires_grad) {
+        Node nd;
+        nd.op = Op::Reshape;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+static ts_tensor* permute_op(const TensorP& x, const std::vector<int>& perm) {
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    const int rank = (int)perm.size();
+    std::vector<size_t> od((size_t)rank);
+    for (int i = 0; i < rank; ++i) od[i] = x->dims[perm[i]];
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, od) : nullptr;
+    if (!out || !k::permute(px, out->st->ptr, x->dims.data(), perm.data(), rank, c->compute)) return nullptr;
+    if (x->requires_grad) {
+        Node nd;
+        nd.op = Op::Permute;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.perm = perm;
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+TS_API ts_tensor* ts_tensor_permute(ts_tensor* hx, const unsigned long long* order, int n) {
+    if (!hx || (n > 0 && !order)) { set_error("permute: null argument"); return nullptr; }
+    TensorP x = hx->t;
+    const int rank = (int)x->dims.size();
+    if (n != rank) { set_error("permute order must have length equal to rank"); return nullptr; }   // permute.rs:149-153
+    if (rank > 8) { set_error("permute: rank %d not supported (up to 8)", rank); return nullptr; }
+    std::vector<int> perm((size_t)rank);
+    std::vector<bool> seen((size_t)rank, false);
+    for (int i = 0; i < rank; ++i) {
+        if (order[i] >= (unsigned long long)rank) { set_error("permute index %llu out of bounds for rank %d", order[i], rank); return nullptr; }
+        if (seen[order[i]]) { set_error("duplicate dimension %llu in permute", order[i]); return nullptr; }
+        seen[order[i]] = true;
+        perm[i] = (int)order[i];
+    }
+    return permute_op(x, perm);
+}
+
+TS_API ts_tensor* ts_tensor_transpose(ts_tensor* hx, unsigned long long dim0, unsigned long long dim1) {
+    if (!hx) { set_error("transpose: null tensor"); return nullptr; }
+    TensorP x = hx->t;
+    const size_t rank = x->dims.size();
+    if (dim0 >= rank) { set_error("dim0 %llu out of bounds for tensor with rank %zu", dim0, rank); return nullptr; }   // transpose.rs:157-168
+    if (dim1 >= rank) { set_error("dim1 %llu out of bounds for tensor with rank %zu", dim1, rank); return nullptr; }
+    if (rank > 8) { set_error("transpose: rank %zu not supported (up to 8)", rank); return nullptr; }
+    if (dim0 == dim1) {
+        // transpose.rs:169-171 returns self.clone(): a copy with no gradient history
+        DeviceCtx* c = ctx();
+        const float* px = c ? rptr(x) : nullptr;
+        TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+        if (!out) return nullptr;
+        if (x->size && !cuda_ok(cudaMemcpyAsync(out->st->ptr, px, x->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "clone")) return nullptr;
+        return wrap(out);
+    }
+    std::vector<int> perm(rank);
+    for (size_t i = 0; i < rank; ++i) perm[i] = (int)i;
+    std::swap(perm[dim0], perm[dim1]);
+    return permute_op(x, perm);
+}
+
+// contiguous.rs:123-137: for a contiguous tensor, a copy that stays connected to its source in the graph
+TS_API ts_tensor* ts_tensor_contiguous(ts_tensor* hx) {
+    if (!hx) { set_error("contiguous: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+    if (!out) return nullptr;
+    if (x->size && !cuda_ok(cudaMemcpyAsync(out->st->ptr, px, x->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "contiguous")) return nullptr;
+    if (x->requires_grad) {
+        Node nd;
+        nd.op = Op::Reshape;   // the gradient passes through unchanged (GradFn::Contiguous)
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
         record(out, std::move(nd));
     }
     return wrap(out);

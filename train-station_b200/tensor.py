@@ -225,6 +225,59 @@ class Tensor:
         """Raises where the reference panics: a zero scalar (div.rs:511-514)."""
         return Tensor(_ffi.lib().ts_tensor_div_scalar(self._h, float(scalar)))
 
+    # shape and layout (tensor/transform/{reshape,flatten,squeeze,unsqueeze,transpose,permute,contiguous}.rs)
+    def reshape(self, new_shape: Sequence[int]) -> "Tensor":
+        """reshape.rs:139-215: shares the storage; one dimension may be -1."""
+        arr = (C.c_longlong * max(len(new_shape), 1))(*[int(d) for d in new_shape])
+        return Tensor(_ffi.lib().ts_tensor_reshape(self._h, arr, len(new_shape)))
+
+    def flatten(self) -> "Tensor":                       # flatten.rs:124-126
+        return self.reshape([-1])
+
+    def squeeze(self, dim: Optional[int] = None) -> "Tensor":
+        """squeeze.rs:184-214, including its checks."""
+        dims = self.shape().dims
+        if dim is not None:
+            if not 0 <= dim < len(dims):
+                raise TrainStationError(f"Dimension {dim} out of bounds")
+            if dims[dim] != 1:
+                raise TrainStationError(f"Cannot squeeze dimension {dim} with size {dims[dim]}")
+            new = [s for i, s in enumerate(dims) if i != dim]
+        else:
+            new = [s for s in dims if s != 1]
+        return self.reshape(new or [1])
+
+    def unsqueeze(self, dim: int) -> "Tensor":           # unsqueeze.rs:218-224
+        dims = list(self.shape().dims)
+        if not 0 <= dim <= len(dims):
+            raise TrainStationError(f"Dimension {dim} out of bounds")
+        dims.insert(dim, 1)
+        return self.reshape(dims)
+
+    def transpose(self, dim0: int, dim1: int) -> "Tensor":
+        """transpose.rs:156-200; the permuted copy is contiguous here (the reference returns a strided view)."""
+        if dim0 < 0 or dim1 < 0:
+            raise TrainStationError("transpose axes are unsigned")
+        return Tensor(_ffi.lib().ts_tensor_transpose(self._h, int(dim0), int(dim1)))
+
+    def t(self) -> "Tensor":                             # transpose.rs:283-291
+        rank = self.shape().rank()
+        if rank < 2:
+            raise TrainStationError(f"Matrix transpose requires at least 2 dimensions, got {rank}")
+        return self.transpose(rank - 2, rank - 1)
+
+    def permute(self, dims: Sequence[int]) -> "Tensor":  # permute.rs:147-190
+        if any(d < 0 for d in dims):
+            raise TrainStationError("permute axes are unsigned")
+        arr = (C.c_ulonglong * max(len(dims), 1))(*[int(d) for d in dims])
+        return Tensor(_ffi.lib().ts_tensor_permute(self._h, arr, len(dims)))
+
+    def contiguous(self) -> "Tensor":                    # contiguous.rs:123-137
+        return Tensor(_ffi.lib().ts_tensor_contiguous(self._h))
+
+    def is_contiguous(self) -> bool:
+        return True
+
     # operator sugar: tensor/core/operators.rs forwards Tensor (op) Tensor to the *_tensor methods (:120-410),
     # Tensor (op) f32 to the *_scalar methods (:418-660) and -Tensor to mul_scalar(-1.0) (:690-705)
     @staticmethod
