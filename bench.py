@@ -554,7 +554,8 @@ def run_c2(args):
 # ------------------------------------------------------------------------ single-kernel cases
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
-               "softmax_inner", "transpose", "permute_021", "permute_gather")
+               "softmax_inner", "transpose", "permute_021", "permute_gather", "reduce_rows", "reduce_cols", "reduce_all_max",
+               "reduce_middle")
 
 
 def run_micro(args):
@@ -666,6 +667,17 @@ def run_micro(args):
         pm = (C.c_int * len(shape))(*perm)
         launch = lambda: chk(lib.launch_permute_kernel(x, o1, dims, pm, len(shape), None), name)
         work, unit, peak = 8.0 * n, "GB/s", peaks["hbm_gbs"]
+    elif name in ("reduce_rows", "reduce_cols", "reduce_all_max", "reduce_middle"):
+        # sum over the last axis, over the first axis, max of everything, sum over the middle axis of [64, 256, 4096]
+        shape, axes, op = {"reduce_rows": ((16384, 4096), (1,), 0), "reduce_cols": ((16384, 4096), (0,), 0),
+                           "reduce_all_max": ((1 << 26,), (0,), 1), "reduce_middle": ((64, 256, 4096), (1,), 0)}[name]
+        n = int(np.prod(shape))
+        x, o1 = dev(rng.standard_normal(n, dtype=np.float32)), empty(n)
+        sc = empty(int(lib.ts_reduce_dims_scratch_elems()))
+        dims = (C.c_ulonglong * len(shape))(*shape)
+        ax = (C.c_ulonglong * len(axes))(*axes)
+        launch = lambda: chk(lib.launch_reduce_dims_kernel(op, x, None, o1, dims, len(shape), ax, len(axes), sc, None), name)
+        work, unit, peak = 4.0 * n, "GB/s", peaks["hbm_gbs"]
     elif name in ("colsum", "relu_backward_colsum"):
         rows, cols = (n or 16384), 8192
         g, ref = dev(rng.standard_normal((rows, cols), dtype=np.float32)), dev(rng.standard_normal((rows, cols), dtype=np.float32))

@@ -189,6 +189,27 @@ bool launch_softmax_backward_kernel(const float* y, const float* grad_out, float
  * A batched swap of the last two merged axes runs as a tiled transpose, anything else as a gather. */
 bool launch_permute_kernel(const float* in, float* out, const unsigned long long* dims, const int* perm, int rank,
                            void* stream);
+/* Reduction of a contiguous tensor over a set of its axes (`axes`: n_axes axis numbers; `dims`: the input's
+ * extents, rank 1..8).  out has one element per combination of the kept axes, in their order.
+ *   op 0 sum, 1 max, 2 min, 3 sum of squares, 4 sum of squared deviations from aux[output],
+ *      5 number of elements equal to aux[output]   (aux is only read by ops 4 and 5)
+ * These are the accumulation loops of tensor/reductions/{sum.rs:250-290, max.rs:90-130, min.rs, norm.rs, var.rs,
+ * std.rs}; the scaling, square root and two-pass structure on top of them are done by the caller (the engine).
+ * `scratch`: ts_reduce_dims_scratch_elems() f32 elements.  Max and min ignore NaN as the reference's comparisons do. */
+unsigned long long ts_reduce_dims_scratch_elems(void);
+bool launch_reduce_dims_kernel(int op, const float* x, const float* aux, float* out, const unsigned long long* dims,
+                               int rank, const unsigned long long* axes, int n_axes, float* scratch, void* stream);
+/* The matching backward passes (gradtrack/grad_fn/reductions/*.rs): grad_in has the input's shape, grad_out the
+ * output's (or is a single value when grad_out_is_scalar).
+ *   mode 0 sum: grad_out[o]                      1 mean: grad_out[o] * scale, scale = 1/count
+ *   mode 2 max/min: x == a1[o] ? grad_out[o] / a2[o] : 0   (a1 the extremum, a2 the number of ties)
+ *   mode 3 norm: a1[o] > 0 ? x * (grad_out[o] / a1[o]) : 0
+ *   mode 4 var: (x - a1[o]) * (grad_out[o] * scale), a1 the mean, scale = 2/count
+ *   mode 5 std: a2[o] > 0 ? (x - a1[o]) * (grad_out[o] * scale / a2[o]) : 0, a1 the mean, a2 the std, scale = 1/count */
+bool launch_reduce_dims_backward_kernel(int mode, const float* x, const float* a1, const float* a2, const float* grad_out,
+                                        float* grad_in, const unsigned long long* dims, int rank,
+                                        const unsigned long long* axes, int n_axes, int grad_out_is_scalar, float scale,
+                                        void* stream);
 /* reductions/sum.rs:80-143 and mean.rs:48-110: out[0] = sum(x) or sum(x)/(f32)size.
  * Deterministic two-level tree (the reference adds sequentially).  `scratch` needs
  * ts_reduce_scratch_elems() f32 elements of device memory. */
@@ -328,6 +349,15 @@ ts_tensor* ts_tensor_reshape(ts_tensor* x, const long long* new_shape, int rank)
 ts_tensor* ts_tensor_permute(ts_tensor* x, const unsigned long long* order, int n);
 ts_tensor* ts_tensor_transpose(ts_tensor* x, unsigned long long dim0, unsigned long long dim1);
 ts_tensor* ts_tensor_contiguous(ts_tensor* x);
+/* Reductions over axes (tensor/reductions/*.rs): sum_dims, mean_dims, max_dims, min_dims, norm_dims, var_dims,
+ * std_dims with `keepdim`, and the whole-tensor max / min / norm / var / std (result [1]).  Variance and standard
+ * deviation are the population ones (divide by the count), as in the reference. */
+enum ts_reduce_kind {
+    TS_REDUCE_SUM = 0, TS_REDUCE_MEAN = 1, TS_REDUCE_MAX = 2, TS_REDUCE_MIN = 3, TS_REDUCE_NORM = 4,
+    TS_REDUCE_VAR = 5, TS_REDUCE_STD = 6
+};
+ts_tensor* ts_tensor_reduce_dims(ts_tensor* x, int kind, const unsigned long long* dims, int n_dims, int keepdim);
+ts_tensor* ts_tensor_reduce_all(ts_tensor* x, int kind);
 /* The reference panics inside log() when an element is <= 0.  1 (default): ts_tensor_log waits for its kernel and
  * fails at the call, like the panic.  0: no wait; the failure is reported by the next ts_sync_stream. */
 void ts_set_domain_checks(int at_the_call);

@@ -23,7 +23,7 @@ _f = C.POINTER(C.c_float)
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside it (gcc, a second or two)."""
-    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("ts_oracle.c", "ts_oracle_unary.c", "ts_oracle_variants.c", "Makefile"))
+    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("ts_oracle.c", "ts_oracle_unary.c", "ts_oracle_variants.c", "ts_oracle_reduce.c", "Makefile"))
     if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < newest:
         subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
     return _SO
@@ -102,6 +102,13 @@ def lib():
                                               C.c_float, C.c_float, C.c_uint64]
         L.ora_xorshift_u64.argtypes = [C.c_uint64, C.POINTER(C.c_uint64), sz]
         L.ora_randn.argtypes = [_f, sz, C.c_uint64]
+        szp, u8p = C.POINTER(C.c_size_t), C.POINTER(C.c_ubyte)
+        L.ora_reduce_dims.argtypes = [C.c_int, _f, _f, _f, szp, C.c_int, u8p]
+        L.ora_reduce_dims.restype = C.c_int
+        L.ora_reduce_all.argtypes = [C.c_int, _f, sz, _f]
+        L.ora_reduce_all.restype = C.c_float
+        L.ora_reduce_dims_backward.argtypes = [C.c_int, _f, _f, _f, _f, _f, szp, C.c_int, u8p, C.c_int]
+        L.ora_reduce_dims_backward.restype = C.c_int
         _lib = L
     return _lib
 
@@ -249,6 +256,63 @@ def softmax_backward(y, go, dim):
     gi = np.empty_like(y)
     o, r, i = _softmax_axes(y.shape, dim)
     lib().ora_softmax_backward(_p(y), _p(go), _p(gi), o, r, i)
+    return gi
+
+
+REDUCE = {"sum": 0, "mean": 1, "max": 2, "min": 3, "norm": 4, "var": 5, "std": 6}
+
+
+def _red_args(shape, dims):
+    rank = len(shape)
+    d = (C.c_size_t * rank)(*[int(s) for s in shape])
+    flags = [0] * rank
+    for a in dims:
+        if not 0 <= int(a) < rank:
+            raise IndexError(f"dim {a} out of bounds for rank {rank}")
+        flags[int(a)] = 1
+    return d, (C.c_ubyte * rank)(*flags), flags
+
+
+def reduce_out_shape(shape, dims, keepdim):
+    """sum.rs:236-249: a reduced axis becomes 1 (keepdim) or disappears; nothing left means [1]."""
+    flags = [i in set(int(a) for a in dims) for i in range(len(shape))]
+    out = [1 if f else s for s, f in zip(shape, flags)] if keepdim else [s for s, f in zip(shape, flags) if not f]
+    return out or [1]
+
+
+def reduce_dims(kind, x, dims, keepdim=False, want_mean=False):
+    """sum_dims / mean_dims / max_dims / min_dims / norm_dims / var_dims / std_dims of the reference."""
+    x = _c(x)
+    if len(dims) == 0:
+        raise ValueError(f"{kind}_dims requires at least one dimension")
+    d, flags, _ = _red_args(x.shape, dims)
+    oshape = reduce_out_shape(x.shape, dims, keepdim)
+    out = np.empty(oshape, np.float32)
+    mean = np.empty(oshape, np.float32)
+    st = lib().ora_reduce_dims(REDUCE[kind], _p(x), _p(out), _p(mean), d, x.ndim, flags)
+    assert st == 0
+    return (out, mean) if want_mean else out
+
+
+def reduce_all(kind, x, want_mean=False):
+    """max() / min() / norm() / var() / std() of the reference: one value, shape [1]."""
+    x = _c(x)
+    m = np.zeros(1, np.float32)
+    v = lib().ora_reduce_all(REDUCE[kind], _p(x.reshape(-1)), x.size, _p(m))
+    out = np.array([v], np.float32)
+    return (out, m) if want_mean else out
+
+
+def reduce_dims_backward(kind, x, y, mean, go, dims):
+    """dims=None means the whole-tensor form (every axis reduced)."""
+    x, go = _c(x), _c(go)
+    axes = list(range(x.ndim)) if dims is None else dims
+    d, flags, _ = _red_args(x.shape, axes)
+    gi = np.empty_like(x)
+    yp = _p(_c(y).reshape(-1)) if y is not None else None
+    mp = _p(_c(mean).reshape(-1)) if mean is not None else None
+    st = lib().ora_reduce_dims_backward(REDUCE[kind], _p(x), yp, mp, _p(go.reshape(-1)), _p(gi), d, x.ndim, flags, 1 if go.size == 1 else 0)
+    assert st == 0
     return gi
 
 

@@ -123,6 +123,15 @@ class OracleGraph:
                 perm[d0], perm[d1] = perm[d1], perm[d0]
             inv = [perm.index(i) for i in range(len(perm))]
             return self._mk(o.permute(x.data, perm), [x], lambda g: [o.permute(g, inv)])      # grad_fn/transforms/permute.rs
+        if name.endswith("_dims") and name[:-5] in o.REDUCE:       # sum_dims, mean_dims, max_dims, ...: [x, dims, keepdim]
+            kind = name[:-5]
+            x, dims, keepdim = args
+            y, mu = o.reduce_dims(kind, x.data, dims, bool(keepdim), want_mean=True)
+            return self._mk(y, [x], lambda g: [o.reduce_dims_backward(kind, x.data, y, mu, g, dims)])
+        if name in ("max", "min", "norm", "var", "std"):           # whole-tensor forms, result [1]
+            (x,) = args
+            y, mu = o.reduce_all(name, x.data, want_mean=True)
+            return self._mk(y, [x], lambda g: [o.reduce_dims_backward(name, x.data, y, mu, g, None)])
         if name == "softmax":
             x, dim = args
             y = o.softmax(x.data, int(dim))

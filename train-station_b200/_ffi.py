@@ -78,6 +78,10 @@ SIGNATURES = {
     "launch_unary_kernel": (C.c_bool, [C.c_int, vp, vp, u64, C.c_float, vp]),
     "launch_unary_backward_kernel": (C.c_bool, [C.c_int, vp, vp, vp, u64, C.c_float, vp]),
     "launch_permute_kernel": (C.c_bool, [vp, vp, u64p, C.POINTER(C.c_int), C.c_int, vp]),
+    "ts_reduce_dims_scratch_elems": (u64, []),
+    "launch_reduce_dims_kernel": (C.c_bool, [C.c_int, vp, vp, vp, u64p, C.c_int, u64p, C.c_int, vp, vp]),
+    "launch_reduce_dims_backward_kernel": (C.c_bool, [C.c_int, vp, vp, vp, vp, vp, u64p, C.c_int, u64p, C.c_int, C.c_int,
+                                                      C.c_float, vp]),
     "launch_softmax_kernel": (C.c_bool, [vp, vp, u64, u64, u64, vp]),
     "launch_softmax_backward_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, vp]),
     "ts_reduce_scratch_elems": (u64, []),
@@ -130,6 +134,8 @@ SIGNATURES = {
     "ts_tensor_sub_scalar": (vp, [vp, C.c_float]),
     "ts_tensor_mul_scalar": (vp, [vp, C.c_float]),
     "ts_tensor_div_scalar": (vp, [vp, C.c_float]),
+    "ts_tensor_reduce_dims": (vp, [vp, C.c_int, u64p, C.c_int, C.c_int]),
+    "ts_tensor_reduce_all": (vp, [vp, C.c_int]),
     "ts_tensor_reshape": (vp, [vp, C.POINTER(C.c_longlong), C.c_int]),
     "ts_tensor_permute": (vp, [vp, u64p, C.c_int]),
     "ts_tensor_transpose": (vp, [vp, u64, u64]),

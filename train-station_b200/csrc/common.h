@@ -109,6 +109,15 @@ bool softmax(const float* x, float* y, size_t outer, size_t reduce, size_t inner
 bool softmax_bwd(const float* y, const float* go, float* gi, size_t outer, size_t reduce, size_t inner, cudaStream_t s);
 // out = in with its axes permuted: output axis i is input axis perm[i]; dims are the input's (rank <= 8)
 bool permute(const float* in, float* out, const size_t* dims, const int* perm, int rank, cudaStream_t s);
+// Reduction over the axes flagged in `reduced` (one byte per input axis).  op: 0 sum, 1 max, 2 min, 3 sum of squares,
+// 4 sum of squared deviations from aux[output], 5 count of elements equal to aux[output].  scratch: reduce_dims_scratch_elems().
+size_t reduce_dims_scratch_elems();
+bool reduce_dims(int op, const float* x, const float* aux, float* out, const size_t* dims, int rank, const unsigned char* reduced,
+                 float* scratch, cudaStream_t s);
+// mode: 0 sum, 1 mean (scale = 1/count), 2 max/min (a1 extremum, a2 tie count), 3 norm (a1), 4 var (a1 mean, scale 2/n),
+// 5 std (a1 mean, a2 std, scale 1/n)
+bool reduce_dims_backward(int mode, const float* x, const float* a1, const float* a2, const float* go, float* gi, const size_t* dims,
+                          int rank, const unsigned char* reduced, bool go_is_scalar, float scale, cudaStream_t s);
 bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaStream_t s);
 // loss[0] = mean((y-t)^2) without materialising the difference.
 bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s);

@@ -213,7 +213,7 @@ static bool materialize(const TensorP& t, bool for_gemm) {
 }
 
 // ------------------------------------------------------------------ tape
-enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax, Reshape, Permute };
+enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax, Reshape, Permute, ReduceDims };
 
 struct Saved {
     TensorP t;
@@ -234,11 +234,11 @@ struct Node {
     Op op;
     std::vector<uint64_t> inputs;       // ids, positional: [a, b] or [x]
     std::vector<bool> needs;            // which inputs want a gradient
-    Saved s0, s1;                       // saved tensors (meaning depends on op)
+    Saved s0, s1, s2;                   // saved tensors (meaning depends on op)
     std::vector<size_t> dims0, dims1;   // operand shapes
     float scalar = 0.0f;
     int code = 0;                       // Unary: the ts_unary_op; Softmax: the axis
-    std::vector<int> perm;              // Permute: output axis i is input axis perm[i]
+    std::vector<int> perm;              // Permute: output axis i is input axis perm[i]; ReduceDims: 1 for each reduced axis
 };
 
 struct Graph {
@@ -594,6 +594,60 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             const float* gp = rptr(go);
             TensorP r = gp ? new_tensor(c, go->dims) : nullptr;
             if (!r || !k::unary_bwd(nd.code, saved, gp, r->st->ptr, r->size, nd.scalar, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::ReduceDims: {
+            // grad_fn/reductions/{sum,mean,max,min,norm,var,std}.rs, the *_dims variants (the whole-tensor variants are
+            // the same formulas with every axis reduced)
+            if (!nd.needs[0]) return true;
+            const int rank = (int)nd.dims0.size();
+            std::vector<unsigned char> red((size_t)rank);
+            size_t factor = 1;
+            for (int i = 0; i < rank; ++i) { red[i] = (unsigned char)nd.perm[i]; if (red[i]) factor *= nd.dims0[i]; }
+            const float* gp = rptr(go);
+            TensorP r = gp ? new_tensor(c, nd.dims0) : nullptr;
+            if (!r) return false;
+            const bool scalar_go = go->size == 1;
+            const float inv = factor > 0 ? 1.0f / (float)factor : 0.0f;
+            const float *x = nullptr, *a1 = nullptr, *a2 = nullptr;
+            TensorP counts;
+            int mode = 0;
+            float scale = 1.0f;
+            switch (nd.code) {
+                case TS_REDUCE_SUM: mode = 0; break;
+                case TS_REDUCE_MEAN: mode = 1; scale = inv; break;
+                case TS_REDUCE_MAX:
+                case TS_REDUCE_MIN: {
+                    if (!nd.s0.check("max/min") || !nd.s1.check("max/min")) return false;
+                    x = rptr(nd.s0.t); a1 = rptr(nd.s1.t);
+                    counts = (x && a1) ? new_tensor(c, nd.s1.t->dims) : nullptr;
+                    float* scratch = counts ? c->alloc.alloc(k::reduce_dims_scratch_elems() * sizeof(float)) : nullptr;
+                    if (!scratch) return false;
+                    bool ok = k::reduce_dims(5, x, a1, counts->st->ptr, nd.dims0.data(), rank, red.data(), scratch, s);
+                    c->alloc.free(scratch);
+                    if (!ok) return false;
+                    a2 = counts->st->ptr;
+                    mode = 2;
+                    break;
+                }
+                case TS_REDUCE_NORM:
+                    if (!nd.s0.check("norm") || !nd.s1.check("norm")) return false;
+                    x = rptr(nd.s0.t); a1 = rptr(nd.s1.t); mode = 3;
+                    break;
+                case TS_REDUCE_VAR:
+                    if (!nd.s0.check("var")) return false;
+                    x = rptr(nd.s0.t); a1 = rptr(nd.s2.t); mode = 4;
+                    scale = factor > 0 ? 2.0f / (float)factor : 0.0f;
+                    break;
+                case TS_REDUCE_STD:
+                    if (!nd.s0.check("std") || !nd.s1.check("std")) return false;
+                    x = rptr(nd.s0.t); a1 = rptr(nd.s2.t); a2 = rptr(nd.s1.t); mode = 5; scale = inv;
+                    break;
+                default: set_error("backward: unknown reduction"); return false;
+            }
+            if (mode >= 2 && (!x || !a1)) return false;
+            if (!k::reduce_dims_backward(mode, x, a1, a2, gp, r->st->ptr, nd.dims0.data(), rank, red.data(), scalar_go, scale, s)) return false;
             gin[0] = r;
             return true;
         }
@@ -1248,6 +1302,103 @@ TS_API ts_tensor* ts_tensor_contiguous(ts_tensor* hx) {
         record(out, std::move(nd));
     }
     return wrap(out);
+}
+
+// ---- reductions over axes: sum_dims / mean_dims / max_dims / min_dims / norm_dims / var_dims / std_dims and the
+// whole-tensor max / min / norm / var / std (every axis reduced, result [1])
+static const char* reduce_name(int kind, bool all) {
+    static const char* dims_names[] = {"sum_dims", "mean_dims", "max_dims", "min_dims", "norm_dims", "var_dims", "std_dims"};
+    static const char* all_names[] = {"sum", "mean", "max", "min", "norm", "var", "std"};
+    return (kind < 0 || kind > 6) ? "reduce" : (all ? all_names[kind] : dims_names[kind]);
+}
+
+static ts_tensor* reduce_dims_op(ts_tensor* hx, int kind, const unsigned long long* axes, int n_axes, bool keepdim, bool all) {
+    const char* name = reduce_name(kind, all);
+    if (!hx) { set_error("%s: null tensor", name); return nullptr; }
+    if (kind < TS_REDUCE_SUM || kind > TS_REDUCE_STD) { set_error("reduce: unknown kind %d", kind); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const int rank = (int)x->dims.size();
+    if (rank > 8) { set_error("%s: rank %d not supported (up to 8)", name, rank); return nullptr; }
+    std::vector<unsigned char> red((size_t)rank, all ? 1 : 0);
+    if (!all) {
+        if (n_axes <= 0 || !axes) { set_error("%s requires at least one dimension", name); return nullptr; }      // sum.rs:226
+        for (int i = 0; i < n_axes; ++i) {
+            if (axes[i] >= (unsigned long long)rank) { set_error("%s dim %llu out of bounds for rank %d", name, axes[i], rank); return nullptr; }   // sum.rs:228-235
+            red[axes[i]] = 1;
+        }
+    }
+    // output shape: a reduced axis becomes 1 (keepdim) or disappears; nothing left means [1] (sum.rs:236-249)
+    std::vector<size_t> od;
+    size_t factor = 1;
+    for (int i = 0; i < rank; ++i) {
+        if (red[i]) { factor *= x->dims[i]; if (keepdim && !all) od.push_back(1); }
+        else od.push_back(x->dims[i]);
+    }
+    if (od.empty()) od.push_back(1);
+    if ((kind == TS_REDUCE_VAR || kind == TS_REDUCE_STD) && !all && factor == 0) { set_error("reduced size must be > 0"); return nullptr; }   // std.rs:349
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, od) : nullptr;
+    if (!out) return nullptr;
+    float* scratch = c->alloc.alloc(k::reduce_dims_scratch_elems() * sizeof(float));
+    if (!scratch) return nullptr;
+    cudaStream_t s = c->compute;
+    const size_t* d = x->dims.data();
+    float* o = out->st->ptr;
+    TensorP mean_t;
+    bool ok = true;
+    switch (kind) {
+        case TS_REDUCE_SUM: ok = k::reduce_dims(0, px, nullptr, o, d, rank, red.data(), scratch, s); break;
+        case TS_REDUCE_MEAN:   // mean.rs:186-200: sum_dims, then mul_scalar(1 / count)
+            ok = k::reduce_dims(0, px, nullptr, o, d, rank, red.data(), scratch, s) &&
+                 k::scale(o, factor > 0 ? 1.0f / (float)factor : 0.0f, o, out->size, s);
+            break;
+        case TS_REDUCE_MAX: ok = k::reduce_dims(1, px, nullptr, o, d, rank, red.data(), scratch, s); break;
+        case TS_REDUCE_MIN: ok = k::reduce_dims(2, px, nullptr, o, d, rank, red.data(), scratch, s); break;
+        case TS_REDUCE_NORM:   // norm.rs: sqrt of the sum of squares
+            ok = k::reduce_dims(3, px, nullptr, o, d, rank, red.data(), scratch, s) && k::unary(TS_UNARY_SQRT, o, o, out->size, 0.0f, s);
+            break;
+        case TS_REDUCE_VAR:
+        case TS_REDUCE_STD: {
+            // var.rs / std.rs: mean = sum / n, then the sum of squared deviations / n (population variance); std = sqrt
+            mean_t = new_tensor(c, od);
+            ok = mean_t != nullptr;
+            if (ok && factor == 0) {
+                ok = k::fill(mean_t->st->ptr, 0.0f, out->size, s) && k::fill(o, 0.0f, out->size, s);   // var.rs:103-105: an empty tensor gives 0
+            } else if (ok) {
+                ok = k::reduce_dims(0, px, nullptr, mean_t->st->ptr, d, rank, red.data(), scratch, s) &&
+                     k::unary(TS_UNARY_DIV_SCALAR, mean_t->st->ptr, mean_t->st->ptr, out->size, (float)factor, s) &&
+                     k::reduce_dims(4, px, mean_t->st->ptr, o, d, rank, red.data(), scratch, s) &&
+                     k::unary(TS_UNARY_DIV_SCALAR, o, o, out->size, (float)factor, s);
+                if (ok && kind == TS_REDUCE_STD) ok = k::unary(TS_UNARY_SQRT, o, o, out->size, 0.0f, s);
+            }
+            break;
+        }
+    }
+    c->alloc.free(scratch);
+    if (!ok) return nullptr;
+    if (x->requires_grad) {   // registered whenever the input requires a gradient, as in the reference (sum.rs:292-301)
+        Node nd;
+        nd.op = Op::ReduceDims;
+        nd.code = kind;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.perm.assign(red.begin(), red.end());
+        if (kind >= TS_REDUCE_MAX) { nd.s0.set(x); nd.s1.set(out); }
+        if (mean_t) nd.s2.set(mean_t);
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+TS_API ts_tensor* ts_tensor_reduce_dims(ts_tensor* x, int kind, const unsigned long long* dims, int n_dims, int keepdim) {
+    return reduce_dims_op(x, kind, dims, n_dims, keepdim != 0, false);
+}
+TS_API ts_tensor* ts_tensor_reduce_all(ts_tensor* x, int kind) {
+    if (kind == TS_REDUCE_SUM) return ts_tensor_sum(x);
+    if (kind == TS_REDUCE_MEAN) return ts_tensor_mean(x);
+    return reduce_dims_op(x, kind, nullptr, 0, false, true);
 }
 
 TS_API ts_tensor* ts_tensor_pow_scalar(ts_tensor* hx, float exponent) {

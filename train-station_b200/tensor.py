@@ -225,6 +225,49 @@ class Tensor:
         """Raises where the reference panics: a zero scalar (div.rs:511-514)."""
         return Tensor(_ffi.lib().ts_tensor_div_scalar(self._h, float(scalar)))
 
+    # reductions over axes (tensor/reductions/*.rs); kinds as enum ts_reduce_kind
+    def _reduce_dims(self, kind: int, dims: Sequence[int], keepdim: bool) -> "Tensor":
+        if any(int(d) < 0 for d in dims):
+            raise TrainStationError("reduction axes are unsigned")
+        arr = (C.c_ulonglong * max(len(dims), 1))(*[int(d) for d in dims])
+        return Tensor(_ffi.lib().ts_tensor_reduce_dims(self._h, kind, arr, len(dims), 1 if keepdim else 0))
+
+    def sum_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":     # sum.rs:225-306
+        return self._reduce_dims(0, dims, keepdim)
+
+    def mean_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":    # mean.rs:186-215
+        return self._reduce_dims(1, dims, keepdim)
+
+    def max_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":     # max.rs:65-145
+        return self._reduce_dims(2, dims, keepdim)
+
+    def min_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":
+        return self._reduce_dims(3, dims, keepdim)
+
+    def norm_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":
+        return self._reduce_dims(4, dims, keepdim)
+
+    def var_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":
+        return self._reduce_dims(5, dims, keepdim)
+
+    def std_dims(self, dims: Sequence[int], keepdim: bool) -> "Tensor":
+        return self._reduce_dims(6, dims, keepdim)
+
+    def max(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_reduce_all(self._h, 2))
+
+    def min(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_reduce_all(self._h, 3))
+
+    def norm(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_reduce_all(self._h, 4))
+
+    def var(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_reduce_all(self._h, 5))
+
+    def std(self) -> "Tensor":
+        return Tensor(_ffi.lib().ts_tensor_reduce_all(self._h, 6))
+
     # shape and layout (tensor/transform/{reshape,flatten,squeeze,unsqueeze,transpose,permute,contiguous}.rs)
     def reshape(self, new_shape: Sequence[int]) -> "Tensor":
         """reshape.rs:139-215: shares the storage; one dimension may be -1."""
