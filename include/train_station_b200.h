@@ -392,6 +392,10 @@ unsigned long long ts_adam_step_count(const ts_adam* opt);
 ts_tensor* ts_adam_state_m(const ts_adam* opt, const ts_tensor* p);
 ts_tensor* ts_adam_state_v(const ts_adam* opt, const ts_tensor* p);
 ts_tensor* ts_adam_state_v_hat_max(const ts_adam* opt, const ts_tensor* p);   /* NULL unless amsgrad */
+/* Counters for checkpoints (optimizers/adam/serialization.rs:692-752; the moments are written through the views above). */
+void ts_adam_set_step_count(ts_adam* opt, unsigned long long n);
+unsigned long long ts_adam_param_step(const ts_adam* opt, const ts_tensor* p);
+bool ts_adam_set_param_step(ts_adam* opt, const ts_tensor* p, unsigned long long n);
 
 /* ===================================================================================
  * 5. Data parallelism: batch rows sharded over GPUs, one NCCL all-reduce of the parameter

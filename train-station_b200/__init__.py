@@ -18,6 +18,7 @@ from .device import (FP32, TF32, TF32X3, allocator_stats, cuda_device_count, cud
 from . import optim as optimizers
 from .optim import Adam, AdamConfig, Optimizer
 from . import distributed
+from . import serialization
 
 __all__ = [
     "Tensor", "Shape", "PinnedBuffer", "TrainStationError", "NoGradTrack", "with_no_grad",

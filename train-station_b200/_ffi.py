@@ -154,6 +154,9 @@ SIGNATURES = {
     "ts_adam_new": (vp, [C.c_float, C.c_float, C.c_float, C.c_float, C.c_float]),
     "ts_adam_new_amsgrad": (vp, [C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]),
     "ts_adam_state_v_hat_max": (vp, [vp, vp]),
+    "ts_adam_set_step_count": (None, [vp, u64]),
+    "ts_adam_param_step": (u64, [vp, vp]),
+    "ts_adam_set_param_step": (C.c_bool, [vp, vp, u64]),
     "ts_adam_free": (None, [vp]),
     "ts_adam_add_parameter": (C.c_bool, [vp, vp]),
     "ts_adam_step": (C.c_bool, [vp, C.POINTER(vp), C.c_int, C.c_float]),

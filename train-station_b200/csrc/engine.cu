@@ -1644,6 +1644,21 @@ static ts_tensor* state_view(const ts_adam* o, const ts_tensor* p, int which) {
     t->st = st;
     return wrap(t);
 }
+// Checkpoint support (optimizers/adam/serialization.rs:692-752, mod.rs:396-458 relink_parameters): the moments are
+// reached through the state views above; these set and read the counters.
+TS_API void ts_adam_set_step_count(ts_adam* o, unsigned long long n) { if (o) o->step_count = n; }
+TS_API unsigned long long ts_adam_param_step(const ts_adam* o, const ts_tensor* p) {
+    if (!o || !p) return 0;
+    auto it = o->states.find(p->t->id);
+    return it == o->states.end() ? 0 : it->second.step;
+}
+TS_API bool ts_adam_set_param_step(ts_adam* o, const ts_tensor* p, unsigned long long n) {
+    if (!o || !p) { set_error("ts_adam_set_param_step: null argument"); return false; }
+    auto it = o->states.find(p->t->id);
+    if (it == o->states.end()) { set_error("ts_adam_set_param_step: parameter is not linked to the optimizer"); return false; }
+    it->second.step = n;
+    return true;
+}
 TS_API ts_tensor* ts_adam_state_m(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 0); }
 TS_API ts_tensor* ts_adam_state_v(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 1); }
 TS_API ts_tensor* ts_adam_state_v_hat_max(const ts_adam* o, const ts_tensor* p) { return state_view(o, p, 2); }

@@ -363,6 +363,47 @@ class Tensor:
 
     __matmul__ = matmul
 
+    # ------------------------------------------------------------------ checkpoints (serialization/mod.rs:271-460)
+    # The reference's JSON and TS_B binary formats (see serialization.py).  `device` is what the file records: "Cpu" by
+    # default, so that a reference build without CUDA can load it; loading ignores the recorded device and puts the
+    # tensor on this thread's current device.
+    def _fields(self, device: str):
+        from . import serialization as S
+        return S.tensor_fields(self.data(), self.shape().dims, self.requires_grad(), device=device, index=0)
+
+    def to_json(self, device: str = "Cpu") -> str:
+        from . import serialization as S
+        return S.fields_to_json(self._fields(device))
+
+    def to_binary(self, device: str = "Cpu") -> bytes:
+        from . import serialization as S
+        return S.fields_to_binary(self._fields(device))
+
+    @staticmethod
+    def _from_fields(f) -> "Tensor":
+        from . import serialization as S
+        arr, rg, _dev, _idx = S.tensor_from_fields(f)
+        t = Tensor.from_slice(arr, list(arr.shape))
+        return t.with_requires_grad() if rg else t
+
+    @staticmethod
+    def from_json(text: str) -> "Tensor":
+        from . import serialization as S
+        return Tensor._from_fields(S.json_to_fields(text))
+
+    @staticmethod
+    def from_binary(data: bytes) -> "Tensor":
+        from . import serialization as S
+        return Tensor._from_fields(S.binary_to_fields(data))
+
+    def save(self, path: str, format: str) -> None:
+        """format: "json" or "binary" (serialization/mod.rs Format)."""
+        _save(path, format, self.to_json, self.to_binary)
+
+    @staticmethod
+    def load(path: str, format: str) -> "Tensor":
+        return _load(path, format, Tensor.from_json, Tensor.from_binary)
+
     # ------------------------------------------------------------------ gradtrack
     def backward(self, grad_output: Optional["Tensor"] = None) -> None:
         """core/utils.rs:634-636 -> gradtrack/engine.rs:962-1047."""
@@ -376,6 +417,29 @@ class Tensor:
 
     def __repr__(self):
         return f"Tensor(id={self.id()}, dims={self.shape().dims}, requires_grad={self.requires_grad()})"
+
+
+def _save(path: str, format: str, to_json, to_binary) -> None:
+    fmt = str(format).lower()
+    if fmt == "json":
+        with open(path, "w", encoding="utf-8") as fh:
+            fh.write(to_json())
+    elif fmt in ("binary", "bin"):
+        with open(path, "wb") as fh:
+            fh.write(to_binary())
+    else:
+        raise TrainStationError(f"unknown format {format!r} (json or binary)")
+
+
+def _load(path: str, format: str, from_json, from_binary):
+    fmt = str(format).lower()
+    if fmt == "json":
+        with open(path, "r", encoding="utf-8") as fh:
+            return from_json(fh.read())
+    if fmt in ("binary", "bin"):
+        with open(path, "rb") as fh:
+            return from_binary(fh.read())
+    raise TrainStationError(f"unknown format {format!r} (json or binary)")
 
 
 class PinnedBuffer:
