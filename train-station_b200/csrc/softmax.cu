@@ -16,9 +16,12 @@
 //    Longer rows fall back to three sweeps over global memory (the second and third hit L2).
 //  * short rows (inner == 1, reduce <= 32): a CTA stages 256 rows through shared memory with coalesced copies,
 //    transposed and padded so that both the copy and the per-row sweep are free of bank conflicts.
-//  * columns (inner > 1): a CTA owns 32 neighbouring lines (coalesced along the contiguous axis); its W warps
-//    (8, 16 or 32 by line length) split the reduced axis, 8 elements per thread, and combine through shared
-//    memory.  Lines longer than 256 elements take the three-sweep fallback.
+//  * columns (inner > 1): when inner is a multiple of 4 (16-byte rows), a CTA streams whole [reduce][TI] tiles of
+//    32, 64 or 128 neighbouring lines into shared memory with asynchronous 16-byte copies, double-buffered, and
+//    its 512 threads split the reduced axis (the tile limit is 200 KB of shared memory: lines up to about 780
+//    elements).  Otherwise a CTA owns 32 neighbouring lines, its W warps (8, 16 or 32 by line length) hold 8
+//    elements per thread in registers and combine through shared memory; lines longer than 256 elements then take
+//    the three-sweep fallback.
 #include <cfloat>
 
 #include "../../include/train_station_b200.h"
@@ -415,6 +418,157 @@ __global__ void __launch_bounds__(32 * W) softmax_bwd_cols_kernel(const float* _
     }
 }
 
+// ------------------------------------------------------------------ columns, staged: inner > 1, inner % 4 == 0
+// A CTA copies a whole [reduce][TI] tile of neighbouring lines into shared memory with 16-byte asynchronous
+// copies (no registers held while the data is in flight), double-buffered: the next tile streams in while the
+// current one is reduced.  Thread (col, jg) owns line `col` of the tile and the elements j = jg, jg + JG, ...
+constexpr int kStagedThreads = 512;
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src, int src_bytes) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Streams tile `tile` of `src` into buf[reduce][TI]; columns past `inner` are zero-filled (src_bytes = 0 reads nothing).
+template <int TI>
+__device__ __forceinline__ void stage_tile(float* buf, const float* __restrict__ src, size_t tile, size_t itiles, size_t reduce, size_t inner) {
+    const size_t o = tile / itiles, i0 = (tile - o * itiles) * TI;
+    const int chunks_per_row = TI / 4, total = (int)reduce * chunks_per_row;
+    for (int c = threadIdx.x; c < total; c += kStagedThreads) {
+        const int j = c / chunks_per_row, q = c - j * chunks_per_row;
+        const size_t i = i0 + (size_t)q * 4;
+        const bool in = i < inner;                       // inner % 4 == 0: a chunk is entirely inside or outside
+        const float* g = in ? src + (o * reduce + j) * inner + i : src;
+        cp_async16(buf + j * TI + q * 4, g, in ? 16 : 0);
+    }
+}
+template <int JG, int TI, bool IS_MAX>
+__device__ __forceinline__ float cross_groups(float v, float* red) {
+    const int col = threadIdx.x % TI, jg = threadIdx.x / TI;
+    red[jg * TI + col] = v;
+    __syncthreads();
+    float r = red[col];
+#pragma unroll
+    for (int g = 1; g < JG; ++g) r = IS_MAX ? fmaxf(r, red[g * TI + col]) : __fadd_rn(r, red[g * TI + col]);
+    __syncthreads();
+    return r;
+}
+
+template <int TI>
+__global__ void __launch_bounds__(kStagedThreads) softmax_cols_staged_kernel(const float* __restrict__ x, float* __restrict__ y, size_t outer,
+                                                                             size_t reduce, size_t inner) {
+    constexpr int JG = kStagedThreads / TI;
+    extern __shared__ __align__(16) float smem[];
+    const size_t tile_elems = reduce * TI;   // buffer b starts at smem + b * tile_elems
+    float* red = smem + 2 * tile_elems;
+    const int col = threadIdx.x % TI, jg = threadIdx.x / TI;
+    const size_t itiles = (inner + TI - 1) / TI, tiles = outer * itiles;
+    size_t tile = blockIdx.x;
+    if (tile < tiles) stage_tile<TI>(smem, x, tile, itiles, reduce, inner);
+    cp_async_commit();
+    int cur = 0;
+    for (; tile < tiles; tile += gridDim.x, cur ^= 1) {
+        if (tile + gridDim.x < tiles) stage_tile<TI>(smem + (size_t)(cur ^ 1) * tile_elems, x, tile + gridDim.x, itiles, reduce, inner);
+        cp_async_commit();
+        cp_async_wait<1>();          // everything but the newest group has landed: the current tile
+        __syncthreads();
+        float* t = smem + (size_t)cur * tile_elems;
+        const size_t o = tile / itiles, i = (tile - o * itiles) * TI + col;
+        const bool active = i < inner;
+        float mx = -INFINITY;
+        for (size_t j = jg; j < reduce; j += JG) { const float a = t[j * TI + col]; if (a > mx) mx = a; }
+        mx = cross_groups<JG, TI, true>(mx, red);
+        float sum = 0.0f;
+        for (size_t j = jg; j < reduce; j += JG) {
+            const float e = expf(__fsub_rn(t[j * TI + col], mx));
+            t[j * TI + col] = e;
+            sum = __fadd_rn(sum, e);
+        }
+        sum = cross_groups<JG, TI, false>(sum, red);
+        const float inv = __fdiv_rn(1.0f, sum);
+        if (active) {
+            float* dst = y + o * reduce * inner + i;
+            for (size_t j = jg; j < reduce; j += JG) __stcs(dst + j * inner, __fmul_rn(t[j * TI + col], inv));
+        }
+        __syncthreads();             // the buffer is free for the copy issued in the next iteration
+    }
+    cp_async_wait<0>();
+}
+
+template <int TI>
+__global__ void __launch_bounds__(kStagedThreads) softmax_bwd_cols_staged_kernel(const float* __restrict__ y, const float* __restrict__ go,
+                                                                                 float* __restrict__ gi, size_t outer, size_t reduce, size_t inner) {
+    constexpr int JG = kStagedThreads / TI;
+    extern __shared__ __align__(16) float smem[];
+    const size_t tile_elems = reduce * TI;
+    float* red = smem + 4 * tile_elems;      // buffer b holds y at smem + 2b * tile_elems and go right after it
+    const int col = threadIdx.x % TI, jg = threadIdx.x / TI;
+    const size_t itiles = (inner + TI - 1) / TI, tiles = outer * itiles;
+    size_t tile = blockIdx.x;
+    if (tile < tiles) { stage_tile<TI>(smem, y, tile, itiles, reduce, inner); stage_tile<TI>(smem + tile_elems, go, tile, itiles, reduce, inner); }
+    cp_async_commit();
+    int cur = 0;
+    for (; tile < tiles; tile += gridDim.x, cur ^= 1) {
+        if (tile + gridDim.x < tiles) {
+            float* nb = smem + (size_t)(cur ^ 1) * 2 * tile_elems;
+            stage_tile<TI>(nb, y, tile + gridDim.x, itiles, reduce, inner);
+            stage_tile<TI>(nb + tile_elems, go, tile + gridDim.x, itiles, reduce, inner);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const float* ty = smem + (size_t)cur * 2 * tile_elems;
+        const float* tg = ty + tile_elems;
+        const size_t o = tile / itiles, i = (tile - o * itiles) * TI + col;
+        float dot = 0.0f;
+        for (size_t j = jg; j < reduce; j += JG) dot = __fadd_rn(dot, __fmul_rn(tg[j * TI + col], ty[j * TI + col]));
+        dot = cross_groups<JG, TI, false>(dot, red);
+        if (i < inner) {
+            float* dst = gi + o * reduce * inner + i;
+            for (size_t j = jg; j < reduce; j += JG) __stcs(dst + j * inner, __fmul_rn(ty[j * TI + col], __fsub_rn(tg[j * TI + col], dot)));
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+}
+
+constexpr size_t kStagedSmemLimit = 200 * 1024;   // of the 227 KB a CTA may have
+
+template <int TI>
+bool launch_cols_staged(bool bwd, const float* a, const float* b, float* o, size_t outer, size_t reduce, size_t inner, int sm, cudaStream_t s) {
+    const size_t tiles_in_smem = bwd ? 4 : 2;
+    const size_t bytes = (tiles_in_smem * reduce * TI + (size_t)kStagedThreads) * sizeof(float);
+    if (bytes > kStagedSmemLimit) return false;
+    const size_t tiles = outer * ((inner + TI - 1) / TI);
+    int per_sm = (int)(kStagedSmemLimit / bytes);
+    if (per_sm > 2048 / kStagedThreads) per_sm = 2048 / kStagedThreads;
+    if (per_sm < 1) per_sm = 1;
+    const size_t cap = (size_t)sm * per_sm;
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    if (bwd) {
+        if (!cuda_ok(cudaFuncSetAttribute(softmax_bwd_cols_staged_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), "softmax smem")) return false;
+        softmax_bwd_cols_staged_kernel<TI><<<grid, kStagedThreads, bytes, s>>>(a, b, o, outer, reduce, inner);
+    } else {
+        if (!cuda_ok(cudaFuncSetAttribute(softmax_cols_staged_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), "softmax smem")) return false;
+        softmax_cols_staged_kernel<TI><<<grid, kStagedThreads, bytes, s>>>(a, o, outer, reduce, inner);
+    }
+    return true;
+}
+
+// The widest tile whose buffers fit; false when the line is too long, too short to be worth it, or unaligned.
+bool try_cols_staged(bool bwd, const float* a, const float* b, float* o, size_t outer, size_t reduce, size_t inner, int sm, cudaStream_t s) {
+    if (inner % 4 != 0 || inner < 32 || reduce < 16) return false;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (bwd && (reinterpret_cast<uintptr_t>(b) & 15))) return false;
+    const size_t per_col = (bwd ? 4 : 2) * reduce * sizeof(float);      // shared-memory bytes per tile column
+    if (inner >= 128 && per_col * 128 + 2048 <= kStagedSmemLimit) return launch_cols_staged<128>(bwd, a, b, o, outer, reduce, inner, sm, s);
+    if (inner >= 64 && per_col * 64 + 2048 <= kStagedSmemLimit) return launch_cols_staged<64>(bwd, a, b, o, outer, reduce, inner, sm, s);
+    if (per_col * 32 + 2048 <= kStagedSmemLimit) return launch_cols_staged<32>(bwd, a, b, o, outer, reduce, inner, sm, s);
+    return false;
+}
+
 // ------------------------------------------------------------------ dispatch
 inline int grid_for(size_t units, int sm_count, int cta_threads) {
     int per_sm = 1536 / cta_threads;
@@ -465,6 +619,7 @@ void dispatch(bool bwd, const float* a, const float* b, float* o, size_t outer, 
         else if (bwd) softmax_bwd_rows_kernel<256, false><<<grid_for(outer, sm, 256), 256, 0, s>>>(a, b, o, outer, reduce);
         else softmax_rows_kernel<256, false><<<grid_for(outer, sm, 256), 256, 0, s>>>(a, o, outer, reduce);
     } else {
+        if (try_cols_staged(bwd, a, b, o, outer, reduce, inner, sm, s)) return;
         if (reduce <= 8 * kV) launch_cols<8>(bwd, a, b, o, outer, reduce, inner, sm, s);
         else if (reduce <= 16 * kV) launch_cols<16>(bwd, a, b, o, outer, reduce, inner, sm, s);
         else if (reduce <= 32 * kV) launch_cols<32>(bwd, a, b, o, outer, reduce, inner, sm, s);
