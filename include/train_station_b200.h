@@ -349,6 +349,7 @@ ts_tensor* ts_tensor_reshape(ts_tensor* x, const long long* new_shape, int rank)
 ts_tensor* ts_tensor_permute(ts_tensor* x, const unsigned long long* order, int n);
 ts_tensor* ts_tensor_transpose(ts_tensor* x, unsigned long long dim0, unsigned long long dim1);
 ts_tensor* ts_tensor_contiguous(ts_tensor* x);
+ts_tensor* ts_tensor_clone(ts_tensor* x);   /* Clone (tensor/core/mod.rs:344-378): same values, no gradient history */
 /* Reductions over axes (tensor/reductions/*.rs): sum_dims, mean_dims, max_dims, min_dims, norm_dims, var_dims,
  * std_dims with `keepdim`, and the whole-tensor max / min / norm / var / std (result [1]).  Variance and standard
  * deviation are the population ones (divide by the count), as in the reference. */

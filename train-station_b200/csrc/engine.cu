@@ -1283,6 +1283,19 @@ TS_API ts_tensor* ts_tensor_transpose(ts_tensor* hx, unsigned long long dim0, un
     return permute_op(x, perm);
 }
 
+// Clone for Tensor (tensor/core/mod.rs:344-378): a fresh tensor with the same values and no gradient history.
+TS_API ts_tensor* ts_tensor_clone(ts_tensor* hx) {
+    if (!hx) { set_error("clone: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const float* px = rptr(x);
+    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
+    if (!out) return nullptr;
+    if (x->size && !cuda_ok(cudaMemcpyAsync(out->st->ptr, px, x->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "clone")) return nullptr;
+    return wrap(out);
+}
+
 // contiguous.rs:123-137: for a contiguous tensor, a copy that stays connected to its source in the graph
 TS_API ts_tensor* ts_tensor_contiguous(ts_tensor* hx) {
     if (!hx) { set_error("contiguous: null tensor"); return nullptr; }

@@ -162,6 +162,20 @@ class Adam(Optimizer):
         from .tensor import _load
         return _load(path, format, Adam.from_json, Adam.from_binary)
 
+    def save_json(self, path: str) -> None:
+        self.save(path, "json")
+
+    def save_binary(self, path: str) -> None:
+        self.save(path, "binary")
+
+    @staticmethod
+    def load_json(path: str) -> "Adam":
+        return Adam.load(path, "json")
+
+    @staticmethod
+    def load_binary(path: str) -> "Adam":
+        return Adam.load(path, "binary")
+
     def saved_parameter_count(self) -> int:
         """Parameters in a loaded checkpoint that relink_parameters still has to attach (0 once linked)."""
         return len(self._saved[1]) if self._saved is not None else 0

@@ -318,6 +318,14 @@ class Tensor:
     def contiguous(self) -> "Tensor":                    # contiguous.rs:123-137
         return Tensor(_ffi.lib().ts_tensor_contiguous(self._h))
 
+    def view(self, new_shape: Sequence[int]) -> "Tensor":
+        """core/utils.rs:1285-1289: a view with a new shape over the same storage (the reshape of a contiguous tensor)."""
+        return self.reshape(new_shape)
+
+    def clone(self) -> "Tensor":
+        """Clone (tensor/core/mod.rs:344-378): a copy of the values with no gradient history."""
+        return Tensor(_ffi.lib().ts_tensor_clone(self._h))
+
     def is_contiguous(self) -> bool:
         return True
 
@@ -403,6 +411,21 @@ class Tensor:
     @staticmethod
     def load(path: str, format: str) -> "Tensor":
         return _load(path, format, Tensor.from_json, Tensor.from_binary)
+
+    # StructSerializable's shorthands (serialization/core/traits.rs:265-340)
+    def save_json(self, path: str) -> None:
+        self.save(path, "json")
+
+    def save_binary(self, path: str) -> None:
+        self.save(path, "binary")
+
+    @staticmethod
+    def load_json(path: str) -> "Tensor":
+        return Tensor.load(path, "json")
+
+    @staticmethod
+    def load_binary(path: str) -> "Tensor":
+        return Tensor.load(path, "binary")
 
     # ------------------------------------------------------------------ gradtrack
     def backward(self, grad_output: Optional["Tensor"] = None) -> None:
