@@ -101,7 +101,8 @@ bool sqdiff(const float* a, const float* b, float* o, size_t n, cudaStream_t s);
 // gi = (scale * (*upstream)) * (2 * x): ReduceMean / ReduceSum backward followed by PowScalar(2) backward.
 bool square_bwd_scalar(const float* x, const float* upstream, float scale, float* gi, size_t n, cudaStream_t s);
 // gy = ((inv_n) * (*upstream)) * (2 * (y - t)): ReduceMean -> PowScalar(2) -> Sub in one pass.
-bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s);
+// round_tf32: store the result rounded to the nearest TF32 value (it feeds tensor-core GEMMs directly).
+bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, bool round_tf32, cudaStream_t s);
 // op codes: enum ts_unary_op of the public header; p is the slope, scalar or exponent
 bool unary(int op, const float* x, float* o, size_t n, float p, cudaStream_t s);
 bool unary_bwd(int op, const float* saved, const float* go, float* gi, size_t n, float p, cudaStream_t s);

@@ -169,11 +169,19 @@ struct SplitTf32F {
 };
 // inputs y, t: ((inv_n * upstream) * (2 * (y - t))): ReduceMean -> PowScalar(2) -> Sub chain
 // (grad_fn/reductions/mean.rs:10-19, grad_fn/ops/pow.rs:5-27, grad_fn/ops/sub.rs:26-31).
+// round_tf32: the gradient goes straight into tensor-core GEMMs in TF32 mode, so it is stored rounded to the nearest
+// TF32 value (what those GEMMs would otherwise get from a separate rounding pass).
 struct MseGradF {
-    const float* upstream; float inv_n;
+    const float* upstream; float inv_n; bool round_tf32;
     __device__ void apply(const float* x, float* o) const {
         float sc = __fmul_rn(inv_n, __ldg(upstream));
-        o[0] = __fmul_rn(sc, __fmul_rn(2.0f, __fsub_rn(x[0], x[1])));
+        float g = __fmul_rn(sc, __fmul_rn(2.0f, __fsub_rn(x[0], x[1])));
+        if (round_tf32) {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(g));
+            g = __uint_as_float(r);
+        }
+        o[0] = g;
     }
 };
 
@@ -305,9 +313,9 @@ bool square_bwd_scalar(const float* x, const float* upstream, float scale, float
     if (!upstream) { set_error("square_bwd_scalar: null upstream"); return false; }
     return launch_ew(Ptrs<1, 1>{{x}, {gi}}, n, SquareBwdScalarF{upstream, scale}, s);
 }
-bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, cudaStream_t s) {
+bool mse_grad(const float* y, const float* t, const float* upstream, float inv_n, float* gy, size_t n, bool round_tf32, cudaStream_t s) {
     if (!upstream) { set_error("mse_grad: null upstream"); return false; }
-    return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n}, s);
+    return launch_ew(Ptrs<2, 1>{{y, t}, {gy}}, n, MseGradF{upstream, inv_n, round_tf32}, s);
 }
 
 bool unary(int op, const float* x, float* o, size_t n, float p, cudaStream_t s) {

@@ -567,7 +567,28 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
                 const TensorP& x = nd.s0.t;
                 if (x->pending_ew && x->pending_ew->kind == PendingEw::Diff) {
                     const float *pa = rptr(x->pending_ew->a), *pb = rptr(x->pending_ew->b);
-                    if (!pa || !pb || !k::mse_grad(pa, pb, up, scale, r->st->ptr, r->size, s)) return false;
+                    // In TF32 mode, when the minuend came out of a matmul (directly or through its bias add) and only it
+                    // wants a gradient, this gradient's consumers are that matmul's two backward GEMMs and the bias
+                    // column sum: store it already rounded to TF32, as a deferred GEMM that produces a gradient does.
+                    bool round_out = false;
+                    if (matmul_precision() == 1) {
+                        auto sub = g_graph.ops.find(nd.inputs[0]);
+                        if (sub != g_graph.ops.end() && sub->second.op == Op::Sub && sub->second.needs[0] && !sub->second.needs[1]) {
+                            auto prod = g_graph.ops.find(sub->second.inputs[0]);
+                            if (prod != g_graph.ops.end() && prod->second.op == Op::Add) {
+                                // a row-bias add only: the other operand is the matmul result, the bias gets a column sum
+                                if (prod->second.dims0 != prod->second.dims1) {
+                                    const int big = prod->second.dims0.size() >= prod->second.dims1.size() ? 0 : 1;
+                                    auto mm = g_graph.ops.find(prod->second.inputs[big]);
+                                    round_out = mm != g_graph.ops.end() && mm->second.op == Op::MatMul;
+                                }
+                            } else {
+                                round_out = prod != g_graph.ops.end() && prod->second.op == Op::MatMul;
+                            }
+                        }
+                    }
+                    if (!pa || !pb || !k::mse_grad(pa, pb, up, scale, r->st->ptr, r->size, round_out, s)) return false;
+                    r->st->tf32_clean = round_out;
                 } else {
                     const float* px = rptr(x);
                     if (!px || !k::square_bwd_scalar(px, up, scale, r->st->ptr, r->size, s)) return false;
