@@ -350,6 +350,10 @@ ts_tensor* ts_tensor_permute(ts_tensor* x, const unsigned long long* order, int 
 ts_tensor* ts_tensor_transpose(ts_tensor* x, unsigned long long dim0, unsigned long long dim1);
 ts_tensor* ts_tensor_contiguous(ts_tensor* x);
 ts_tensor* ts_tensor_clone(ts_tensor* x);   /* Clone (tensor/core/mod.rs:344-378): same values, no gradient history */
+/* Tensor::cat (tensor/transform/cat.rs:110-230) and one piece of split / split_with_sizes (split.rs:159-330:
+ * elements [start, start + length) of axis dim); strided device-to-device copies, GradFn::Cat / GradFn::Split. */
+ts_tensor* ts_tensor_cat(ts_tensor* const* tensors, int n, unsigned long long dim);
+ts_tensor* ts_tensor_split_piece(ts_tensor* x, unsigned long long dim, unsigned long long start, unsigned long long length);
 /* Reductions over axes (tensor/reductions/*.rs): sum_dims, mean_dims, max_dims, min_dims, norm_dims, var_dims,
  * std_dims with `keepdim`, and the whole-tensor max / min / norm / var / std (result [1]).  Variance and standard
  * deviation are the population ones (divide by the count), as in the reference. */

@@ -141,6 +141,8 @@ SIGNATURES = {
     "ts_tensor_transpose": (vp, [vp, u64, u64]),
     "ts_tensor_contiguous": (vp, [vp]),
     "ts_tensor_clone": (vp, [vp]),
+    "ts_tensor_cat": (vp, [C.POINTER(vp), C.c_int, u64]),
+    "ts_tensor_split_piece": (vp, [vp, u64, u64, u64]),
     "ts_set_domain_checks": (None, [C.c_int]),
     "ts_get_domain_checks": (C.c_int, []),
     "ts_tensor_sum": (vp, [vp]),

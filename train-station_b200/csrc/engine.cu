@@ -213,7 +213,7 @@ static bool materialize(const TensorP& t, bool for_gemm) {
 }
 
 // ------------------------------------------------------------------ tape
-enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax, Reshape, Permute, ReduceDims };
+enum class Op { Add, Sub, Mul, Div, Relu, MatMul, PowScalar, ReduceSum, ReduceMean, Unary, Softmax, Reshape, Permute, ReduceDims, Cat, Split };
 
 struct Saved {
     TensorP t;
@@ -421,6 +421,17 @@ static TensorP reshaped_alias(const TensorP& t, const std::vector<size_t>& dims)
     auto r = std::make_shared<TensorImpl>(dims);
     r->st = t->st;
     return r;
+}
+
+// `rows` runs of `width` contiguous elements from src (row pitch src_pitch, starting at src_off) to dst (row pitch
+// dst_pitch, starting at dst_off): the slab of an axis that cat / split address.  A strided device-to-device copy.
+static bool copy_slab(float* dst, size_t dst_pitch, size_t dst_off, const float* src, size_t src_pitch, size_t src_off, size_t width,
+                      size_t rows, cudaStream_t s) {
+    if (width == 0 || rows == 0) return true;
+    if (rows == 1 || (dst_pitch == width && src_pitch == width))
+        return cuda_ok(cudaMemcpyAsync(dst + dst_off, src + src_off, rows * width * sizeof(float), cudaMemcpyDeviceToDevice, s), "slab copy");
+    return cuda_ok(cudaMemcpy2DAsync(dst + dst_off, dst_pitch * sizeof(float), src + src_off, src_pitch * sizeof(float),
+                                     width * sizeof(float), rows, cudaMemcpyDeviceToDevice, s), "slab copy");
 }
 
 // ------------------------------------------------------------------ backward of one node
@@ -669,6 +680,43 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             }
             if (mode >= 2 && (!x || !a1)) return false;
             if (!k::reduce_dims_backward(mode, x, a1, a2, gp, r->st->ptr, nd.dims0.data(), rank, red.data(), scalar_go, scale, s)) return false;
+            gin[0] = r;
+            return true;
+        }
+        case Op::Cat: {
+            // grad_fn/transforms/cat.rs: each input gets its slab of the gradient (nd.dims0 = output dims, nd.perm = lengths along the axis)
+            const float* gp = rptr(go);
+            if (!gp) return false;
+            const int dim = nd.code;
+            size_t outer = 1, inner = 1, prefix = 0;
+            for (int d = 0; d < dim; ++d) outer *= nd.dims0[d];
+            for (size_t d = dim + 1; d < nd.dims0.size(); ++d) inner *= nd.dims0[d];
+            const size_t total = nd.dims0[dim];
+            for (size_t i = 0; i < nd.inputs.size(); ++i) {
+                const size_t len = (size_t)nd.perm[i];
+                if (nd.needs[i]) {
+                    std::vector<size_t> gd = nd.dims0;
+                    gd[dim] = len;
+                    TensorP r = new_tensor(c, gd);
+                    if (!r || !copy_slab(r->st->ptr, len * inner, 0, gp, total * inner, prefix * inner, len * inner, outer, s)) return false;
+                    gin[i] = r;
+                }
+                prefix += len;
+            }
+            return true;
+        }
+        case Op::Split: {
+            // grad_fn/transforms/split.rs: zeros of the input's shape with the gradient added into its slab
+            if (!nd.needs[0]) return true;
+            const float* gp = rptr(go);
+            TensorP r = gp ? new_tensor(c, nd.dims0) : nullptr;
+            if (!r || !k::fill(r->st->ptr, 0.0f, r->size, s)) return false;
+            const int dim = nd.code;
+            const size_t start = (size_t)nd.perm[0], len = (size_t)nd.perm[1];
+            size_t outer = 1, inner = 1;
+            for (int d = 0; d < dim; ++d) outer *= nd.dims0[d];
+            for (size_t d = dim + 1; d < nd.dims0.size(); ++d) inner *= nd.dims0[d];
+            if (!copy_slab(r->st->ptr, nd.dims0[dim] * inner, start * inner, gp, len * inner, 0, len * inner, outer, s)) return false;
             gin[0] = r;
             return true;
         }
@@ -1333,6 +1381,92 @@ TS_API ts_tensor* ts_tensor_contiguous(ts_tensor* hx) {
         nd.inputs = {x->id};
         nd.needs = {true};
         nd.dims0 = x->dims;
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+// ---- joining and splitting along an axis (tensor/transform/cat.rs:110-230, split.rs:159-330)
+TS_API ts_tensor* ts_tensor_cat(ts_tensor* const* tensors, int n, unsigned long long dim) {
+    if (n <= 0 || !tensors) { set_error("cat requires at least one tensor"); return nullptr; }   // cat.rs:111
+    for (int i = 0; i < n; ++i)
+        if (!tensors[i]) { set_error("cat: null tensor at index %d", i); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    const std::vector<size_t>& base = tensors[0]->t->dims;
+    const size_t rank = base.size();
+    if (dim >= rank) { set_error("concat dim %llu out of bounds for rank %zu", dim, rank); return nullptr; }
+    std::vector<size_t> od = base;
+    size_t total = 0;
+    bool any_grad = false;
+    for (int i = 0; i < n; ++i) {
+        const std::vector<size_t>& d = tensors[i]->t->dims;
+        if (d.size() != rank) { set_error("All tensors must have same rank"); return nullptr; }
+        for (size_t a = 0; a < rank; ++a)
+            if (a != dim && d[a] != base[a]) {
+                set_error("All dims except concat dim must match (dim %zu: %zu vs %zu)", a, base[a], d[a]);
+                return nullptr;
+            }
+        total += d[dim];
+        any_grad = any_grad || tensors[i]->t->requires_grad;
+    }
+    od[dim] = total;
+    TensorP out = new_tensor(c, od);
+    if (!out) return nullptr;
+    size_t outer = 1, inner = 1, prefix = 0;
+    for (size_t a = 0; a < dim; ++a) outer *= od[a];
+    for (size_t a = dim + 1; a < rank; ++a) inner *= od[a];
+    for (int i = 0; i < n; ++i) {
+        const size_t len = tensors[i]->t->dims[dim];
+        if (len && outer && inner) {
+            const float* px = rptr(tensors[i]->t);
+            if (!px || !copy_slab(out->st->ptr, total * inner, prefix * inner, px, len * inner, 0, len * inner, outer, c->compute)) return nullptr;
+        }
+        prefix += len;
+    }
+    if (any_grad) {   // cat.rs registers GradFn::Cat whenever an input requires a gradient
+        Node nd;
+        nd.op = Op::Cat;
+        nd.code = (int)dim;
+        nd.dims0 = od;
+        for (int i = 0; i < n; ++i) {
+            nd.inputs.push_back(tensors[i]->t->id);
+            nd.needs.push_back(tensors[i]->t->requires_grad);
+            nd.perm.push_back((int)tensors[i]->t->dims[dim]);
+        }
+        record(out, std::move(nd));
+    }
+    return wrap(out);
+}
+
+// One piece of split_with_sizes: elements [start, start + length) of axis `dim`, as a contiguous copy.
+TS_API ts_tensor* ts_tensor_split_piece(ts_tensor* hx, unsigned long long dim, unsigned long long start, unsigned long long length) {
+    if (!hx) { set_error("split: null tensor"); return nullptr; }
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    TensorP x = hx->t;
+    const size_t rank = x->dims.size();
+    if (dim >= rank) { set_error("split dim %llu out of bounds for rank %zu", dim, rank); return nullptr; }   // split.rs:161-167
+    if (start + length > x->dims[dim]) { set_error("split: piece [%llu, %llu) exceeds size %zu of dim %llu", start, start + length, x->dims[dim], dim); return nullptr; }
+    std::vector<size_t> od = x->dims;
+    od[dim] = (size_t)length;
+    TensorP out = new_tensor(c, od);
+    if (!out) return nullptr;
+    size_t outer = 1, inner = 1;
+    for (size_t a = 0; a < dim; ++a) outer *= od[a];
+    for (size_t a = dim + 1; a < rank; ++a) inner *= od[a];
+    if (out->size) {
+        const float* px = rptr(x);
+        if (!px || !copy_slab(out->st->ptr, length * inner, 0, px, x->dims[dim] * inner, start * inner, length * inner, outer, c->compute)) return nullptr;
+    }
+    if (x->requires_grad && length > 0) {   // split.rs:300-312; zero-length pieces are plain zeros tensors
+        Node nd;
+        nd.op = Op::Split;
+        nd.code = (int)dim;
+        nd.inputs = {x->id};
+        nd.needs = {true};
+        nd.dims0 = x->dims;
+        nd.perm = {(int)start, (int)length};
         record(out, std::move(nd));
     }
     return wrap(out);

@@ -329,6 +329,59 @@ class Tensor:
     def is_contiguous(self) -> bool:
         return True
 
+    # joining and splitting (tensor/transform/{cat,stack,split}.rs)
+    @staticmethod
+    def cat(tensors: Sequence["Tensor"], dim: int) -> "Tensor":
+        if len(tensors) == 0:
+            raise TrainStationError("cat requires at least one tensor")
+        if dim < 0:
+            raise TrainStationError("cat axis is unsigned")
+        arr = (vp * len(tensors))(*[t._h for t in tensors])
+        return Tensor(_ffi.lib().ts_tensor_cat(arr, len(tensors), int(dim)), keep=list(tensors))
+
+    @staticmethod
+    def stack(tensors: Sequence["Tensor"], dim: int) -> "Tensor":
+        """stack.rs:165-230: a new axis of length len(tensors) at `dim`; here the concatenation of the unsqueezed inputs."""
+        if len(tensors) == 0:
+            raise TrainStationError("stack requires at least one tensor")
+        base = tensors[0].shape().dims
+        for t in tensors:
+            if t.shape().dims != base:
+                raise TrainStationError("All tensors must have identical shapes for stack")
+        if not 0 <= dim <= len(base):
+            raise TrainStationError(f"stack dim {dim} out of bounds for rank {len(base)}")
+        return Tensor.cat([t.unsqueeze(dim) for t in tensors], dim)
+
+    def split(self, split_size: int, dim: int) -> list:
+        """split.rs:159-180: pieces of `split_size` along `dim`, the last one shorter."""
+        dims = self.shape().dims
+        if len(dims) == 0:
+            raise TrainStationError("split requires non-zero rank")
+        if not 0 <= dim < len(dims):
+            raise TrainStationError(f"split dim {dim} out of bounds for rank {len(dims)}")
+        if split_size <= 0:
+            raise TrainStationError("split_size must be > 0")
+        sizes, remaining = [], dims[dim]
+        while remaining > 0:
+            sizes.append(min(remaining, split_size))
+            remaining -= sizes[-1]
+        return self.split_with_sizes(sizes, dim) if sizes else []
+
+    def split_with_sizes(self, split_sizes: Sequence[int], dim: int) -> list:
+        """split.rs:284-330.  Each piece is a contiguous copy (the reference returns a view for the first one)."""
+        dims = self.shape().dims
+        if len(dims) == 0:
+            raise TrainStationError("split requires non-zero rank")
+        if not 0 <= dim < len(dims):
+            raise TrainStationError(f"split dim {dim} out of bounds for rank {len(dims)}")
+        if sum(split_sizes) != dims[dim]:
+            raise TrainStationError(f"sum of split sizes {sum(split_sizes)} must equal size {dims[dim]} of dim {dim}")
+        out, start = [], 0
+        for n in split_sizes:
+            out.append(Tensor(_ffi.lib().ts_tensor_split_piece(self._h, int(dim), int(start), int(n))))
+            start += n
+        return out
+
     # operator sugar: tensor/core/operators.rs forwards Tensor (op) Tensor to the *_tensor methods (:120-410),
     # Tensor (op) f32 to the *_scalar methods (:418-660) and -Tensor to mul_scalar(-1.0) (:690-705)
     @staticmethod
