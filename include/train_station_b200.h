@@ -320,7 +320,11 @@ bool ts_tensor_fill(ts_tensor* t, float value);
 
 /* Ops.  Each returns a new tensor and records a GradFn when grad mode is on and an input
  * requires grad (template: tensor/ops/relu.rs:77-90). */
-ts_tensor* ts_tensor_matmul(ts_tensor* a, ts_tensor* b);       /* matmul/mod.rs:263-310 */
+/* matmul/mod.rs:263-310: 1-D and 2-D operands in every pairing; with an operand of rank > 2 the batched product of
+ * mod.rs:634-760 (both operands at least 2-D, batch axes broadcast from the right, a leading batch axis of extent 1
+ * squeezed away when one operand is 2-D; errors "Batched matmul requires at least 2D tensors", "Inner dimensions
+ * must match for batched matmul: K vs K'", "Cannot broadcast dimensions A and B"). */
+ts_tensor* ts_tensor_matmul(ts_tensor* a, ts_tensor* b);
 ts_tensor* ts_tensor_add_tensor(ts_tensor* a, ts_tensor* b);   /* add.rs:107-146 (+ broadcast) */
 ts_tensor* ts_tensor_sub_tensor(ts_tensor* a, ts_tensor* b);   /* sub.rs:121-160 */
 ts_tensor* ts_tensor_mul_tensor(ts_tensor* a, ts_tensor* b);   /* mul.rs:94-135 */

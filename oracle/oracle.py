@@ -322,6 +322,86 @@ def permute(x, dims):
     return np.ascontiguousarray(np.transpose(_c(x), tuple(int(d) for d in dims)))
 
 
+def _batch_broadcast(a_batch, b_batch):
+    """tensor/ops/matmul/mod.rs:661-690: batch axes pair up from the right; 1 stretches; anything else must agree."""
+    n = max(len(a_batch), len(b_batch))
+    out = []
+    for i in range(n):
+        da = a_batch[len(a_batch) - 1 - i] if i < len(a_batch) else 1
+        db = b_batch[len(b_batch) - 1 - i] if i < len(b_batch) else 1
+        if da == 1:
+            out.append(db)
+        elif db == 1 or da == db:
+            out.append(da)
+        else:
+            raise ValueError(f"Cannot broadcast dimensions {da} and {db}")
+    return out[::-1]
+
+
+def _batch_offset(idx, batch, own, mat):
+    """mod.rs:764-835: the element offset of batch entry idx in an operand whose own batch dims are `own`."""
+    off, stride = 0, mat
+    for i in range(len(batch)):
+        bd = batch[len(batch) - 1 - i]
+        coord, idx = idx % bd, idx // bd
+        if i < len(own):
+            od = own[len(own) - 1 - i]
+            if od != 1:
+                off += coord * stride
+            stride *= od
+    return off
+
+
+def batched_matmul(a, b):
+    """mod.rs:634-740: one matrix product per entry of the broadcast batch, each the same blocked kernel as the 2-D
+    case, then the leading axis of extent 1 squeezed away when one operand was 2-D (mod.rs:752-756)."""
+    a, b = _c(a), _c(b)
+    if a.ndim < 2 or b.ndim < 2:
+        raise ValueError("Batched matmul requires at least 2D tensors")
+    m, k, k2, n = a.shape[-2], a.shape[-1], b.shape[-2], b.shape[-1]
+    if k != k2:
+        raise ValueError(f"Inner dimensions must match for batched matmul: {k} vs {k2}")
+    ab, bb = list(a.shape[:-2]), list(b.shape[:-2])
+    batch = _batch_broadcast(ab, bb)
+    count = int(np.prod(batch, dtype=np.int64)) if batch else 1
+    out = np.empty((count, m, n), np.float32)
+    af, bf = a.reshape(-1), b.reshape(-1)
+    for i in range(count):
+        ao, bo = _batch_offset(i, batch, ab, m * k), _batch_offset(i, batch, bb, k * n)
+        out[i] = matmul(af[ao:ao + m * k].reshape(m, k), bf[bo:bo + k * n].reshape(k, n))
+    dims = batch + [m, n]
+    if (a.ndim == 2 or b.ndim == 2) and len(dims) > 2 and dims[0] == 1:
+        dims = dims[1:]
+    return out.reshape(dims)
+
+
+def _reduce_to_shape(g, want):
+    """grad_fn/ops/matmul.rs reduce_gradient_to_original_shape: extra leading axes are summed away first, then the
+    axes the operand held at extent 1 are summed with keepdim."""
+    want = list(want)
+    if g.ndim > len(want):
+        extra = g.ndim - len(want)
+        g = reduce_dims("sum", g, list(range(extra)), keepdim=False).reshape(g.shape[extra:])
+    dims = [i for i in range(g.ndim) if want[i] == 1 and g.shape[i] > 1]
+    if dims:
+        g = reduce_dims("sum", g, dims, keepdim=True)
+    return np.ascontiguousarray(g).reshape(want)
+
+
+def batched_matmul_backward(a, b, go):
+    """grad_fn/ops/matmul.rs, the batched branches: dA = go . B^T and dB = A^T . go per batch entry, then reduced to
+    the operand's own shape.  go may carry the squeezed shape of the forward's result."""
+    a, b = _c(a), _c(b)
+    batch = _batch_broadcast(list(a.shape[:-2]), list(b.shape[:-2]))
+    m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+    go = _c(go).reshape(batch + [m, n])
+    bt = np.ascontiguousarray(np.swapaxes(b, -1, -2))
+    at = np.ascontiguousarray(np.swapaxes(a, -1, -2))
+    ga = batched_matmul(go, bt).reshape(batch + [m, k])
+    gb = batched_matmul(at, go).reshape(batch + [k, n])
+    return _reduce_to_shape(ga, a.shape), _reduce_to_shape(gb, b.shape)
+
+
 def reshape_dims(size, new_shape):
     """transform/reshape.rs:185-215: one -1 is inferred; other entries must be positive; sizes must agree."""
     dims, infer, known = [], None, 1

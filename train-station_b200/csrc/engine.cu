@@ -434,6 +434,101 @@ static bool copy_slab(float* dst, size_t dst_pitch, size_t dst_off, const float*
                                      width * sizeof(float), rows, cudaMemcpyDeviceToDevice, s), "slab copy");
 }
 
+// ---- batched matmul (tensor/ops/matmul/mod.rs:634-835): the last two axes multiply, the leading axes broadcast
+// right-aligned; one GEMM launch per batch entry on offsets into the operands.
+struct BatchGeom {
+    std::vector<size_t> batch;      // broadcast batch dims of the result
+    size_t count = 1;
+};
+// element offset of batch entry `idx` (over `batch`) in an operand whose own batch dims are `own` (right-aligned,
+// extent 1 broadcasts) and whose matrices have `mat` elements (mod.rs:764-835)
+static size_t batch_offset(size_t idx, const std::vector<size_t>& batch, const std::vector<size_t>& own, size_t mat) {
+    size_t off = 0, stride = mat;
+    const size_t nb = batch.size(), no = own.size();
+    for (size_t i = 0; i < nb; ++i) {            // from the innermost batch axis outwards
+        const size_t bd = batch[nb - 1 - i];
+        const size_t coord = idx % bd;
+        idx /= bd;
+        if (i < no) {
+            const size_t od = own[no - 1 - i];
+            if (od != 1) off += coord * stride;
+            stride *= od;
+        }
+    }
+    return off;
+}
+static bool broadcast_batch(const std::vector<size_t>& a, const std::vector<size_t>& b, BatchGeom* g) {
+    const size_t na = a.size(), nb = b.size(), n = na > nb ? na : nb;
+    g->batch.assign(n, 1);
+    g->count = 1;
+    for (size_t i = 0; i < n; ++i) {
+        const size_t da = i < na ? a[na - 1 - i] : 1, db = i < nb ? b[nb - 1 - i] : 1;
+        if (da != 1 && db != 1 && da != db) { set_error("Cannot broadcast dimensions %zu and %zu", da, db); return false; }   // mod.rs:672
+        g->batch[n - 1 - i] = da == 1 ? db : da;
+        g->count *= g->batch[n - 1 - i];
+    }
+    return true;
+}
+// out[batch][m][n] = op(A)[batch] . op(B)[batch]; a_batch / b_batch are the operands' own batch dims.
+static bool batched_gemm(DeviceCtx* c, const TensorP& ta, const std::vector<size_t>& a_batch, bool trans_a, const TensorP& tb,
+                         const std::vector<size_t>& b_batch, bool trans_b, float* out, const BatchGeom& g, size_t m, size_t n, size_t kk) {
+    const float* pa = rptr(ta, true);
+    const float* pb = rptr(tb, true);
+    if (!pa || !pb) return false;
+    const int prec = matmul_precision();
+    const float *ra = pa, *rb = pb;
+    if (prec == 1) {   // TF32: operands rounded to nearest first (cached copies beside the data)
+        ra = tf32_operand(c, ta);
+        rb = tf32_operand(c, tb);
+        if (!ra || !rb) return false;
+    }
+    const size_t a_mat = m * kk, b_mat = kk * n;
+    for (size_t i = 0; i < g.count; ++i) {
+        const size_t ao = batch_offset(i, g.batch, a_batch, a_mat), bo = batch_offset(i, g.batch, b_batch, b_mat);
+        k::GemmArgs ga{ra + ao, rb + bo, out + i * m * n, m, n, kk, trans_a, trans_b, nullptr, false, nullptr};
+        bool ok;
+        if (prec == 1 && !k::gemm_tc_supported(ga)) {
+            k::GemmArgs raw{pa + ao, pb + bo, out + i * m * n, m, n, kk, trans_a, trans_b, nullptr, false, nullptr};
+            ok = k::sgemm(raw, c->compute);      // shapes the tensor-core kernel cannot take run in FP32 on the unrounded data
+        } else {
+            ok = k::gemm(ga, prec, c, c->compute);
+        }
+        if (!ok) return false;
+    }
+    return true;
+}
+// grad_fn/ops/matmul.rs reduce_gradient_to_original_shape: leading extra axes are summed away, then axes that
+// were 1 in the operand are summed with keepdim.
+static TensorP reduce_to_shape(DeviceCtx* c, const TensorP& g, const std::vector<size_t>& want) {
+    if (g->dims == want) return g;
+    TensorP cur = g;
+    auto sum_axes = [&](const std::vector<unsigned char>& red, const std::vector<size_t>& od) -> TensorP {
+        TensorP o = new_tensor(c, od);
+        float* scratch = o ? c->alloc.alloc(k::reduce_dims_scratch_elems() * sizeof(float)) : nullptr;
+        if (!scratch) return nullptr;
+        bool ok = k::reduce_dims(0, cur->st->ptr, nullptr, o->st->ptr, cur->dims.data(), (int)cur->dims.size(), red.data(), scratch, c->compute);
+        c->alloc.free(scratch);
+        return ok ? o : nullptr;
+    };
+    if (cur->dims.size() > want.size()) {
+        const size_t extra = cur->dims.size() - want.size();
+        std::vector<unsigned char> red(cur->dims.size(), 0);
+        for (size_t i = 0; i < extra; ++i) red[i] = 1;
+        cur = sum_axes(red, std::vector<size_t>(cur->dims.begin() + extra, cur->dims.end()));
+        if (!cur) return nullptr;
+    }
+    std::vector<unsigned char> red(cur->dims.size(), 0);
+    bool any = false;
+    for (size_t i = 0; i < cur->dims.size() && i < want.size(); ++i)
+        if (want[i] == 1 && cur->dims[i] > 1) { red[i] = 1; any = true; }
+    if (any) {
+        cur = sum_axes(red, want);
+        if (!cur) return nullptr;
+    }
+    if (cur->dims != want) cur = reshaped_alias(cur, want);
+    return cur;
+}
+
 // ------------------------------------------------------------------ backward of one node
 static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& go, std::vector<TensorP>& gin) {
     cudaStream_t s = c->compute;
@@ -548,6 +643,32 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             // grad_fn/ops/matmul.rs:68-80: dA = go . B^T, dB = A^T . go; the transposes are operand
             // layouts of the GEMM, not copies.
             if (!nd.s0.check("matmul") || !nd.s1.check("matmul")) return false;
+            if (nd.dims0.size() > 2 || nd.dims1.size() > 2) {
+                // batched (matmul.rs, the general branch): dA = go . B^T and dB = A^T . go per batch entry, then summed
+                // back over the axes the operand was broadcast along
+                const std::vector<size_t>&da = nd.dims0, &db = nd.dims1;
+                const size_t m = da[da.size() - 2], kk = da.back(), n = db.back();
+                const std::vector<size_t> a_batch(da.begin(), da.end() - 2), b_batch(db.begin(), db.end() - 2);
+                BatchGeom g;
+                if (!broadcast_batch(a_batch, b_batch, &g)) return false;
+                if (!materialize(go)) return false;
+                const std::vector<size_t> no_batch;
+                for (int side = 0; side < 2; ++side) {
+                    if (!nd.needs[side]) continue;
+                    std::vector<size_t> raw_dims = g.batch;
+                    raw_dims.push_back(side == 0 ? m : kk);
+                    raw_dims.push_back(side == 0 ? kk : n);
+                    TensorP raw = new_tensor(c, raw_dims);
+                    if (!raw) return false;
+                    // the upstream gradient has one [m, n] matrix per batch entry whatever squeezing the forward did
+                    bool ok = side == 0 ? batched_gemm(c, go, g.batch, false, nd.s1.t, b_batch, true, raw->st->ptr, g, m, kk, n)
+                                        : batched_gemm(c, nd.s0.t, a_batch, true, go, g.batch, false, raw->st->ptr, g, kk, n, m);
+                    if (!ok) return false;
+                    gin[side] = reduce_to_shape(c, raw, side == 0 ? da : db);
+                    if (!gin[side]) return false;
+                }
+                return true;
+            }
             const size_t m = nd.dims0.size() == 2 ? nd.dims0[0] : 1, kk = nd.dims0.back();
             const size_t n = nd.dims1.size() == 2 ? nd.dims1[1] : 1;
             if (nd.needs[0]) {
@@ -1121,7 +1242,37 @@ TS_API ts_tensor* ts_tensor_matmul(ts_tensor* ha, ts_tensor* hb) {
     if (!c) return nullptr;
     TensorP a = ha->t, b = hb->t;
     const size_t ra = a->dims.size(), rb = b->dims.size();
-    if (ra < 1 || ra > 2 || rb < 1 || rb > 2) { set_error("matmul: only 1-D and 2-D operands are implemented on this path"); return nullptr; }
+    if (ra < 1 || rb < 1) { set_error("matmul: operands need at least one dimension"); return nullptr; }
+    if (ra > 2 || rb > 2) {
+        // N-D . N-D (matmul/mod.rs:634-760): batch axes broadcast, one GEMM per batch entry, launched now
+        if (ra < 2 || rb < 2) { set_error("Batched matmul requires at least 2D tensors"); return nullptr; }
+        const size_t m = a->dims[ra - 2], ka = a->dims[ra - 1], kb = b->dims[rb - 2], n = b->dims[rb - 1];
+        if (ka != kb) { set_error("Inner dimensions must match for batched matmul: %zu vs %zu", ka, kb); return nullptr; }
+        const std::vector<size_t> a_batch(a->dims.begin(), a->dims.end() - 2), b_batch(b->dims.begin(), b->dims.end() - 2);
+        BatchGeom g;
+        if (!broadcast_batch(a_batch, b_batch, &g)) return nullptr;
+        std::vector<size_t> od = g.batch;
+        od.push_back(m);
+        od.push_back(n);
+        TensorP out = new_tensor(c, od);
+        if (!out) return nullptr;
+        if (out->size && !batched_gemm(c, a, a_batch, false, b, b_batch, false, out->st->ptr, g, m, n, ka)) return nullptr;
+        // mod.rs:752-756: with a 2-D operand, a leading batch axis of extent 1 is squeezed away
+        if ((ra == 2 || rb == 2) && od.size() > 2 && od[0] == 1) {
+            out = reshaped_alias(out, std::vector<size_t>(od.begin() + 1, od.end()));
+            if (!out) return nullptr;
+        }
+        if (grad_on() && (a->requires_grad || b->requires_grad)) {
+            Node nd;
+            nd.op = Op::MatMul;
+            nd.inputs = {a->id, b->id};
+            nd.needs = {a->requires_grad, b->requires_grad};
+            nd.dims0 = a->dims; nd.dims1 = b->dims;
+            nd.s0.set(a); nd.s1.set(b);
+            record(out, std::move(nd));
+        }
+        return wrap(out);
+    }
     // rank dispatch: matmul/mod.rs:263-310
     const size_t m = ra == 2 ? a->dims[0] : 1, ka = a->dims.back();
     const size_t kb = b->dims[0], n = rb == 2 ? b->dims[1] : 1;
