@@ -555,7 +555,7 @@ def run_c2(args):
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
                "softmax_inner", "transpose", "permute_021", "permute_gather", "reduce_rows", "reduce_cols", "reduce_all_max",
-               "reduce_middle")
+               "reduce_middle", "broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward")
 
 
 def run_micro(args):
@@ -678,6 +678,22 @@ def run_micro(args):
         ax = (C.c_ulonglong * len(axes))(*axes)
         launch = lambda: chk(lib.launch_reduce_dims_kernel(op, x, None, o1, dims, len(shape), ax, len(axes), sc, None), name)
         work, unit, peak = 4.0 * n, "GB/s", peaks["hbm_gbs"]
+    elif name in ("broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward"):
+        # [16384, 4096] with a row [4096], with a column [16384, 1]; a column times a row; both gradients of the column case
+        sa, sb = {"broadcast_row": ((16384, 4096), (4096,)), "broadcast_col": ((16384, 4096), (16384, 1)),
+                  "broadcast_outer": ((16384, 1), (1, 4096)), "broadcast_mul_backward": ((16384, 4096), (16384, 1))}[name]
+        so = np.broadcast_shapes(sa, sb)
+        n = int(np.prod(so))
+        a, b, o1 = dev(rng.standard_normal(sa, dtype=np.float32)), dev(rng.standard_normal(sb, dtype=np.float32)), empty(n)
+        da, db = (C.c_ulonglong * len(sa))(*sa), (C.c_ulonglong * len(sb))(*sb)
+        if name.endswith("backward"):
+            g, o2 = dev(rng.standard_normal(so, dtype=np.float32)), empty(n)
+            launch = lambda: chk(lib.launch_binary_broadcast_backward_kernel(2, a, da, len(sa), b, db, len(sb), g, o1, o2, None), name)
+            work = 4.0 * (3 * n + int(np.prod(sa)) + int(np.prod(sb)))
+        else:
+            launch = lambda: chk(lib.launch_binary_broadcast_kernel(0, a, da, len(sa), b, db, len(sb), o1, None), name)
+            work = 4.0 * (n + int(np.prod(sa)) + int(np.prod(sb)))
+        unit, peak = "GB/s", peaks["hbm_gbs"]
     elif name in ("colsum", "relu_backward_colsum"):
         rows, cols = (n or 16384), 8192
         g, ref = dev(rng.standard_normal((rows, cols), dtype=np.float32)), dev(rng.standard_normal((rows, cols), dtype=np.float32))

@@ -145,6 +145,18 @@ bool launch_square_backward_kernel(const float* x, const float* grad_out, float*
 /* grad_fn/ops/mul.rs:4-49: ga = go*b, gb = go*a.  Either output may be NULL. */
 bool launch_mul_backward_kernel(const float* a, const float* b, const float* grad_out, float* grad_a,
                                 float* grad_b, unsigned long long size, void* stream);
+/* add / sub / mul / div (op 0..3) of two contiguous operands of different shapes under NumPy-style broadcasting
+ * (tensor/ops/broadcasting.rs:100-135; what add_tensor does at add.rs:113-125 by first materialising both stretched
+ * operands, broadcasting.rs:299-333).  out is contiguous over the broadcast shape; ranks 1..8; false with
+ * "incompatible dimensions at axis N" when the shapes do not broadcast. */
+bool launch_binary_broadcast_kernel(int op, const float* a, const unsigned long long* dims_a, int rank_a, const float* b,
+                                    const unsigned long long* dims_b, int rank_b, float* out, void* stream);
+/* The full-size gradients of a broadcast mul (op 2: go*b, go*a) or div (op 3: go/b, -((go*a)/(b*b))) over the
+ * broadcast shape (grad_fn/ops/mul.rs, div.rs with original_shapes); grad_out is contiguous over that shape; the
+ * caller sums each back to its operand's shape (grad_fn/utils.rs:23-60).  Either output may be NULL. */
+bool launch_binary_broadcast_backward_kernel(int op, const float* a, const unsigned long long* dims_a, int rank_a, const float* b,
+                                             const unsigned long long* dims_b, int rank_b, const float* grad_out, float* grad_a,
+                                             float* grad_b, void* stream);
 /* grad_fn/ops/div.rs:4-49: ga = go/b, gb = -((go*a)/(b*b)).  Either output may be NULL. */
 bool launch_div_backward_kernel(const float* a, const float* b, const float* grad_out, float* grad_a,
                                 float* grad_b, unsigned long long size, void* stream);

@@ -375,17 +375,71 @@ def batched_matmul(a, b):
     return out.reshape(dims)
 
 
-def _reduce_to_shape(g, want):
-    """grad_fn/ops/matmul.rs reduce_gradient_to_original_shape: extra leading axes are summed away first, then the
-    axes the operand held at extent 1 are summed with keepdim."""
+def _reduce_to_shape(g, want, last_first=True):
+    """grad_fn/ops/matmul.rs:276-331 reduce_gradient_to_original_shape (last_first) and grad_fn/utils.rs:23-60
+    reduce_gradient_to_shape (not last_first): extra leading axes are summed away one at a time with sum_dims(&[0]),
+    then each axis the operand held at extent 1 is summed with keepdim, from the last such axis backwards in the
+    first function and from the first forwards in the second."""
     want = list(want)
-    if g.ndim > len(want):
-        extra = g.ndim - len(want)
-        g = reduce_dims("sum", g, list(range(extra)), keepdim=False).reshape(g.shape[extra:])
-    dims = [i for i in range(g.ndim) if want[i] == 1 and g.shape[i] > 1]
-    if dims:
-        g = reduce_dims("sum", g, dims, keepdim=True)
+    g = _c(g)
+    if list(g.shape) == want:
+        return g
+    while g.ndim > len(want):
+        rest = g.shape[1:]
+        g = reduce_dims("sum", g, [0], keepdim=False).reshape(rest if rest else (1,))
+        if not rest:
+            break
+    dims = [i for i in range(min(g.ndim, len(want))) if want[i] == 1 and g.shape[i] > 1]
+    for i in (reversed(dims) if last_first else dims):
+        g = reduce_dims("sum", g, [i], keepdim=True)
     return np.ascontiguousarray(g).reshape(want)
+
+
+def broadcast_shape(sa, sb):
+    """tensor/ops/broadcasting.rs:100-135 and the panic text of add.rs:114-122."""
+    sa, sb = [int(x) for x in sa], [int(x) for x in sb]
+    n = max(len(sa), len(sb))
+    out = []
+    for i in range(n):
+        da = sa[len(sa) - 1 - i] if i < len(sa) else 1
+        db = sb[len(sb) - 1 - i] if i < len(sb) else 1
+        if da == db or db == 1:
+            out.append(da)
+        elif da == 1:
+            out.append(db)
+        else:
+            raise ValueError(f"Cannot broadcast tensor shapes {sa} and {sb}: Cannot broadcast shapes {sa} and {sb}: "
+                             f"incompatible dimensions at axis {n - 1 - i}")
+    return out[::-1]
+
+
+_BINARY = {"add": add, "sub": sub, "mul": mul, "div": div}
+
+
+def binary_broadcast(name, a, b):
+    """add/sub/mul/div_tensor with broadcasting (add.rs:107-146): both operands are stretched to the common shape
+    (the reference materialises them, broadcasting.rs:299-333) and the same-shape loop runs over the copies."""
+    a, b = _c(a), _c(b)
+    shape = broadcast_shape(a.shape, b.shape)
+    return _BINARY[name](np.broadcast_to(a, shape).copy(), np.broadcast_to(b, shape).copy())
+
+
+def binary_broadcast_backward(name, a, b, go):
+    """grad_fn/ops/{add,sub,mul,div}.rs with original_shapes: the full-size gradients over the broadcast shape, each
+    reduced to its operand's shape by grad_fn/utils.rs:23-60."""
+    a, b, go = _c(a), _c(b), _c(go)
+    shape = broadcast_shape(a.shape, b.shape)
+    fa, fb = np.broadcast_to(a, shape).copy(), np.broadcast_to(b, shape).copy()
+    go = go.reshape(shape)
+    if name == "add":
+        ga, gb = go, go
+    elif name == "sub":
+        ga, gb = go, neg(go)
+    elif name == "mul":
+        ga, gb = mul_bwd(fa, fb, go)
+    else:
+        ga, gb = div_bwd(fa, fb, go)
+    return _reduce_to_shape(ga, a.shape, last_first=False), _reduce_to_shape(gb, b.shape, last_first=False)
 
 
 def batched_matmul_backward(a, b, go):

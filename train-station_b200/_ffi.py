@@ -72,6 +72,8 @@ SIGNATURES = {
     "launch_square_backward_kernel": (C.c_bool, [vp, vp, vp, u64, vp]),
     "launch_mul_backward_kernel": (C.c_bool, [vp, vp, vp, vp, vp, u64, vp]),
     "launch_div_backward_kernel": (C.c_bool, [vp, vp, vp, vp, vp, u64, vp]),
+    "launch_binary_broadcast_kernel": (C.c_bool, [C.c_int, vp, u64p, C.c_int, vp, u64p, C.c_int, vp, vp]),
+    "launch_binary_broadcast_backward_kernel": (C.c_bool, [C.c_int, vp, u64p, C.c_int, vp, u64p, C.c_int, vp, vp, vp, vp]),
     "launch_scale_kernel": (C.c_bool, [vp, C.c_float, vp, u64, vp]),
     "launch_fill_kernel": (C.c_bool, [vp, C.c_float, u64, vp]),
     "launch_fill_from_scalar_kernel": (C.c_bool, [vp, vp, C.c_float, u64, vp]),

@@ -86,6 +86,12 @@ namespace k {
 constexpr size_t kReduceScratchElems = 4096;
 
 bool binary(int op, const float* a, const float* b, float* o, size_t n, cudaStream_t s);  // 0 add 1 sub 2 mul 3 div
+// the same four ops over a broadcast shape `dims` (outermost first); stride_a / stride_b are the operands' element
+// strides along those axes, 0 where an operand is stretched
+bool binary_bcast(int op, const float* a, const float* b, float* o, const size_t* dims, int rank, const size_t* stride_a,
+                  const size_t* stride_b, cudaStream_t s);
+bool binary_bcast_bwd(int op, const float* a, const float* b, const float* go, float* ga, float* gb, const size_t* dims, int rank,
+                      const size_t* stride_a, const size_t* stride_b, cudaStream_t s);
 bool bias_act(const float* z, const float* bias, float* o, size_t rows, size_t cols, bool relu, cudaStream_t s);
 bool add_scalar_bcast(const float* a, const float* scalar_dev, float* o, size_t n, cudaStream_t s);
 bool relu(const float* x, float* o, size_t n, cudaStream_t s);

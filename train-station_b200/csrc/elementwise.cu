@@ -264,7 +264,145 @@ __global__ void __launch_bounds__(kThreads) bias_act_scalar_kernel(const float* 
     }
 }
 
+// ---- NumPy-style broadcasting (tensor/ops/broadcasting.rs:100-135) without the reference's materialised operands:
+// outputs are contiguous over the broadcast shape, each input is read through element strides that are 0 along the
+// axes it is stretched over.  Axes are merged on the host, innermost first, so that typical cases (row, column,
+// outer product) reach the kernel with rank 1-3.
+constexpr int kBcastRank = 6;
+template <int NIN>
+struct BcastGeom {
+    int rank;
+    unsigned dims[kBcastRank];                               // innermost first
+    unsigned long long stride[NIN][kBcastRank];
+};
+
+// One group of VEC consecutive outputs along the innermost axis per thread and iteration.  VEC == 4 needs the
+// innermost extent to be a multiple of 4, innermost strides of 0 or 1 and 16-byte aligned rows (host-checked).
+template <int NIN, int NOUT, class F, int VEC>
+__global__ void __launch_bounds__(kThreads) bcast_kernel(Ptrs<NIN, NOUT> p, BcastGeom<NIN> g, size_t n_groups, F f) {
+    const size_t step = (size_t)gridDim.x * kThreads;
+    const unsigned d0 = g.dims[0] / VEC;
+    for (size_t gi = (size_t)blockIdx.x * kThreads + threadIdx.x; gi < n_groups; gi += step) {
+        size_t rem = gi / d0;
+        const size_t c0 = (gi - rem * d0) * VEC;
+        size_t off[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) off[a] = c0 * g.stride[a][0];
+        for (int d = 1; d < g.rank; ++d) {
+            const size_t q = rem / g.dims[d];
+            const size_t cd = rem - q * g.dims[d];
+            rem = q;
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) off[a] += cd * g.stride[a][d];
+        }
+        float xi[VEC][NIN], xo[VEC][NOUT];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) {
+            if (VEC == 4 && g.stride[a][0] == 1) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(p.in[a] + off[a]));
+                xi[0][a] = v.x; xi[1 % VEC][a] = v.y; xi[2 % VEC][a] = v.z; xi[3 % VEC][a] = v.w;
+            } else {
+                const float v = __ldg(p.in[a] + off[a]);     // stretched along the innermost axis (or VEC == 1)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) xi[e][a] = v;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) f.apply(xi[e], xo[e]);
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) {
+            if (!p.out[o]) continue;
+            if (VEC == 4) {
+                __stcs(reinterpret_cast<float4*>(p.out[o]) + gi, make_float4(xo[0][o], xo[1 % VEC][o], xo[2 % VEC][o], xo[3 % VEC][o]));
+            } else {
+                p.out[o][gi] = xo[0][o];
+            }
+        }
+    }
+}
+
+// dims (outermost first) and per-input strides over them; `contiguous_inputs` trailing inputs (the upstream
+// gradient of a backward pass) are read with the output's own contiguous strides.
+template <int NIN, int NOUT, class F>
+bool launch_bcast(Ptrs<NIN, NOUT> p, const size_t* dims, int rank, const size_t* const* strides, int strided_inputs, F f, cudaStream_t s) {
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    size_t n = 1;
+    for (int d = 0; d < rank; ++d) n *= dims[d];
+    if (n == 0) return true;
+    for (int a = 0; a < NIN; ++a)
+        if (!p.in[a]) { set_error("broadcast kernel: null input pointer"); return false; }
+    // innermost first, extents of 1 dropped, neighbours merged while every input walks them as one axis
+    BcastGeom<NIN> g;
+    g.rank = 0;
+    size_t contiguous = 1;
+    for (int d = rank - 1; d >= 0; --d) {
+        const size_t ext = dims[d];
+        size_t st[NIN];
+        for (int a = 0; a < NIN; ++a) st[a] = a < strided_inputs ? (ext == 1 ? 0 : strides[a][d]) : contiguous;
+        contiguous *= ext;
+        if (ext == 1) continue;
+        bool merge = g.rank > 0;
+        for (int a = 0; a < NIN && merge; ++a) merge = st[a] == g.stride[a][g.rank - 1] * g.dims[g.rank - 1];
+        if (merge && (size_t)g.dims[g.rank - 1] * ext <= 0xFFFFFFFFull) {
+            g.dims[g.rank - 1] *= (unsigned)ext;
+            continue;
+        }
+        if (g.rank == kBcastRank || ext > 0xFFFFFFFFull) { set_error("broadcast: more than %d separate axes after merging", kBcastRank); return false; }
+        g.dims[g.rank] = (unsigned)ext;
+        for (int a = 0; a < NIN; ++a) g.stride[a][g.rank] = st[a];
+        ++g.rank;
+    }
+    if (g.rank == 0) {                                       // a single element
+        g.rank = 1;
+        g.dims[0] = 1;
+        for (int a = 0; a < NIN; ++a) g.stride[a][0] = 0;
+    }
+    bool vec = g.dims[0] % 4 == 0;
+    for (int a = 0; a < NIN && vec; ++a) {
+        vec = g.stride[a][0] <= 1 && (g.stride[a][0] == 0 || aligned16(p.in[a]));
+        for (int d = 1; d < g.rank && vec; ++d) vec = g.stride[a][0] == 0 || g.stride[a][d] % 4 == 0;
+    }
+    for (int o = 0; o < NOUT; ++o) vec = vec && aligned16(p.out[o]);
+    int n_out = 0;
+    for (int o = 0; o < NOUT; ++o) n_out += p.out[o] ? 1 : 0;
+    if (!n_out) { set_error("broadcast kernel: null output pointer"); return false; }
+    ProfScope prof(kProfElementwise, s, 4.0 * (double)n * (n_out + NIN - strided_inputs));
+    const size_t n_groups = vec ? n / 4 : n;
+    const size_t want = (n_groups + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm;
+    const int grid = (int)(want < cap ? want : cap);
+    if (vec) bcast_kernel<NIN, NOUT, F, 4><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    else bcast_kernel<NIN, NOUT, F, 1><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    return cuda_ok(cudaGetLastError(), "broadcast launch");
+}
+
 }  // namespace
+
+bool binary_bcast(int op, const float* a, const float* b, float* o, const size_t* dims, int rank, const size_t* stride_a,
+                  const size_t* stride_b, cudaStream_t s) {
+    Ptrs<2, 1> p{{a, b}, {o}};
+    const size_t* st[2] = {stride_a, stride_b};
+    switch (op) {
+        case 0: return launch_bcast(p, dims, rank, st, 2, AddF{}, s);
+        case 1: return launch_bcast(p, dims, rank, st, 2, SubF{}, s);
+        case 2: return launch_bcast(p, dims, rank, st, 2, MulF{}, s);
+        case 3: return launch_bcast(p, dims, rank, st, 2, DivF{}, s);
+    }
+    set_error("binary_bcast: unknown op %d", op);
+    return false;
+}
+
+// Full-size gradients of a broadcast mul (op 2) or div (op 3): ga = go*b or go/b, gb = go*a or -((go*a)/(b*b)),
+// each over the broadcast shape (grad_fn/ops/mul.rs, div.rs); the caller sums them back to the operands' shapes.
+bool binary_bcast_bwd(int op, const float* a, const float* b, const float* go, float* ga, float* gb, const size_t* dims, int rank,
+                      const size_t* stride_a, const size_t* stride_b, cudaStream_t s) {
+    Ptrs<3, 2> p{{a, b, go}, {ga, gb}};
+    const size_t* st[2] = {stride_a, stride_b};
+    if (op == 2) return launch_bcast(p, dims, rank, st, 2, MulBwdF{}, s);
+    if (op == 3) return launch_bcast(p, dims, rank, st, 2, DivBwdF{}, s);
+    set_error("binary_bcast_bwd: unknown op %d", op);
+    return false;
+}
 
 bool binary(int op, const float* a, const float* b, float* o, size_t n, cudaStream_t s) {
     Ptrs<2, 1> p{{a, b}, {o}};
@@ -449,6 +587,43 @@ TS_API bool launch_mul_backward_kernel(const float* a, const float* b, const flo
                                        unsigned long long n, void* stream) {
     TS_STREAM_OR_FAIL(s);
     return k::mul_bwd(a, b, go, ga, gb, n, s);
+}
+namespace {
+// shapes of the two operands -> the broadcast shape and each operand's strides over it; false on a mismatch
+bool broadcast_plan(const unsigned long long* dims_a, int rank_a, const unsigned long long* dims_b, int rank_b, size_t* out, size_t* sa,
+                    size_t* sb, int* rank) {
+    if (rank_a < 1 || rank_b < 1 || rank_a > 8 || rank_b > 8 || !dims_a || !dims_b) { ts::set_error("broadcast: rank must be 1..8"); return false; }
+    const int n = rank_a > rank_b ? rank_a : rank_b;
+    size_t run_a = 1, run_b = 1;
+    for (int i = 0; i < n; ++i) {
+        const size_t da = i < rank_a ? dims_a[rank_a - 1 - i] : 1, db = i < rank_b ? dims_b[rank_b - 1 - i] : 1;
+        if (da != db && da != 1 && db != 1) { ts::set_error("broadcast: incompatible dimensions at axis %d", n - 1 - i); return false; }
+        out[n - 1 - i] = da == 1 ? db : da;
+        sa[n - 1 - i] = da == 1 ? 0 : run_a;
+        sb[n - 1 - i] = db == 1 ? 0 : run_b;
+        run_a *= da;
+        run_b *= db;
+    }
+    *rank = n;
+    return true;
+}
+}  // namespace
+TS_API bool launch_binary_broadcast_kernel(int op, const float* a, const unsigned long long* dims_a, int rank_a, const float* b,
+                                           const unsigned long long* dims_b, int rank_b, float* out, void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    size_t od[8], sa[8], sb[8];
+    int rank;
+    if (!broadcast_plan(dims_a, rank_a, dims_b, rank_b, od, sa, sb, &rank)) return false;
+    return k::binary_bcast(op, a, b, out, od, rank, sa, sb, s);
+}
+TS_API bool launch_binary_broadcast_backward_kernel(int op, const float* a, const unsigned long long* dims_a, int rank_a, const float* b,
+                                                    const unsigned long long* dims_b, int rank_b, const float* go, float* ga, float* gb,
+                                                    void* stream) {
+    TS_STREAM_OR_FAIL(s);
+    size_t od[8], sa[8], sb[8];
+    int rank;
+    if (!broadcast_plan(dims_a, rank_a, dims_b, rank_b, od, sa, sb, &rank)) return false;
+    return k::binary_bcast_bwd(op, a, b, go, ga, gb, od, rank, sa, sb, s);
 }
 TS_API bool launch_div_backward_kernel(const float* a, const float* b, const float* go, float* ga, float* gb,
                                        unsigned long long n, void* stream) {

@@ -394,6 +394,42 @@ static bool is_suffix_broadcast(const std::vector<size_t>& big, const std::vecto
     return true;
 }
 
+// a shape as Rust's {:?} prints a Vec<usize>: "[2, 3]"
+static std::string dims_debug(const std::vector<size_t>& d) {
+    std::string s = "[";
+    for (size_t i = 0; i < d.size(); ++i) s += (i ? ", " : "") + std::to_string(d[i]);
+    return s + "]";
+}
+// tensor/ops/broadcasting.rs:100-135: axes pair up from the right; equal extents or a 1 on either side; the message
+// is the one add/sub/mul/div_tensor panic with (add.rs:114-122 around the Display of BroadcastError).
+static bool broadcast_shape(const std::vector<size_t>& a, const std::vector<size_t>& b, std::vector<size_t>* out) {
+    const size_t ra = a.size(), rb = b.size(), n = ra > rb ? ra : rb;
+    out->assign(n, 1);
+    for (size_t i = 0; i < n; ++i) {
+        const size_t da = i < ra ? a[ra - 1 - i] : 1, db = i < rb ? b[rb - 1 - i] : 1;
+        if (da != db && da != 1 && db != 1) {
+            const std::string sa = dims_debug(a), sb = dims_debug(b);
+            set_error("Cannot broadcast tensor shapes %s and %s: Cannot broadcast shapes %s and %s: incompatible dimensions at axis %zu",
+                      sa.c_str(), sb.c_str(), sa.c_str(), sb.c_str(), n - 1 - i);
+            return false;
+        }
+        (*out)[n - 1 - i] = da == 1 ? db : da;
+    }
+    return true;
+}
+// element strides of a contiguous operand of shape `own` along the axes of the broadcast shape `out`: 0 where the
+// operand is stretched (broadcasting.rs compute_broadcast_strides)
+static std::vector<size_t> broadcast_strides(const std::vector<size_t>& own, const std::vector<size_t>& out) {
+    std::vector<size_t> st(out.size(), 0);
+    size_t run = 1;
+    for (size_t i = 0; i < own.size(); ++i) {
+        const size_t d = own[own.size() - 1 - i];
+        if (d != 1) st[out.size() - 1 - i] = run;
+        run *= d;
+    }
+    return st;
+}
+
 static TensorP grad_lookup(uint64_t id) {
     auto it = g_graph.grads.find(id);
     return it == g_graph.grads.end() ? nullptr : it->second;
@@ -501,6 +537,12 @@ static bool batched_gemm(DeviceCtx* c, const TensorP& ta, const std::vector<size
 // were 1 in the operand are summed with keepdim.
 static TensorP reduce_to_shape(DeviceCtx* c, const TensorP& g, const std::vector<size_t>& want) {
     if (g->dims == want) return g;
+    if (!materialize(g)) return nullptr;
+    if (g->size == 0) {                          // nothing to sum: zeros of the wanted shape
+        TensorP z = new_tensor(c, want);
+        if (z && z->size && !k::fill(z->st->ptr, 0.0f, z->size, c->compute)) return nullptr;
+        return z;
+    }
     TensorP cur = g;
     auto sum_axes = [&](const std::vector<unsigned char>& red, const std::vector<size_t>& od) -> TensorP {
         TensorP o = new_tensor(c, od);
@@ -544,7 +586,11 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
                 size_t osz = 1; for (size_t x : od) osz *= x;
                 if (osz == go->size) { gin[i] = reshaped_alias(go, od); if (!gin[i]) return false; continue; }
                 size_t rows, cols;
-                if (!is_suffix_broadcast(other, od, &rows, &cols)) { set_error("backward(add): unsupported broadcast"); return false; }
+                if (!is_suffix_broadcast(other, od, &rows, &cols)) {
+                    gin[i] = reduce_to_shape(c, go, od);       // broadcasting in general
+                    if (!gin[i]) return false;
+                    continue;
+                }
                 auto pre = g_graph.bias_grad_ready.find(out_id);
                 if (pre != g_graph.bias_grad_ready.end() && pre->second->size == cols) {
                     gin[i] = reshaped_alias(pre->second, od);
@@ -574,11 +620,16 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             return true;
         }
         case Op::Sub: {
-            // grad_fn/ops/sub.rs:4-33: (go, -go)
-            if (nd.needs[0]) gin[0] = go;
+            // grad_fn/ops/sub.rs:4-33: (go, -go), each summed back to its operand's shape after a broadcast
+            // (negating before or after the sums gives the same bits)
+            if (nd.needs[0]) {
+                gin[0] = nd.dims0 == go->dims ? go : reduce_to_shape(c, go, nd.dims0);
+                if (!gin[0]) return false;
+            }
             if (nd.needs[1]) {
-                const float* gp = rptr(go);
-                TensorP r = gp ? new_tensor(c, go->dims) : nullptr;
+                TensorP g1 = nd.dims1 == go->dims ? go : reduce_to_shape(c, go, nd.dims1);
+                const float* gp = g1 ? rptr(g1) : nullptr;
+                TensorP r = gp ? new_tensor(c, g1->dims) : nullptr;
                 if (!r || !k::scale(gp, -1.0f, r->st->ptr, r->size, s)) return false;
                 gin[1] = r;
             }
@@ -589,6 +640,22 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             if (!nd.s0.check("mul/div") || !nd.s1.check("mul/div")) return false;
             const float *a = rptr(nd.s0.t), *b = rptr(nd.s1.t), *gp = rptr(go);
             if (!a || !b || !gp) return false;
+            if (nd.dims0 != nd.dims1) {
+                // grad_fn/ops/mul.rs, div.rs with original_shapes: the full-size gradients over the broadcast
+                // shape, then each summed back to its operand's shape (grad_fn/utils.rs:23-60)
+                std::vector<size_t> od;
+                if (!broadcast_shape(nd.dims0, nd.dims1, &od)) return false;
+                TensorP fa = nd.needs[0] ? new_tensor(c, od) : nullptr;
+                TensorP fb = nd.needs[1] ? new_tensor(c, od) : nullptr;
+                if ((nd.needs[0] && !fa) || (nd.needs[1] && !fb)) return false;
+                const std::vector<size_t> sa = broadcast_strides(nd.dims0, od), sb = broadcast_strides(nd.dims1, od);
+                if (!k::binary_bcast_bwd(nd.op == Op::Mul ? 2 : 3, a, b, gp, fa ? fa->st->ptr : nullptr, fb ? fb->st->ptr : nullptr, od.data(),
+                                         (int)od.size(), sa.data(), sb.data(), s))
+                    return false;
+                if (fa && !(gin[0] = reduce_to_shape(c, fa, nd.dims0))) return false;
+                if (fb && !(gin[1] = reduce_to_shape(c, fb, nd.dims1))) return false;
+                return true;
+            }
             TensorP ga = nd.needs[0] ? new_tensor(c, go->dims) : nullptr;
             TensorP gb = nd.needs[1] ? new_tensor(c, go->dims) : nullptr;
             if ((nd.needs[0] && !ga) || (nd.needs[1] && !gb)) return false;
@@ -1194,31 +1261,36 @@ static ts_tensor* binary_op(ts_tensor* ha, ts_tensor* hb, int op, const char* na
         const float *pa = rptr(a), *pb = rptr(b);
         out = (pa && pb) ? new_tensor(c, a->dims) : nullptr;
         if (!out || !k::binary(op, pa, pb, out->st->ptr, out->size, c->compute)) return nullptr;
-    } else if (op == 0) {
-        // add with broadcasting (add.rs:107-146 -> broadcasting.rs:299-333), without materialising the broadcast
+    } else {
+        // NumPy-style broadcasting (add.rs:107-146 -> broadcasting.rs:299-333), read through strides instead of
+        // the reference's materialised operands
+        std::vector<size_t> od;
+        if (!broadcast_shape(a->dims, b->dims, &od)) return nullptr;
         TensorP big = a->size >= b->size ? a : b, small = a->size >= b->size ? b : a;
-        size_t rows, cols;
-        if (!is_suffix_broadcast(big->dims, small->dims, &rows, &cols)) {
-            set_error("add_tensor: shapes are not broadcast-compatible on this path (a smaller operand must match the trailing dimensions)");
-            return nullptr;
-        }
-        // deferred GEMM + row bias: fold the add into the GEMM epilogue
-        if (fusion_enabled() && big->pending && !big->pending->bias && !big->pending->relu && !big->pending->mask && cols == big->pending->n && cols > 1) {
+        size_t rows = 0, cols = 0;
+        const bool bias_like = op == 0 && od == big->dims && is_suffix_broadcast(big->dims, small->dims, &rows, &cols);
+        if (bias_like && fusion_enabled() && big->pending && !big->pending->bias && !big->pending->relu && !big->pending->mask &&
+            cols == big->pending->n && cols > 1) {
+            // deferred GEMM + row bias: fold the add into the GEMM epilogue
             out = std::make_shared<TensorImpl>(big->dims);
             out->pending.reset(new PendingGemm(*big->pending));
             out->pending->bias = small;
             register_pending(out);
-        } else {
+        } else if (bias_like) {
+            // the smaller operand matches the trailing dimensions of the larger one
             const float *pb = rptr(big), *ps = rptr(small);
             out = (pb && ps) ? new_tensor(c, big->dims) : nullptr;
             if (!out) return nullptr;
             bool ok = cols == 1 ? k::add_scalar_bcast(pb, ps, out->st->ptr, out->size, c->compute)
                                 : k::bias_act(pb, ps, out->st->ptr, rows, cols, false, c->compute);
             if (!ok) return nullptr;
+        } else {
+            const float *pa = rptr(a), *pb = rptr(b);
+            out = (pa && pb) ? new_tensor(c, od) : nullptr;
+            if (!out) return nullptr;
+            const std::vector<size_t> sa = broadcast_strides(a->dims, od), sb = broadcast_strides(b->dims, od);
+            if (!k::binary_bcast(op, pa, pb, out->st->ptr, od.data(), (int)od.size(), sa.data(), sb.data(), c->compute)) return nullptr;
         }
-    } else {
-        set_error("%s: operands must have the same shape on this path (broadcasting is implemented for add_tensor only)", name);
-        return nullptr;
     }
     if (track) {
         Node nd;
