@@ -274,48 +274,64 @@ struct BcastGeom {
     int rank;
     unsigned dims[kBcastRank];                               // innermost first
     unsigned long long stride[NIN][kBcastRank];
+    bool reused[NIN];                                        // stretched along at least one axis
 };
 
 // One group of VEC consecutive outputs along the innermost axis per thread and iteration.  VEC == 4 needs the
 // innermost extent to be a multiple of 4, innermost strides of 0 or 1 and 16-byte aligned rows (host-checked).
-template <int NIN, int NOUT, class F, int VEC>
+// IDX is unsigned when the group count fits 32 bits (cheap divisions), size_t otherwise.  kUnroll groups per thread
+// are loaded before any is computed, as in ew_vec_kernel, so that several 128-bit loads are in flight per thread.
+template <int NIN, int NOUT, class F, int VEC, typename IDX>
 __global__ void __launch_bounds__(kThreads) bcast_kernel(Ptrs<NIN, NOUT> p, BcastGeom<NIN> g, size_t n_groups, F f) {
-    const size_t step = (size_t)gridDim.x * kThreads;
+    const size_t step = (size_t)gridDim.x * kThreads * kUnroll;
     const unsigned d0 = g.dims[0] / VEC;
-    for (size_t gi = (size_t)blockIdx.x * kThreads + threadIdx.x; gi < n_groups; gi += step) {
-        size_t rem = gi / d0;
-        const size_t c0 = (gi - rem * d0) * VEC;
-        size_t off[NIN];
+    for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n_groups; base += step) {
+        float xi[kUnroll][VEC][NIN];
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) off[a] = c0 * g.stride[a][0];
-        for (int d = 1; d < g.rank; ++d) {
-            const size_t q = rem / g.dims[d];
-            const size_t cd = rem - q * g.dims[d];
-            rem = q;
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t gi = base + (size_t)u * kThreads;
+            if (gi >= n_groups) break;
+            IDX rem = (IDX)gi / d0;
+            const size_t c0 = (size_t)((IDX)gi - rem * d0) * VEC;
+            size_t off[NIN];
 #pragma unroll
-            for (int a = 0; a < NIN; ++a) off[a] += cd * g.stride[a][d];
-        }
-        float xi[VEC][NIN], xo[VEC][NOUT];
+            for (int a = 0; a < NIN; ++a) off[a] = c0 * g.stride[a][0];
+            for (int d = 1; d < g.rank; ++d) {
+                const IDX q = rem / g.dims[d];
+                const size_t cd = rem - q * g.dims[d];
+                rem = q;
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) {
-            if (VEC == 4 && g.stride[a][0] == 1) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(p.in[a] + off[a]));
-                xi[0][a] = v.x; xi[1 % VEC][a] = v.y; xi[2 % VEC][a] = v.z; xi[3 % VEC][a] = v.w;
-            } else {
-                const float v = __ldg(p.in[a] + off[a]);     // stretched along the innermost axis (or VEC == 1)
+                for (int a = 0; a < NIN; ++a) off[a] += cd * g.stride[a][d];
+            }
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) xi[e][a] = v;
+            for (int a = 0; a < NIN; ++a) {
+                if (VEC == 4 && g.stride[a][0] == 1) {
+                    // an operand that is stretched along some axis is read many times: keep it cached
+                    const float4* q4 = reinterpret_cast<const float4*>(p.in[a] + off[a]);
+                    const float4 v = g.reused[a] ? __ldg(q4) : __ldcs(q4);
+                    xi[u][0][a] = v.x; xi[u][1 % VEC][a] = v.y; xi[u][2 % VEC][a] = v.z; xi[u][3 % VEC][a] = v.w;
+                } else {
+                    const float v = __ldg(p.in[a] + off[a]);     // stretched along the innermost axis (or VEC == 1)
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) xi[u][e][a] = v;
+                }
             }
         }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) f.apply(xi[e], xo[e]);
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t gi = base + (size_t)u * kThreads;
+            if (gi >= n_groups) break;
+            float xo[VEC][NOUT];
 #pragma unroll
-        for (int o = 0; o < NOUT; ++o) {
-            if (!p.out[o]) continue;
-            if (VEC == 4) {
-                __stcs(reinterpret_cast<float4*>(p.out[o]) + gi, make_float4(xo[0][o], xo[1 % VEC][o], xo[2 % VEC][o], xo[3 % VEC][o]));
-            } else {
-                p.out[o][gi] = xo[0][o];
+            for (int e = 0; e < VEC; ++e) f.apply(xi[u][e], xo[e]);
+#pragma unroll
+            for (int o = 0; o < NOUT; ++o) {
+                if (!p.out[o]) continue;
+                if (VEC == 4) {
+                    __stcs(reinterpret_cast<float4*>(p.out[o]) + gi, make_float4(xo[0][o], xo[1 % VEC][o], xo[2 % VEC][o], xo[3 % VEC][o]));
+                } else {
+                    p.out[o][gi] = xo[0][o];
+                }
             }
         }
     }
@@ -368,11 +384,17 @@ bool launch_bcast(Ptrs<NIN, NOUT> p, const size_t* dims, int rank, const size_t*
     for (int o = 0; o < NOUT; ++o) n_out += p.out[o] ? 1 : 0;
     if (!n_out) { set_error("broadcast kernel: null output pointer"); return false; }
     ProfScope prof(kProfElementwise, s, 4.0 * (double)n * (n_out + NIN - strided_inputs));
+    for (int a = 0; a < NIN; ++a) {
+        g.reused[a] = false;
+        for (int d = 0; d < g.rank; ++d) g.reused[a] = g.reused[a] || (g.stride[a][d] == 0 && g.dims[d] > 1);
+    }
     const size_t n_groups = vec ? n / 4 : n;
-    const size_t want = (n_groups + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm;
-    const int grid = (int)(want < cap ? want : cap);
-    if (vec) bcast_kernel<NIN, NOUT, F, 4><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
-    else bcast_kernel<NIN, NOUT, F, 1><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    const int grid = grid_for(n_groups, c->sm_count);
+    const bool small = n_groups <= 0xFFFFFFFFull;
+    if (vec && small) bcast_kernel<NIN, NOUT, F, 4, unsigned><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    else if (vec) bcast_kernel<NIN, NOUT, F, 4, size_t><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    else if (small) bcast_kernel<NIN, NOUT, F, 1, unsigned><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    else bcast_kernel<NIN, NOUT, F, 1, size_t><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
     return cuda_ok(cudaGetLastError(), "broadcast launch");
 }
 
