@@ -52,11 +52,16 @@ struct AdamTable { AdamTensor t[kMaxTensorsPerLaunch]; };
 
 template <bool AMS>
 __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ AdamTable tab, const ChunkEntry* __restrict__ chunks,
-                                                        int chunk_base, int tensor_base, Scalars sc) {
-    const ChunkEntry ce = chunks[chunk_base + blockIdx.x];
+                                                        int chunk_base, int tensor_base, int split_log2, Scalars sc) {
+    // 2^split_log2 CTAs share a chunk (each a 1024-element-aligned slice of it): small parameter sets, which would
+    // otherwise run as a handful of CTAs making sixteen dependent trips each, spread over the SMs instead
+    const ChunkEntry ce = chunks[chunk_base + (blockIdx.x >> split_log2)];
     const AdamTensor t = tab.t[ce.tensor - tensor_base];
     const unsigned long long body = t.n / 8 * 8;
-    unsigned long long end = ce.offset + kChunk;
+    const unsigned long long slice = kChunk >> split_log2;
+    const unsigned long long start = ce.offset + (blockIdx.x & ((1u << split_log2) - 1)) * slice;
+    if (start >= t.n) return;
+    unsigned long long end = start + slice;
     if (end > t.n) end = t.n;
     uintptr_t bits = reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
                      reinterpret_cast<uintptr_t>(t.v);
@@ -64,8 +69,8 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
     const bool vec = (bits & 15) == 0;
     float unused = 0.0f;
     if (vec) {
-        // ce.offset is a multiple of kChunk, hence of 4
-        const unsigned long long v0 = ce.offset / 4, v1 = end / 4;
+        // start is a multiple of 1024, hence of 4
+        const unsigned long long v0 = start / 4, v1 = end / 4;
         float4* pp = reinterpret_cast<float4*>(t.p);
         const float4* gp = reinterpret_cast<const float4*>(t.g);
         float4* mp = reinterpret_cast<float4*>(t.m);
@@ -104,7 +109,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
             if (AMS) t.vmax[i] = x;
         }
     } else {
-        for (unsigned long long i = ce.offset + threadIdx.x; i < end; i += kThreads) {
+        for (unsigned long long i = start + threadIdx.x; i < end; i += kThreads) {
             float p = t.p[i], m = t.m[i], v = t.v[i], x = AMS ? t.vmax[i] : unused;
             adam_one<AMS>(p, t.g[i], m, v, x, i < body, sc);
             t.p[i] = p; t.m[i] = m; t.v[i] = v;
@@ -160,8 +165,13 @@ bool adam_launch_range(const AdamTensor* tensors, int first, int last, const voi
             // every tensor of one optimizer has a running maximum, or none has
             const bool ams = tab.t[0].vmax != nullptr;
             ProfScope prof(kProfAdam, s, (ams ? 36.0 : 28.0) * elems);
-            if (ams) adam_kernel<true><<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
-            else adam_kernel<false><<<n_chunks, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, sc);
+            DeviceCtx* c = ctx();
+            const int want = 2 * (c ? c->sm_count : 148);
+            int split_log2 = 0;
+            while (split_log2 < 4 && (n_chunks << split_log2) < want) ++split_log2;
+            const int grid = n_chunks << split_log2;
+            if (ams) adam_kernel<true><<<grid, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
+            else adam_kernel<false><<<grid, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
             if (!cuda_ok(cudaGetLastError(), "adam launch")) return false;
         }
         chunk_base += n_chunks;

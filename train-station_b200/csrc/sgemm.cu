@@ -179,12 +179,21 @@ void launch(const GemmArgs& g, dim3 grid, cudaStream_t s) {
 // The same arithmetic on 32 x 32 tiles (2 x 2 outputs per thread, 32 k per stage) for results that would fill only a
 // few 128 x 128 tiles: a [1024 x 10] bias-layer weight gradient reduced over 4096 rows is 8 CTAs of the big kernel,
 // each walking all of K alone, but 32 CTAs here.  Per output element the chain over p is unchanged.
+// These shapes are latency-bound (a handful of CTAs, each walking all of K), so the k-stages arrive through a ring
+// of asynchronous 4-byte copies (transposing as they land, zero-filled outside the matrices) three stages ahead of
+// the one being multiplied: a stage costs its 32 multiply-add steps, not a round trip to memory.
 constexpr int SM_T = 32;
+constexpr int SM_STAGES = 4;
+
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* gmem_src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(valid ? 4 : 0) : "memory");
+}
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
-    __shared__ float As[SM_T][SM_T + 1];   // [k][m]
-    __shared__ float Bs[SM_T][SM_T + 1];   // [k][n]
+    __shared__ float As[SM_STAGES][SM_T][SM_T + 1];   // [stage][k][m]
+    __shared__ float Bs[SM_STAGES][SM_T][SM_T + 1];   // [stage][k][n]
     const int t = threadIdx.x, ty = t / 16, tx = t % 16;
     const size_t m0 = (size_t)blockIdx.y * SM_T, n0 = (size_t)blockIdx.x * SM_T;
     const size_t M = g.m, N = g.n, K = g.k;
@@ -193,26 +202,44 @@ __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) tailc[j] = HAS_TAIL && (n0 + tx * 2 + j) >= N / 8 * 8;
 
-    for (size_t k0 = 0; k0 < K; k0 += SM_T) {
+    auto issue = [&](int slot, size_t k0) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int e = t + kThreads * q, lo = e % SM_T, hi = e / SM_T;
             {   // A: stored [K][M] (TA, contiguous along m) or [M][K] (contiguous along k)
                 const int kk = TA ? hi : lo, mm = TA ? lo : hi;
                 const size_t p = k0 + kk, i = m0 + mm;
-                As[kk][mm] = (p < K && i < M) ? (TA ? g.a[p * M + i] : g.a[i * K + p]) : 0.0f;
+                const bool in = p < K && i < M;
+                cp_async4(&As[slot][kk][mm], in ? (TA ? g.a + p * M + i : g.a + i * K + p) : g.a, in);
             }
             {   // B: stored [N][K] (TB, contiguous along k) or [K][N] (contiguous along n)
                 const int kk = TB ? lo : hi, nn = TB ? hi : lo;
                 const size_t p = k0 + kk, j = n0 + nn;
-                Bs[kk][nn] = (p < K && j < N) ? (TB ? g.b[j * K + p] : g.b[p * N + j]) : 0.0f;
+                const bool in = p < K && j < N;
+                cp_async4(&Bs[slot][kk][nn], in ? (TB ? g.b + j * K + p : g.b + p * N + j) : g.b, in);
             }
         }
-        __syncthreads();
+    };
+
+    const size_t nk = (K + SM_T - 1) / SM_T;
+#pragma unroll
+    for (int st = 0; st < SM_STAGES - 1; ++st) {
+        if ((size_t)st < nk) issue(st, (size_t)st * SM_T);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (size_t kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(SM_STAGES - 2) : "memory");   // this thread's part of stage kt landed
+        __syncthreads();                            // everyone's part landed; everyone is done with stage kt - 1
+        const size_t nxt = kt + SM_STAGES - 1;
+        if (nxt < nk) issue((int)(nxt % SM_STAGES), nxt * SM_T);     // into the slot stage kt - 1 used
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const int slot = (int)(kt % SM_STAGES);
+        const size_t k0 = kt * SM_T;
         const int pmax = (K - k0) < (size_t)SM_T ? (int)(K - k0) : SM_T;   // no padded terms enter the chain
+#pragma unroll 8
         for (int p = 0; p < pmax; ++p) {
-            const float a0 = As[p][ty * 2], a1 = As[p][ty * 2 + 1];
-            const float b[2] = {Bs[p][tx * 2], Bs[p][tx * 2 + 1]};
+            const float a0 = As[slot][p][ty * 2], a1 = As[slot][p][ty * 2 + 1];
+            const float b[2] = {Bs[slot][p][tx * 2], Bs[slot][p][tx * 2 + 1]};
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 if (HAS_TAIL && tailc[j]) {
@@ -224,7 +251,6 @@ __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
