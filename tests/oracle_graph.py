@@ -43,6 +43,13 @@ class OracleGraph:
 
     def op(self, name, *args):
         o = self.o
+        if name == "matmul" and (args[0].data.ndim > 2 or args[1].data.ndim > 2):
+            a, b = args
+
+            def bw(g):
+                ga, gb = o.batched_matmul_backward(a.data, b.data, g)
+                return [ga if a.rg else None, gb if b.rg else None]
+            return self._mk(o.batched_matmul(a.data, b.data), [a, b], bw)
         if name == "matmul":
             a, b = args
             a2 = a.data.reshape(1, -1) if a.data.ndim == 1 else a.data
@@ -67,6 +74,14 @@ class OracleGraph:
                      else o.add(big.data, np.full_like(big.data, small.data.reshape(-1)[0]))).reshape(big.data.shape)
             return self._mk(r, [a, b], lambda g: [self._unbroadcast(o, g, a.data.shape) if a.rg else None,
                                                   self._unbroadcast(o, g, b.data.shape) if b.rg else None])
+        if name in ("sub_tensor", "mul_tensor", "div_tensor") and args[0].data.shape != args[1].data.shape:
+            a, b = args                      # NumPy-style broadcasting: the stretched operands, then the same-shape op
+            kind = name[:3]
+
+            def bw(g):
+                ga, gb = o.binary_broadcast_backward(kind, a.data, b.data, g)
+                return [ga if a.rg else None, gb if b.rg else None]
+            return self._mk(o.binary_broadcast(kind, a.data, b.data), [a, b], bw)
         if name == "sub_tensor":
             a, b = args
             return self._mk(o.sub(a.data, b.data), [a, b], lambda g: [g if a.rg else None, o.neg(g) if b.rg else None])

@@ -10,6 +10,7 @@ from oracle_graph import run_case_oracle
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 KNOWN = json.load(open(os.path.join(GOLDEN, "reference_known_answers.json")))
+KNOWN["cases"] = KNOWN["cases"] + json.load(open(os.path.join(GOLDEN, "reference_known_answers_broadcast.json")))["cases"]
 
 
 @pytest.mark.parametrize("case", KNOWN["cases"], ids=[c["name"] for c in KNOWN["cases"]])

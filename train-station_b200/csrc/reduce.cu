@@ -38,7 +38,8 @@ __device__ __forceinline__ float block_sum(float v) {
 // MODE 0: sum(x); MODE 1: sum((x-y)^2)
 template <int MODE>
 __global__ void __launch_bounds__(kThreads) sum_stage1(const float* __restrict__ x, const float* __restrict__ y,
-                                                       float* __restrict__ partial, size_t n, int vec_ok) {
+                                                       float* __restrict__ partial, size_t n, int vec_ok, float* __restrict__ out,
+                                                       float divisor) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * kThreads;
@@ -93,7 +94,10 @@ __global__ void __launch_bounds__(kThreads) sum_stage1(const float* __restrict__
     }
     float v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     v = block_sum(v);
-    if (threadIdx.x == 0) partial[blockIdx.x] = v;
+    if (threadIdx.x != 0) return;
+    // a single CTA already holds the whole sum: the second stage (which would add 0s to it) is skipped
+    if (gridDim.x == 1) out[0] = divisor > 0.0f ? __fdiv_rn(v, divisor) : v;
+    else partial[blockIdx.x] = v;
 }
 
 __global__ void __launch_bounds__(kThreads) sum_stage2(const float* __restrict__ partial, int n_partial, float* __restrict__ out,
@@ -117,9 +121,10 @@ bool sum_impl(const float* x, const float* y, float* out, size_t n, bool mean, f
     if (cap > kReduceScratchElems) cap = kReduceScratchElems;
     int grid = (int)(want < cap ? want : cap);
     int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && (MODE == 0 || (reinterpret_cast<uintptr_t>(y) & 15) == 0);
-    ProfScope prof(kProfReduce, s, 4.0 * (double)n * (MODE == 1 ? 2 : 1), 2);
-    sum_stage1<MODE><<<grid, kThreads, 0, s>>>(x, y, scratch, n, vec_ok);
-    sum_stage2<<<1, kThreads, 0, s>>>(scratch, grid, out, mean ? (float)n : 0.0f);
+    const float divisor = mean ? (float)n : 0.0f;
+    ProfScope prof(kProfReduce, s, 4.0 * (double)n * (MODE == 1 ? 2 : 1), grid == 1 ? 1 : 2);
+    sum_stage1<MODE><<<grid, kThreads, 0, s>>>(x, y, scratch, n, vec_ok, out, divisor);
+    if (grid > 1) sum_stage2<<<1, kThreads, 0, s>>>(scratch, grid, out, divisor);
     return cuda_ok(cudaGetLastError(), "sum launch");
 }
 
