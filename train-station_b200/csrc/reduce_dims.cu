@@ -87,6 +87,43 @@ __global__ void __launch_bounds__(kThreads) reduce_kept_inner_kernel(const float
     out[(size_t)blockIdx.y * p.n_out + o] = acc;
 }
 
+// The same with four adjacent outputs per thread (128-bit loads, eight rows in flight): the innermost kept extent is a
+// multiple of 4 and everything is 16-byte aligned.  Each output still adds its terms in increasing reduced order.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) reduce_kept_inner_vec4_kernel(const float* __restrict__ x, const float* __restrict__ aux,
+                                                                          float* __restrict__ out, Plan p, size_t chunk) {
+    const size_t o = ((size_t)blockIdx.x * kThreads + threadIdx.x) * 4;
+    if (o >= p.n_out) return;
+    const size_t base = radix_offset(o, p.kdim, p.kstr, p.nk);
+    const size_t r0 = (size_t)blockIdx.y * chunk;
+    size_t r1 = r0 + chunk;
+    if (r1 > p.n_red) r1 = p.n_red;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (OP == kSqDev || OP == kCountEq) a = *reinterpret_cast<const float4*>(aux + o);
+    float4 acc = make_float4(identity<OP>(), identity<OP>(), identity<OP>(), identity<OP>());
+    auto fold = [&](const float4& v) {
+        acc.x = combine<OP>(acc.x, term<OP>(v.x, a.x));
+        acc.y = combine<OP>(acc.y, term<OP>(v.y, a.y));
+        acc.z = combine<OP>(acc.z, term<OP>(v.z, a.z));
+        acc.w = combine<OP>(acc.w, term<OP>(v.w, a.w));
+    };
+    if (p.nr == 1) {
+        const size_t rs = p.rstr[0];
+        size_t r = r0;
+        for (; r + 8 <= r1; r += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(x + base + (r + u) * rs));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) fold(v[u]);
+        }
+        for (; r < r1; ++r) fold(__ldcs(reinterpret_cast<const float4*>(x + base + r * rs)));
+    } else {
+        for (size_t r = r0; r < r1; ++r) fold(__ldcs(reinterpret_cast<const float4*>(x + base + radix_offset(r, p.rdim, p.rstr, p.nr))));
+    }
+    *reinterpret_cast<float4*>(out + (size_t)blockIdx.y * p.n_out + o) = acc;
+}
+
 // One warp per (output, split): the last input axis is reduced, lanes stride over the reduced range.
 template <int OP>
 __global__ void __launch_bounds__(kThreads) reduce_reduced_inner_kernel(const float* __restrict__ x, const float* __restrict__ aux,
@@ -102,18 +139,33 @@ __global__ void __launch_bounds__(kThreads) reduce_reduced_inner_kernel(const fl
         const float a = (OP == kSqDev || OP == kCountEq) ? aux[o] : 0.0f;
         float acc = identity<OP>();
         if (p.nr == 1 && p.rstr[0] == 1) {
-            // four independent loads and accumulators per lane
+            // a contiguous run: scalar loads up to the first 16-byte boundary, then four independent 128-bit loads
+            // and accumulators per lane (2 KB in flight per warp), then a scalar tail
+            const float* row = x + base;
+            const size_t mis = (reinterpret_cast<uintptr_t>(row + r0) & 15) >> 2;
+            size_t head = mis ? 4 - mis : 0;
+            if (head > r1 - r0) head = r1 - r0;
+            if ((size_t)lane < head) acc = combine<OP>(acc, term<OP>(row[r0 + lane], a));
+            const size_t rv = r0 + head, nvec = (r1 - rv) / 4;
+            const float4* v = reinterpret_cast<const float4*>(row + rv);
             float a1 = identity<OP>(), a2 = identity<OP>(), a3 = identity<OP>();
-            size_t r = r0 + lane;
-            for (; r + 96 < r1; r += 128) {
-                const float v0 = __ldcs(x + base + r), v1 = __ldcs(x + base + r + 32), v2 = __ldcs(x + base + r + 64),
-                            v3 = __ldcs(x + base + r + 96);
-                acc = combine<OP>(acc, term<OP>(v0, a));
-                a1 = combine<OP>(a1, term<OP>(v1, a));
-                a2 = combine<OP>(a2, term<OP>(v2, a));
-                a3 = combine<OP>(a3, term<OP>(v3, a));
+            auto fold = [&](float acc_, const float4& q) {
+                acc_ = combine<OP>(acc_, term<OP>(q.x, a));
+                acc_ = combine<OP>(acc_, term<OP>(q.y, a));
+                acc_ = combine<OP>(acc_, term<OP>(q.z, a));
+                return combine<OP>(acc_, term<OP>(q.w, a));
+            };
+            size_t i = lane;
+            for (; i + 96 < nvec; i += 128) {
+                const float4 v0 = __ldcs(v + i), v1 = __ldcs(v + i + 32), v2 = __ldcs(v + i + 64), v3 = __ldcs(v + i + 96);
+                acc = fold(acc, v0);
+                a1 = fold(a1, v1);
+                a2 = fold(a2, v2);
+                a3 = fold(a3, v3);
             }
-            for (; r < r1; r += 32) acc = combine<OP>(acc, term<OP>(__ldcs(x + base + r), a));
+            for (; i < nvec; i += 32) acc = fold(acc, __ldcs(v + i));
+            const size_t t = rv + nvec * 4 + lane;
+            if (t < r1) a1 = combine<OP>(a1, term<OP>(row[t], a));
             acc = combine<OP>(combine<OP>(acc, a1), combine<OP>(a2, a3));
         } else {
             for (size_t r = r0 + lane; r < r1; r += 32) acc = combine<OP>(acc, term<OP>(x[base + radix_offset(r, p.rdim, p.rstr, p.nr)], a));
@@ -129,14 +181,19 @@ bool launch_forward(const float* x, const float* aux, float* out, const Plan& p,
     const bool reduced_inner = p.nr > 0 && p.rstr[p.nr - 1] == 1;
     // how many ways to split the reduced range so that the GPU is busy
     size_t splits = 1;
+    bool vec4 = false;
     if (reduced_inner) {
         const size_t want_warps = (size_t)sm * 64;
         if (p.n_out < want_warps) splits = (want_warps + p.n_out - 1) / p.n_out;
         const size_t max_splits = (p.n_red + 2047) / 2048;     // at least 2048 elements per warp
         if (splits > max_splits) splits = max_splits;
     } else {
-        const size_t want_threads = (size_t)sm * 2048;
-        if (p.n_out < want_threads) splits = (want_threads + p.n_out - 1) / p.n_out;
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        vec4 = p.nk > 0 && p.kstr[p.nk - 1] == 1 && p.kdim[p.nk - 1] % 4 == 0 && al16(x) && al16(out) && al16(scratch) && (!aux || al16(aux));
+        for (int d = 0; d + 1 < p.nk && vec4; ++d) vec4 = p.kstr[d] % 4 == 0;
+        for (int d = 0; d < p.nr && vec4; ++d) vec4 = p.rstr[d] % 4 == 0;
+        const size_t want_threads = (size_t)sm * (vec4 ? 1024 : 2048), owners = vec4 ? p.n_out / 4 : p.n_out;
+        if (owners * 2 <= want_threads) splits = (want_threads + owners - 1) / owners;   // half a GPU of owners is enough
         const size_t max_splits = (p.n_red + 31) / 32;         // at least 32 elements per thread
         if (splits > max_splits) splits = max_splits;
     }
@@ -144,12 +201,16 @@ bool launch_forward(const float* x, const float* aux, float* out, const Plan& p,
     if (splits > 65535) splits = 65535;
     if (splits > 1 && splits * p.n_out > scratch_elems) splits = scratch_elems / p.n_out;
     if (splits < 1) splits = 1;
-    const size_t chunk = (p.n_red + splits - 1) / splits;
+    size_t chunk = (p.n_red + splits - 1) / splits;
+    if (reduced_inner && splits > 1) chunk = (chunk + 127) / 128 * 128;    // every split starts on the row's alignment
     splits = (p.n_red + chunk - 1) / chunk;
     float* dst = splits > 1 ? scratch : out;
     if (reduced_inner) {
         const size_t units = p.n_out * splits, want = (units + 7) / 8, cap = (size_t)sm * 32;
         reduce_reduced_inner_kernel<OP><<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(x, aux, dst, p, chunk, splits);
+    } else if (vec4) {
+        dim3 grid((unsigned)((p.n_out / 4 + kThreads - 1) / kThreads), (unsigned)splits);
+        reduce_kept_inner_vec4_kernel<OP><<<grid, kThreads, 0, s>>>(x, aux, dst, p, chunk);
     } else {
         dim3 grid((unsigned)((p.n_out + kThreads - 1) / kThreads), (unsigned)splits);
         reduce_kept_inner_kernel<OP><<<grid, kThreads, 0, s>>>(x, aux, dst, p, chunk);
