@@ -262,6 +262,57 @@ __global__ void __launch_bounds__(kShortThreads) softmax_short_kernel(const floa
     }
 }
 
+// Row lengths whose stride over the 32 shared-memory banks repeats at most every second lane (odd lengths and
+// 2 x odd: 10 classes among them): a warp owns 32 consecutive rows, which are one contiguous run of 32 x reduce floats.
+// It copies the run into its own staging area with coalesced 128-bit loads, every lane reads its row from there at the
+// row's natural pitch (no transposition, at most 2-way bank conflicts), writes the result back in place, and the warp
+// streams the run out again.  No block-wide barrier: the staging area is private to the warp.
+template <int RMAX>
+__global__ void __launch_bounds__(kShortThreads) softmax_short_warp_kernel(const float* __restrict__ x, float* __restrict__ y, size_t rows,
+                                                                          int reduce) {
+    __shared__ __align__(16) float stage[kShortThreads / 32][32 * RMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* st = stage[warp];
+    const size_t n_warps = (size_t)gridDim.x * (kShortThreads / 32);
+    const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    for (size_t w = (size_t)blockIdx.x * (kShortThreads / 32) + warp; w * 32 < rows; w += n_warps) {
+        const size_t r0 = w * 32;
+        const int nrows = rows - r0 < 32 ? (int)(rows - r0) : 32, nelem = nrows * reduce;
+        const float* src = x + r0 * reduce;      // r0 is a multiple of 32: the run starts 16-byte aligned when x does
+        float* dst = y + r0 * reduce;
+        const int nvec = al ? nelem / 4 : 0;
+        for (int e = lane; e < nvec; e += 32) reinterpret_cast<float4*>(st)[e] = __ldcs(reinterpret_cast<const float4*>(src) + e);
+        for (int e = nvec * 4 + lane; e < nelem; e += 32) st[e] = __ldcs(src + e);
+        __syncwarp();
+        if (lane < nrows) {
+            float* row = st + lane * reduce;
+            float v[RMAX];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j) {
+                v[j] = j < reduce ? row[j] : -INFINITY;
+                if (v[j] > mx) mx = v[j];
+            }
+            float sum = 0.0f;   // sequential, the reference's order
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j) {
+                if (j < reduce) {
+                    v[j] = expf(__fsub_rn(v[j], mx));
+                    sum = __fadd_rn(sum, v[j]);
+                }
+            }
+            const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j)
+                if (j < reduce) row[j] = __fmul_rn(v[j], inv);
+        }
+        __syncwarp();
+        for (int e = lane; e < nvec; e += 32) __stcs(reinterpret_cast<float4*>(dst) + e, reinterpret_cast<const float4*>(st)[e]);
+        for (int e = nvec * 4 + lane; e < nelem; e += 32) __stcs(dst + e, st[e]);
+        __syncwarp();
+    }
+}
+
 template <int RMAX>
 __global__ void __launch_bounds__(kShortThreads) softmax_bwd_short_kernel(const float* __restrict__ y, const float* __restrict__ go,
                                                                           float* __restrict__ gi, size_t rows, int reduce) {
@@ -601,6 +652,8 @@ void launch_cols(bool bwd, const float* a, const float* b, float* o, size_t oute
 template <int RMAX>
 void launch_short(bool bwd, const float* a, const float* b, float* o, size_t rows, int reduce, int sm, cudaStream_t s) {
     if (bwd) softmax_bwd_short_kernel<RMAX><<<grid_for((rows + 127) / 128, sm, kShortThreads), kShortThreads, 0, s>>>(a, b, o, rows, reduce);
+    else if (reduce % 4 != 0)   // the row pitch repeats over the banks at most every second lane
+        softmax_short_warp_kernel<RMAX><<<grid_for((rows + kShortThreads - 1) / kShortThreads, sm, kShortThreads), kShortThreads, 0, s>>>(a, o, rows, reduce);
     else softmax_short_kernel<RMAX><<<grid_for((rows + 255) / 256, sm, kShortThreads), kShortThreads, 0, s>>>(a, o, rows, reduce);
 }
 
