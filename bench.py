@@ -331,10 +331,12 @@ def run_gpu(args, d: Dist):
     # ---- timed region 2: end to end, each step's batch uploaded from pinned memory, loss read back
     h2d = 4 * local * (DIMS[0] + DIMS[-1])
     d.barrier(); ts.synchronize()
-    nxt = (ts.Tensor.from_pinned_async(pins_x[1], [local, DIMS[0]]), ts.Tensor.from_pinned_async(pins_t[1], [local, DIMS[-1]]))
     t0 = time.perf_counter()
     prev = None
     lib.ts_event_record(ev0, None)
+    # every step's upload lies inside the timed region, the first one included (nothing hides it); from then on the
+    # upload of step s + 1 is issued before step s is enqueued and runs on the copy stream beside it
+    nxt = (ts.Tensor.from_pinned_async(pins_x[1], [local, DIMS[0]]), ts.Tensor.from_pinned_async(pins_t[1], [local, DIMS[-1]]))
     for s in range(args.steps):
         cur = nxt
         slot = s % 2   # the slot the step before last used is free again: its upload has been consumed
