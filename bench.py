@@ -557,7 +557,8 @@ def run_c2(args):
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
                "softmax_inner", "transpose", "permute_021", "permute_gather", "reduce_rows", "reduce_cols", "reduce_all_max",
-               "reduce_middle", "broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward")
+               "reduce_middle", "broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward",
+               "matmul_batched_fp32", "matmul_batched_tf32")
 
 
 def run_micro(args):
@@ -680,6 +681,20 @@ def run_micro(args):
         ax = (C.c_ulonglong * len(axes))(*axes)
         launch = lambda: chk(lib.launch_reduce_dims_kernel(op, x, None, o1, dims, len(shape), ax, len(axes), sc, None), name)
         work, unit, peak = 4.0 * n, "GB/s", peaks["hbm_gbs"]
+    elif name in ("matmul_batched_fp32", "matmul_batched_tf32"):
+        # the batched pair of the reference's own matmul benchmark (64 x 128 x 128 times 64 x 128 x 128,
+        # libtorch-validation/examples/benches/matmul_performance.rs:22-46) through Tensor::matmul; the result tensor of
+        # each call is dropped at once, so the caching allocator hands the same block back every time
+        ts.set_matmul_precision(ts.FP32 if name.endswith("fp32") else ts.TF32)
+        bt, mm = 64, 128
+        ta = ts.Tensor.from_slice(rng.standard_normal((bt, mm, mm), dtype=np.float32), [bt, mm, mm])
+        tb = ts.Tensor.from_slice(rng.standard_normal((bt, mm, mm), dtype=np.float32), [bt, mm, mm])
+        n = bt * mm * mm
+
+        def launch():
+            with ts.NoGradTrack():
+                ta.matmul(tb).data_ptr()
+        work, unit, peak = 2.0 * bt * mm * mm * mm, "TFLOP/s", None
     elif name in ("broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward"):
         # [16384, 4096] with a row [4096], with a column [16384, 1]; a column times a row; both gradients of the column case
         sa, sb = {"broadcast_row": ((16384, 4096), (4096,)), "broadcast_col": ((16384, 4096), (16384, 1)),

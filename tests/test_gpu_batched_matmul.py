@@ -58,12 +58,27 @@ def test_reference_unit_test_values(gpu):
     assert_bit_equal(right.grad_by_value().data(), np.array([[[4.0, 4.0], [6.0, 6.0]], [[12.0, 12.0], [14.0, 14.0]]], np.float32))
 
 
+def test_tf32_mode_small_entries_take_the_fp32_launch(gpu, ora):
+    """TF32 mode, entries of at most 512^3 multiply-adds at a fixed stride: one FP32 launch over the batch instead
+    of a tensor-core launch per entry, so the result is the FP32 mode's, bit for bit."""
+    T = gpu.Tensor
+    rng = np.random.default_rng(6)
+    a, b = rng.standard_normal((8, 96, 160)).astype(np.float32), rng.standard_normal((8, 160, 72)).astype(np.float32)
+    gpu.set_matmul_precision(gpu.FP32)
+    want = T.from_slice(a, list(a.shape)).matmul(T.from_slice(b, list(b.shape))).data()
+    gpu.set_matmul_precision(gpu.TF32)
+    got = T.from_slice(a, list(a.shape)).matmul(T.from_slice(b, list(b.shape))).data()
+    assert_bit_equal(got, want, "TF32 mode, small entries")
+    assert_bit_equal(got[3], ora.matmul(a[3], b[3]), "an entry against the oracle")
+
+
 def test_tf32_mode_entries(gpu):
-    """TF32 mode: each entry is the tensor-core product of operands rounded to TF32; checked against float64 of the
-    rounded operands (the bound the 2-D TF32 tests use: FP32 accumulation only)."""
+    """TF32 mode, entries too large for the shared FP32 launch: each is the tensor-core product of operands rounded to
+    TF32; checked against float64 of the rounded operands (the bound the 2-D TF32 tests use: FP32 accumulation only)."""
     T = gpu.Tensor
     rng = np.random.default_rng(4)
-    a, b = rng.standard_normal((4, 128, 256)).astype(np.float32), rng.standard_normal((256, 128)).astype(np.float32)
+    a = (rng.standard_normal((4, 256, 8192)) / 8).astype(np.float32)      # 256 x 128 x 8192 = 2^28 multiply-adds per entry
+    b = (rng.standard_normal((8192, 128)) / 8).astype(np.float32)
 
     def rna(x):     # round to nearest, ties away, to 10 mantissa bits: cvt.rna.tf32.f32
         u = x.view(np.uint32).astype(np.uint64) + 0x1000
@@ -75,7 +90,7 @@ def test_tf32_mode_entries(gpu):
     want = np.matmul(rna(a).astype(np.float64), rna(b).astype(np.float64))
     np.testing.assert_allclose(y.data(), want, rtol=0, atol=2e-4)
     y.sum().backward()
-    ones = np.ones((4, 128, 128))
+    ones = np.ones((4, 256, 128))
     np.testing.assert_allclose(ta.grad_by_value().data(), np.matmul(ones, rna(b).astype(np.float64).T), rtol=0, atol=2e-4)
     np.testing.assert_allclose(tb.grad_by_value().data(), np.matmul(np.swapaxes(rna(a).astype(np.float64), -1, -2), ones).sum(0),
                                rtol=0, atol=1e-3)

@@ -163,6 +163,9 @@ struct GemmArgs {
     // 3xTF32: when both are set, a and b hold the TF32-exact high parts and these the low parts
     const float* a_lo = nullptr;
     const float* b_lo = nullptr;
+    // FP32 kernel only: `batch` independent products in one launch (grid z); entry z reads a + z * batch_stride_a and
+    // b + z * batch_stride_b (a stride of 0 repeats the operand) and writes c + z * m * n.  No bias / mask with batch > 1.
+    size_t batch = 1, batch_stride_a = 0, batch_stride_b = 0;
 };
 // hi = x rounded to nearest TF32, lo = (x - hi) rounded to nearest TF32: x = hi + lo to about 2^-22 relative.
 bool split_tf32(const float* x, float* hi, float* lo, size_t n, cudaStream_t s);

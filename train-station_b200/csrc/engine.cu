@@ -512,13 +512,32 @@ static bool batched_gemm(DeviceCtx* c, const TensorP& ta, const std::vector<size
     const float* pb = rptr(tb, true);
     if (!pa || !pb) return false;
     const int prec = matmul_precision();
+    const size_t a_mat = m * kk, b_mat = kk * n;
+    // The FP32 kernel takes the whole batch as one launch (grid z) when every entry's operands sit at a fixed stride
+    // from the previous entry's (equal batch shapes, or an operand without batch axes: stride 0).
+    // In TF32 mode the tensor-core kernel runs one launch (and three tensor maps) per entry, about 8 us of fixed cost
+    // each: entries of up to 512^3 multiply-adds are faster, and more accurate, as one FP32 launch over the batch.
+    k::GemmArgs probe{pa, pb, out, m, n, kk, trans_a, trans_b, nullptr, false, nullptr};
+    const bool small_entries = (double)m * (double)n * (double)kk <= (double)(1u << 27);
+    if (g.count > 1 && g.count <= 65535 && (prec == 0 || (prec == 1 && (small_entries || !k::gemm_tc_supported(probe))))) {
+        const size_t sa = batch_offset(1, g.batch, a_batch, a_mat), sb = batch_offset(1, g.batch, b_batch, b_mat);
+        bool affine = true;
+        for (size_t i = 2; i < g.count && affine; ++i)
+            affine = batch_offset(i, g.batch, a_batch, a_mat) == i * sa && batch_offset(i, g.batch, b_batch, b_mat) == i * sb;
+        if (affine) {
+            k::GemmArgs all{pa, pb, out, m, n, kk, trans_a, trans_b, nullptr, false, nullptr};
+            all.batch = g.count;
+            all.batch_stride_a = sa;
+            all.batch_stride_b = sb;
+            return k::sgemm(all, c->compute);
+        }
+    }
     const float *ra = pa, *rb = pb;
     if (prec == 1) {   // TF32: operands rounded to nearest first (cached copies beside the data)
         ra = tf32_operand(c, ta);
         rb = tf32_operand(c, tb);
         if (!ra || !rb) return false;
     }
-    const size_t a_mat = m * kk, b_mat = kk * n;
     for (size_t i = 0; i < g.count; ++i) {
         const size_t ao = batch_offset(i, g.batch, a_batch, a_mat), bo = batch_offset(i, g.batch, b_batch, b_mat);
         k::GemmArgs ga{ra + ao, rb + bo, out + i * m * n, m, n, kk, trans_a, trans_b, nullptr, false, nullptr};

@@ -68,6 +68,9 @@ __device__ __forceinline__ void tile_store(float (*sm)[BM], const float (&r)[8])
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
+    g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
+    g.b += (size_t)blockIdx.z * g.batch_stride_b;
+    g.c += (size_t)blockIdx.z * g.m * g.n;
     __shared__ __align__(16) float As[2][BK][BM];
     __shared__ __align__(16) float Bs[2][BK][BN];
     const int t = threadIdx.x;
@@ -192,6 +195,9 @@ __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gmem_src
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
+    g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
+    g.b += (size_t)blockIdx.z * g.batch_stride_b;
+    g.c += (size_t)blockIdx.z * g.m * g.n;
     __shared__ float As[SM_STAGES][SM_T][SM_T + 1];   // [stage][k][m]
     __shared__ float Bs[SM_STAGES][SM_T][SM_T + 1];   // [stage][k][n]
     const int t = threadIdx.x, ty = t / 16, tx = t % 16;
@@ -285,13 +291,15 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
     }
     size_t gx = (g.n + BN - 1) / BN, gy = (g.m + BM - 1) / BM;
     if (gy > 65535) { set_error("gemm: m = %zu too large for the FP32 kernel's grid", g.m); return false; }
-    dim3 grid((unsigned)gx, (unsigned)gy);
-    ProfScope prof(kProfGemmFp32, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
+    if (g.batch == 0) return true;
+    if (g.batch > 65535 || (g.batch > 1 && (g.bias || g.mask))) { set_error("gemm: unsupported batch of %zu products", g.batch); return false; }
+    dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)g.batch);
+    ProfScope prof(kProfGemmFp32, s, 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch);
     DeviceCtx* c = ctx();
     const size_t sgy = (g.m + SM_T - 1) / SM_T;
-    if (c && gx * gy < (size_t)c->sm_count / 2 && sgy <= 65535) {
+    if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && sgy <= 65535) {
         // too few 128 x 128 tiles to occupy the GPU: 32 x 32 tiles, sixteen times as many CTAs
-        dim3 sgrid((unsigned)((g.n + SM_T - 1) / SM_T), (unsigned)sgy);
+        dim3 sgrid((unsigned)((g.n + SM_T - 1) / SM_T), (unsigned)sgy, (unsigned)g.batch);
         if (g.trans_a) { if (g.trans_b) launch_small<true, true>(g, sgrid, s); else launch_small<true, false>(g, sgrid, s); }
         else { if (g.trans_b) launch_small<false, true>(g, sgrid, s); else launch_small<false, false>(g, sgrid, s); }
         return cuda_ok(cudaGetLastError(), "sgemm (small tiles) launch");
