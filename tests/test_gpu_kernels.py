@@ -156,7 +156,9 @@ def test_colsum_and_fused_relu_backward(gpu, ora, rows, cols):
 SGEMM_SHAPES = [(1, 1, 1), (2, 2, 2), (32, 128, 784), (17, 23, 19), (64, 48, 40), (130, 10, 257), (5, 300, 129),
                 (256, 256, 256), (128, 136, 8), (3, 7, 1000), (200, 100, 0),
                 # at least 74 tiles of 128 x 128: the large-tile kernel (the shapes above run on 32 x 32 tiles)
-                (1200, 1156, 70), (1281, 1034, 33)]
+                (1200, 1156, 70), (1281, 1034, 33),
+                # fewer than 74 tiles of 128 x 128 but at least 74 of 64 x 64: the middle kernel (tail columns in two)
+                (520, 1100, 70), (1024, 1024, 100), (600, 603, 129)]
 
 
 @pytest.mark.parametrize("m,n,k", SGEMM_SHAPES)
@@ -169,7 +171,7 @@ def test_fp32_gemm_matches_reference_order_bit_exact(gpu, ora, m, n, k):
     assert_bit_equal(dc.get().reshape(m, n), ora.matmul(a, b), f"sgemm {m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("m,n,k", [(33, 65, 70), (128, 10, 300), (64, 256, 129), (1300, 1102, 40)])
+@pytest.mark.parametrize("m,n,k", [(33, 65, 70), (128, 10, 300), (64, 256, 129), (1300, 1102, 40), (520, 1100, 45), (577, 650, 33)])
 def test_fp32_gemm_transposed_operands_and_epilogue(gpu, ora, m, n, k):
     lib, chk = gpu._ffi.lib(), gpu._ffi.check
     rng = np.random.default_rng(m + n + k)

@@ -281,6 +281,105 @@ void launch_small(const GemmArgs& g, dim3 grid, cudaStream_t s) {
     else sgemm_small_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
 }
 
+// Between the two: 64 x 64 tiles, 4 x 4 outputs per thread, 16 k per stage through the same ring of asynchronous
+// copies.  For results of a few hundred such tiles (1024 x 1024, or a batch of 128 x 128 products) the 128 x 128 tiles
+// would leave most SMs idle and the 32 x 32 tiles spend one shared-memory load per multiply-add; here it is one
+// 128-bit load per eight.  Per output element the chain over p is again unchanged.
+constexpr int MD_T = 64, MD_K = 16, MD_PITCH = MD_T + 4;     // rows stay 16-byte aligned
+
+template <bool TA, bool TB, bool HAS_TAIL>
+__global__ void __launch_bounds__(kThreads) sgemm_mid_kernel(GemmArgs g) {
+    g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
+    g.b += (size_t)blockIdx.z * g.batch_stride_b;
+    g.c += (size_t)blockIdx.z * g.m * g.n;
+    __shared__ __align__(16) float As[SM_STAGES][MD_K][MD_PITCH];   // [stage][k][m]
+    __shared__ __align__(16) float Bs[SM_STAGES][MD_K][MD_PITCH];   // [stage][k][n]
+    const int t = threadIdx.x, ty = t / 16, tx = t % 16;
+    const size_t m0 = (size_t)blockIdx.y * MD_T, n0 = (size_t)blockIdx.x * MD_T;
+    const size_t M = g.m, N = g.n, K = g.k;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    // a thread's four columns are one aligned group, and the boundary N/8*8 is a multiple of 8: tail or not as a whole
+    const bool tail = HAS_TAIL && n0 + tx * 4 >= N / 8 * 8;
+
+    auto issue = [&](int slot, size_t k0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int e = t + kThreads * q;               // 0 .. 1023: one element of the 64 x 16 operand tile
+            {   // A: stored [K][M] (TA, contiguous along m) or [M][K] (contiguous along k)
+                const int kk = TA ? e / MD_T : e % MD_K, mm = TA ? e % MD_T : e / MD_K;
+                const size_t p = k0 + kk, i = m0 + mm;
+                const bool in = p < K && i < M;
+                cp_async4(&As[slot][kk][mm], in ? (TA ? g.a + p * M + i : g.a + i * K + p) : g.a, in);
+            }
+            {   // B: stored [N][K] (TB, contiguous along k) or [K][N] (contiguous along n)
+                const int kk = TB ? e % MD_K : e / MD_T, nn = TB ? e / MD_K : e % MD_T;
+                const size_t p = k0 + kk, j = n0 + nn;
+                const bool in = p < K && j < N;
+                cp_async4(&Bs[slot][kk][nn], in ? (TB ? g.b + j * K + p : g.b + p * N + j) : g.b, in);
+            }
+        }
+    };
+
+    const size_t nk = (K + MD_K - 1) / MD_K;
+#pragma unroll
+    for (int st = 0; st < SM_STAGES - 1; ++st) {
+        if ((size_t)st < nk) issue(st, (size_t)st * MD_K);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (size_t kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(SM_STAGES - 2) : "memory");
+        __syncthreads();
+        const size_t nxt = kt + SM_STAGES - 1;
+        if (nxt < nk) issue((int)(nxt % SM_STAGES), nxt * MD_K);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const int slot = (int)(kt % SM_STAGES);
+        const size_t k0 = kt * MD_K;
+        const int pmax = (K - k0) < (size_t)MD_K ? (int)(K - k0) : MD_K;    // no padded terms enter the chain
+#pragma unroll 4
+        for (int p = 0; p < pmax; ++p) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[slot][p][ty * 4]);
+            const float4 b4 = *reinterpret_cast<const float4*>(&Bs[slot][p][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+            if (HAS_TAIL && tail) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const size_t row = m0 + ty * 4 + i;
+        if (row >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const size_t col = n0 + tx * 4 + j;
+            if (col >= N) continue;
+            float v = acc[i][j];
+            if (g.bias) v = __fadd_rn(v, __ldg(g.bias + col));
+            if (g.relu) v = v > 0.0f ? v : 0.0f;
+            if (g.mask) v = g.mask[row * N + col] > 0.0f ? v : 0.0f;
+            g.c[row * N + col] = v;
+        }
+    }
+}
+
+template <bool TA, bool TB>
+void launch_mid(const GemmArgs& g, dim3 grid, cudaStream_t s) {
+    if (g.n % 8 != 0) sgemm_mid_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
+    else sgemm_mid_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+}
+
 }  // namespace
 
 bool sgemm(const GemmArgs& g, cudaStream_t s) {
@@ -297,8 +396,16 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
     ProfScope prof(kProfGemmFp32, s, 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch);
     DeviceCtx* c = ctx();
     const size_t sgy = (g.m + SM_T - 1) / SM_T;
+    const size_t mgx = (g.n + MD_T - 1) / MD_T, mgy = (g.m + MD_T - 1) / MD_T;
+    if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && mgx * mgy * g.batch >= (size_t)c->sm_count / 2 && mgy <= 65535) {
+        // too few 128 x 128 tiles to occupy the GPU, enough 64 x 64 ones
+        dim3 mgrid((unsigned)mgx, (unsigned)mgy, (unsigned)g.batch);
+        if (g.trans_a) { if (g.trans_b) launch_mid<true, true>(g, mgrid, s); else launch_mid<true, false>(g, mgrid, s); }
+        else { if (g.trans_b) launch_mid<false, true>(g, mgrid, s); else launch_mid<false, false>(g, mgrid, s); }
+        return cuda_ok(cudaGetLastError(), "sgemm (64 x 64 tiles) launch");
+    }
     if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && sgy <= 65535) {
-        // too few 128 x 128 tiles to occupy the GPU: 32 x 32 tiles, sixteen times as many CTAs
+        // too few even of those: 32 x 32 tiles, sixteen times as many CTAs as 128 x 128 ones
         dim3 sgrid((unsigned)((g.n + SM_T - 1) / SM_T), (unsigned)sgy, (unsigned)g.batch);
         if (g.trans_a) { if (g.trans_b) launch_small<true, true>(g, sgrid, s); else launch_small<true, false>(g, sgrid, s); }
         else { if (g.trans_b) launch_small<false, true>(g, sgrid, s); else launch_small<false, false>(g, sgrid, s); }
