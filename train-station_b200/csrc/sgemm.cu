@@ -281,6 +281,96 @@ void launch_small(const GemmArgs& g, dim3 grid, cudaStream_t s) {
     else sgemm_small_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
 }
 
+// The smallest tiling: 16 x 16 tiles, 64 threads, 2 x 2 outputs per thread, 64 k per stage, for results of fewer than
+// 74 tiles of 32 x 32 with K <= 1024 (see the dispatch in sgemm()): a quarter of the outputs per CTA is a quarter of
+// the work per step of the chain, and four times the CTAs spread over SMs that would have been idle.  Per output
+// element the chain over p is unchanged.
+constexpr int TN_T = 16, TN_K = 64, TN_THREADS = 64, TN_PITCH = TN_T + 2;    // rows stay 8-byte aligned
+
+template <bool TA, bool TB, bool HAS_TAIL>
+__global__ void __launch_bounds__(TN_THREADS) sgemm_tiny_kernel(GemmArgs g) {
+    g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
+    g.b += (size_t)blockIdx.z * g.batch_stride_b;
+    g.c += (size_t)blockIdx.z * g.m * g.n;
+    __shared__ __align__(16) float As[SM_STAGES][TN_K][TN_PITCH];   // [stage][k][m]
+    __shared__ __align__(16) float Bs[SM_STAGES][TN_K][TN_PITCH];   // [stage][k][n]
+    const int t = threadIdx.x, ty = t / 8, tx = t % 8;              // rows ty*2 .. +1, columns tx*2 .. +1
+    const size_t m0 = (size_t)blockIdx.y * TN_T, n0 = (size_t)blockIdx.x * TN_T;
+    const size_t M = g.m, N = g.n, K = g.k;
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    // a thread's two columns are one aligned pair, and the boundary N/8*8 is even: tail or not as a whole
+    const bool tail = HAS_TAIL && n0 + tx * 2 >= N / 8 * 8;
+
+    auto issue = [&](int slot, size_t k0) {
+#pragma unroll
+        for (int q = 0; q < TN_T * TN_K / TN_THREADS; ++q) {
+            const int e = t + TN_THREADS * q;             // 0 .. 511: one element of the 16 x 32 operand tile
+            {   // A: stored [K][M] (TA, contiguous along m) or [M][K] (contiguous along k)
+                const int kk = TA ? e / TN_T : e % TN_K, mm = TA ? e % TN_T : e / TN_K;
+                const size_t p = k0 + kk, i = m0 + mm;
+                const bool in = p < K && i < M;
+                cp_async4(&As[slot][kk][mm], in ? (TA ? g.a + p * M + i : g.a + i * K + p) : g.a, in);
+            }
+            {   // B: stored [N][K] (TB, contiguous along k) or [K][N] (contiguous along n)
+                const int kk = TB ? e % TN_K : e / TN_T, nn = TB ? e / TN_K : e % TN_T;
+                const size_t p = k0 + kk, j = n0 + nn;
+                const bool in = p < K && j < N;
+                cp_async4(&Bs[slot][kk][nn], in ? (TB ? g.b + j * K + p : g.b + p * N + j) : g.b, in);
+            }
+        }
+    };
+
+    const size_t nk = (K + TN_K - 1) / TN_K;
+#pragma unroll
+    for (int st = 0; st < SM_STAGES - 1; ++st) {
+        if ((size_t)st < nk) issue(st, (size_t)st * TN_K);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (size_t kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(SM_STAGES - 2) : "memory");
+        __syncthreads();
+        const size_t nxt = kt + SM_STAGES - 1;
+        if (nxt < nk) issue((int)(nxt % SM_STAGES), nxt * TN_K);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const int slot = (int)(kt % SM_STAGES);
+        const size_t k0 = kt * TN_K;
+        const int pmax = (K - k0) < (size_t)TN_K ? (int)(K - k0) : TN_K;    // no padded terms enter the chain
+#pragma unroll 8
+        for (int p = 0; p < pmax; ++p) {
+            const float2 a2 = *reinterpret_cast<const float2*>(&As[slot][p][ty * 2]);
+            const float2 b2 = *reinterpret_cast<const float2*>(&Bs[slot][p][tx * 2]);
+            if (HAS_TAIL && tail) {
+                acc[0][0] = __fadd_rn(acc[0][0], __fmul_rn(a2.x, b2.x)); acc[0][1] = __fadd_rn(acc[0][1], __fmul_rn(a2.x, b2.y));
+                acc[1][0] = __fadd_rn(acc[1][0], __fmul_rn(a2.y, b2.x)); acc[1][1] = __fadd_rn(acc[1][1], __fmul_rn(a2.y, b2.y));
+            } else {
+                acc[0][0] = fmaf(a2.x, b2.x, acc[0][0]); acc[0][1] = fmaf(a2.x, b2.y, acc[0][1]);
+                acc[1][0] = fmaf(a2.y, b2.x, acc[1][0]); acc[1][1] = fmaf(a2.y, b2.y, acc[1][1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const size_t row = m0 + ty * 2 + i;
+        if (row >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const size_t col = n0 + tx * 2 + j;
+            if (col >= N) continue;
+            float v = acc[i][j];
+            if (g.bias) v = __fadd_rn(v, __ldg(g.bias + col));
+            if (g.relu) v = v > 0.0f ? v : 0.0f;
+            if (g.mask) v = g.mask[row * N + col] > 0.0f ? v : 0.0f;
+            g.c[row * N + col] = v;
+        }
+    }
+}
+
+template <bool TA, bool TB>
+void launch_tiny(const GemmArgs& g, dim3 grid, cudaStream_t s) {
+    if (g.n % 8 != 0) sgemm_tiny_kernel<TA, TB, true><<<grid, TN_THREADS, 0, s>>>(g);
+    else sgemm_tiny_kernel<TA, TB, false><<<grid, TN_THREADS, 0, s>>>(g);
+}
+
 // Between the two: 64 x 64 tiles, 4 x 4 outputs per thread, 16 k per stage through the same ring of asynchronous
 // copies.  For results of a few hundred such tiles (1024 x 1024, or a batch of 128 x 128 products) the 128 x 128 tiles
 // would leave most SMs idle and the 32 x 32 tiles spend one shared-memory load per multiply-add; here it is one
@@ -403,6 +493,16 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
         if (g.trans_a) { if (g.trans_b) launch_mid<true, true>(g, mgrid, s); else launch_mid<true, false>(g, mgrid, s); }
         else { if (g.trans_b) launch_mid<false, true>(g, mgrid, s); else launch_mid<false, false>(g, mgrid, s); }
         return cuda_ok(cudaGetLastError(), "sgemm (64 x 64 tiles) launch");
+    }
+    const size_t sgx = (g.n + SM_T - 1) / SM_T, tgy = (g.m + TN_T - 1) / TN_T;
+    if (c && sgx * sgy * g.batch < (size_t)c->sm_count / 2 && tgy <= 65535 && g.k <= 1024) {
+        // too few even of 32 x 32 tiles and a short chain: 16 x 16 ones.  Measured, not derived: the 32 x 784 . 784 x 128
+        // product runs 15 % faster here, but a [1024 x 10] result over K = 4096 took 236 us against 143 us on 32 x 32
+        // tiles, so long chains stay there.
+        dim3 tgrid((unsigned)((g.n + TN_T - 1) / TN_T), (unsigned)tgy, (unsigned)g.batch);
+        if (g.trans_a) { if (g.trans_b) launch_tiny<true, true>(g, tgrid, s); else launch_tiny<true, false>(g, tgrid, s); }
+        else { if (g.trans_b) launch_tiny<false, true>(g, tgrid, s); else launch_tiny<false, false>(g, tgrid, s); }
+        return cuda_ok(cudaGetLastError(), "sgemm (16 x 16 tiles) launch");
     }
     if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && sgy <= 65535) {
         // too few even of those: 32 x 32 tiles, sixteen times as many CTAs as 128 x 128 ones
