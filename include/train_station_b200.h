@@ -93,6 +93,9 @@ typedef struct ts_allocator_stats {
 bool ts_allocator_get_stats(ts_allocator_stats* out);
 void ts_allocator_release_cached(void);              /* return cached blocks to the driver */
 void ts_allocator_set_limit(unsigned long long bytes); /* 0 = no limit; for out-of-memory tests */
+/* Free and total device memory as the driver reports them (cudaMemGetInfo), in bytes; either pointer may be NULL.
+ * A read-only query: lets a caller check from outside the allocator's own counters that a call took nothing. */
+bool ts_device_memory_info(unsigned long long* free_bytes, unsigned long long* total_bytes);
 
 /* CUDA events on a stream of this library, for callers that time kernels without any other CUDA binding.
  * ts_event_elapsed_ms waits for `end` and returns the milliseconds between the two records (negative on error). */
@@ -238,7 +241,9 @@ bool launch_colsum_kernel(const float* g, float* out, unsigned long long rows, u
  * device memory away, or that must not enter the driver's allocator on its hot loop (the allocator can
  * synchronise the whole device) has no scratch buffer to hand to launch_colsum_kernel; this variant
  * keeps the partial sums in a 512 KiB array built into the library (held on every GPU that loads the
- * library, until the process exits) and itself calls no allocation routine of any kind.
+ * library, until the process exits) and itself calls no allocation routine of any kind (with
+ * ts_profile_enable(1) its launches are counted but not bracketed by events, since creating an event
+ * allocates).
  *   - Limit: the row splits times `cols` must fit 131,072 elements (65536 x 8192 needs 73,728; the
  *     kernel plans at most four CTAs per SM, so a 148-SM B200 never needs more than 75,776 and the
  *     limit only bites on devices with more SMs); a problem that does not fit is refused with a

@@ -583,6 +583,56 @@ def mlp_step_f64(weights, biases, x, target=None, loss_kind=LOSS_MSE, relu_last=
     return {"loss": loss, "y": y, "z": z, "gw": gw, "gb": gb, "gx": g}
 
 
+def reduced_precision_step_check(weights, biases, x, target, device_masks, got_gw, got_gb, loss_kind=LOSS_MSE,
+                                 relu_last=False, band_rel=2e-3):
+    """The checkable form of "gradients within rel 2e-3" for a GEMM mode that does not reproduce FP32 bits.
+
+    A pre-activation z within the GEMM's rounding error of zero can take the other ReLU branch than in exact
+    arithmetic, and a flipped mask element changes that element's gradient outright whatever the GEMM's accuracy.
+    So: (1) the masks the device forward produced (`device_masks`, one boolean array per activated layer) must agree
+    with the float64 ones wherever |z| lies outside the band `band_rel * sum_k |a||w|`; (2) the gradients are
+    compared, as Frobenius-norm relative errors, with a float64 evaluation that uses the device's own masks, so that
+    what is left is GEMM arithmetic.  Returns {"outside_mismatch": [...], "flips": [...], "in_band": [...],
+    "elements": [...], "rel_gw": [...], "rel_gb": [...]}, one entry per layer (mask lists: per activated layer)."""
+    w = [np.asarray(a, np.float64) for a in weights]
+    b = [np.asarray(a, np.float64) for a in biases]
+    L = len(w)
+    exact = mlp_step_f64(weights, biases, x, target, loss_kind=loss_kind, relu_last=relu_last)
+    out = {"outside_mismatch": [], "flips": [], "in_band": [], "elements": [], "rel_gw": [None] * L, "rel_gb": [None] * L}
+    act = np.asarray(x, np.float64)
+    n_act = L if relu_last else L - 1
+    for l in range(n_act):
+        band = band_rel * (np.abs(act) @ np.abs(w[l]))
+        z = exact["z"][l]
+        outside = np.abs(z) > band
+        dm = np.asarray(device_masks[l], bool)
+        out["outside_mismatch"].append(int((dm[outside] != (z > 0)[outside]).sum()))
+        out["flips"].append(int((dm != (z > 0)).sum()))
+        out["in_band"].append(int((~outside).sum()))
+        out["elements"].append(int(z.size))
+        act = np.maximum(z, 0.0)
+    # float64 forward and backward with the device's masks
+    hs = [np.asarray(x, np.float64)]
+    for l in range(L):
+        zl = hs[l] @ w[l] + b[l]
+        hs.append(zl * np.asarray(device_masks[l], bool) if l < n_act else zl)
+    y = hs[L]
+    if loss_kind == LOSS_SUM:
+        g = np.ones_like(y)
+    elif loss_kind == LOSS_MEAN:
+        g = np.full_like(y, 1.0 / y.size)
+    else:
+        g = 2.0 * (y - np.asarray(target, np.float64)) / y.size
+    rel = lambda a, r: float(np.linalg.norm(np.asarray(a, np.float64) - r) / max(np.linalg.norm(r), 1e-300))
+    for l in reversed(range(L)):
+        if l < n_act:
+            g = g * np.asarray(device_masks[l], bool)
+        out["rel_gw"][l] = rel(got_gw[l], hs[l].T @ g)
+        out["rel_gb"][l] = rel(got_gb[l], g.sum(axis=0))
+        g = g @ w[l].T
+    return out
+
+
 def adam_update_f64(p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
     """Textbook Adam in float64 using the f32-rounded hyper-parameters, out of place."""
     b1, b2 = float(np.float32(beta1)), float(np.float32(beta2))

@@ -272,8 +272,11 @@ ORA_API void ora_adam_update(float *p, const float *g_in, float *m, float *v, si
  * gx when x_requires_grad) exactly as the GradFns of gradtrack/grad_fn/ would:
  * ReduceSum/ReduceMean fill, PowScalar, Sub, Relu, Add with sum_dims for the bias,
  * MatMul with materialised transposes (grad_fn/ops/matmul.rs:68-80).
- * as_written != 0 additionally performs the deep copies the reference makes of saved
- * and multiplied operands (matmul/mod.rs:296-297,586-595) so that timing reflects them.
+ * as_written != 0 additionally performs the work the reference does around the arithmetic, so
+ * that timing reflects it: the deep copies of saved and multiplied operands
+ * (matmul/mod.rs:296-297,586-595), the element-by-element materialisation of the broadcast
+ * bias (broadcasting.rs:452-477) and the coordinate-walk contiguous() of the transposed
+ * operands in backward (transform/contiguous.rs:283-345).  Values are identical either way.
  * Returns the loss.  dims has layers+1 entries.
  */
 typedef struct {
@@ -303,6 +306,56 @@ static void ora_touch_copy(const float *src, size_t n) { /* a deep copy that is 
     free(t);
 }
 
+/* A small heap vector per element, as Rust's `vec![0; rank]` inside the reference's copy loops: allocated, used and
+ * dropped for every single element.  The barrier keeps the compiler from folding the allocation away. */
+static size_t *ora_index_vec(int rank) {
+    size_t *v = (size_t *)calloc((size_t)rank, sizeof(size_t));
+    if (!v) abort();
+    __asm__ volatile("" : : "r"(v) : "memory");
+    return v;
+}
+/* broadcasting.rs:452-477 (broadcast_copy_data, general path): for each element of the stretched result a fresh
+ * index vector, one div/mod per axis from the innermost outwards, then the offset through the broadcast strides
+ * (0 on stretched axes).  This is how the reference materialises the [rows, cols] copy of a bias row. */
+static void ora_broadcast_copy_walk(const float *src, float *dst, const size_t *bdims, const size_t *bstrides,
+                                    int rank, size_t total) {
+    for (size_t i = 0; i < total; ++i) {
+        size_t *idx = ora_index_vec(rank);
+        size_t t = i;
+        for (int d = rank - 1; d >= 0; --d) { idx[d] = t % bdims[d]; t /= bdims[d]; }
+        size_t off = 0;
+        for (int d = 0; d < rank; ++d)
+            if (bstrides[d] > 0) off += idx[d] * bstrides[d];
+        dst[i] = src[off];
+        free(idx);
+    }
+}
+/* transform/contiguous.rs:283-322 (copy_to_contiguous_large) with linear_to_coords (:337-345): blocks of 1024
+ * destination elements, four per trip, each converting its linear index to coordinates in a fresh vector and
+ * taking the source offset through the view's strides.  This is the materialised transpose matmul makes of
+ * `w.t()` and `a.t()` in backward (matmul/mod.rs:586-595, grad_fn/ops/matmul.rs:68-80). */
+static void ora_contiguous_walk(const float *src, float *dst, const size_t *dims, const size_t *strides, int rank,
+                                size_t total) {
+    const size_t block = 1024;
+    for (size_t start = 0; start < total; start += block) {
+        size_t end = start + block < total ? start + block : total;
+        for (size_t i = start; i < end; ++i) {      /* the 4-way unrolling changes no access, only loop overhead */
+            size_t *c = ora_index_vec(rank);
+            size_t t = i;
+            for (int d = rank - 1; d >= 0; --d) { c[d] = t % dims[d]; t /= dims[d]; }
+            size_t off = 0;
+            for (int d = 0; d < rank; ++d) off += c[d] * strides[d];
+            dst[i] = src[off];
+            free(c);
+        }
+    }
+}
+/* dst[cols][rows] = src[rows][cols]^T the way the reference does it: a stride-swapped view made contiguous */
+static void ora_transpose_as_written(const float *src, float *dst, size_t rows, size_t cols) {
+    size_t dims[2] = {cols, rows}, strides[2] = {1, cols};
+    ora_contiguous_walk(src, dst, dims, strides, 2, rows * cols);
+}
+
 ORA_API float ora_mlp_step(ora_mlp_args *A) {
     int L = A->layers;
     size_t B = A->batch;
@@ -317,8 +370,13 @@ ORA_API float ora_mlp_step(ora_mlp_args *A) {
                              ora_touch_copy(h[l], B * K); ora_touch_copy(A->w[l], K * N); }
         ora_matmul(h[l], A->w[l], mm, B, N, K);
         z[l] = ora_alloc(B * N);
-        if (A->as_written) { float *bb = ora_alloc(B * N);
-            for (size_t i = 0; i < B; ++i) memcpy(bb + i * N, A->b[l], N * sizeof(float));
+        if (A->as_written) {
+            /* add_tensor of [B,N] and [N] (add.rs:107-146 -> broadcasting.rs:299-333): the full-size operand is
+             * deep-copied, the bias is materialised to [B,N] element by element, then the same-shape add runs */
+            float *bb = ora_alloc(B * N);
+            size_t bdims[2] = {B, N}, bstr[2] = {0, 1};
+            ora_touch_copy(mm, B * N);
+            ora_broadcast_copy_walk(A->b[l], bb, bdims, bstr, 2, B * N);
             ora_add(mm, bb, z[l], B * N); free(bb);
         } else ora_add_row(mm, A->b[l], z[l], B, N);
         free(mm);
@@ -356,14 +414,14 @@ ORA_API float ora_mlp_step(ora_mlp_args *A) {
         ora_colsum(gz, A->gb[l], B, N);
         /* dW = h^T . gz */
         float *ht = ora_alloc(K * B);
-        ora_transpose(h[l], ht, B, K);
+        if (A->as_written) ora_transpose_as_written(h[l], ht, B, K); else ora_transpose(h[l], ht, B, K);
         if (A->as_written) { ora_touch_copy(ht, K * B); ora_touch_copy(gz, B * N); }
         ora_matmul(ht, gz, A->gw[l], K, N, B);
         free(ht);
         float *gprev = NULL;
         if (l > 0 || A->gx) {
             float *wt = ora_alloc(N * K);
-            ora_transpose(A->w[l], wt, K, N);
+            if (A->as_written) ora_transpose_as_written(A->w[l], wt, K, N); else ora_transpose(A->w[l], wt, K, N);
             gprev = (l > 0) ? ora_alloc(B * K) : A->gx;
             if (A->as_written) { ora_touch_copy(gz, B * N); ora_touch_copy(wt, N * K); }
             ora_matmul(gz, wt, gprev, B, K, N);

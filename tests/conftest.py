@@ -16,11 +16,12 @@ import __graft_entry__ as entry  # noqa: E402
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
-    # Build what is missing (nvcc and gcc work without a GPU). An existing library is kept as is.
-    bm = entry._load_build_module()
-    if not os.path.exists(bm.LIB):
-        bm.build()
+    # Build what is missing or older than its sources (nvcc and gcc work without a GPU): build() returns at once
+    # when the library is newer than every file it is made from, so an edited kernel is never tested through a
+    # stale binary.
+    entry._load_build_module().build()
     entry.load_oracle().build()
+    entry.build_cpp_tests()
 
 
 @pytest.fixture(scope="session")

@@ -137,7 +137,7 @@ def test_tf32_long_k_accumulation(gpu):
     _check(_run(gpu, np.ascontiguousarray(a.T), b, m, n, k, 1, 0), a, b)   # the dW layout with a long reduction
 
 
-def test_training_step_tf32_within_tolerance(gpu, ora):
+def test_training_step_tf32_within_tolerance(gpu, ora, capsys):
     """A 3-layer MLP step in TF32 mode vs the oracle: loss, gradients and post-Adam parameters within rel 2e-3."""
     from test_gpu_engine import _mlp_device
     rng = np.random.default_rng(4)
@@ -155,7 +155,8 @@ def test_training_step_tf32_within_tolerance(gpu, ora):
 
     # A pre-activation within TF32 error of zero gets the other ReLU mask than on the FP32 path, and a
     # flipped mask element changes that element's gradient outright, whatever the GEMM's accuracy.  So
-    # (1) masks must agree with the exact ones wherever |z| is outside the TF32 error band, and
+    # (1) masks must agree with the exact ones wherever |z| is outside the TF32 error band, the number of
+    #     flips inside it is bounded and reported, and
     # (2) gradients are compared with an f64 evaluation that uses the masks the device forward produced:
     #     what is left is GEMM arithmetic, held to rel 2e-3 of each gradient tensor (Frobenius norm).
     T = gpu.Tensor
@@ -170,28 +171,14 @@ def test_training_step_tf32_within_tolerance(gpu, ora):
     loss = h.sub_tensor(T.from_slice(t, t.shape)).pow_scalar(2.0).mean()
     loss.backward(None)
     masks = [hd.data() > 0 for hd in hidden]
-    f = ora.mlp_step_f64(ws, bs, x, t, loss_kind=ora.LOSS_MSE)
-    act, flips = x.astype(np.float64), []
-    for i in range(2):
-        band = 2e-3 * (np.abs(act) @ np.abs(ws[i]).astype(np.float64))
-        outside = np.abs(f["z"][i]) > band
-        assert np.array_equal(masks[i][outside], (f["z"][i] > 0)[outside]), f"layer {i}: a mask differs outside the TF32 band"
-        flips.append(int((masks[i] != (f["z"][i] > 0)).sum()))
-        act = np.maximum(f["z"][i], 0.0)
-    # f64 forward and backward with the device's masks
-    w64 = [w.astype(np.float64) for w in ws]
-    hs = [x.astype(np.float64)]
-    for i in range(3):
-        z = hs[i] @ w64[i] + bs[i]
-        hs.append(z * masks[i] if i < 2 else z)
-    g = 2.0 * (hs[3] - t) / hs[3].size
-    rel = lambda a, b: float(np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b))
-    for i in reversed(range(3)):
-        if i < 2:
-            g = g * masks[i]
-        assert rel(W[i].grad_by_value().data(), hs[i].T @ g) <= 2e-3, (i, flips)
-        assert rel(B[i].grad_by_value().data(), g.sum(axis=0)) <= 2e-3, (i, flips)
-        g = g @ w64[i].T
+    chk = ora.reduced_precision_step_check(ws, bs, x, t, masks, [w.grad_by_value().data() for w in W],
+                                           [b.grad_by_value().data() for b in B])
+    with capsys.disabled():
+        print(f"\n  TF32 step: ReLU mask flips {chk['flips']} of {chk['elements']} (inside the 2e-3 band: {chk['in_band']})")
+    assert chk["outside_mismatch"] == [0, 0], chk
+    for flips, n in zip(chk["flips"], chk["elements"]):
+        assert flips <= 1e-3 * n, chk          # a flip needs |z| below the GEMM's actual error, far inside the band
+    assert max(chk["rel_gw"]) <= 2e-3 and max(chk["rel_gb"]) <= 2e-3, chk
 
 
 def test_relu_mask_is_exact_for_the_device_forward(gpu):

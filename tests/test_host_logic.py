@@ -98,3 +98,29 @@ def test_two_rank_data_parallel_step_matches_single_process(ora, tmp_path):
         np.testing.assert_allclose(r0[k], single[i], rtol=1e-5, atol=3e-6)
     # the global mean loss is the mean of the per-rank mean losses (equal shard sizes)
     np.testing.assert_allclose((r0["losses"] + r1["losses"]) / 2, full_losses, rtol=1e-5)
+
+
+def test_shard_weight_makes_unequal_shards_add_up_to_the_global_mean(ts, ora):
+    """batch % world != 0: each rank's loss is the mean over its own rows, so a plain sum / world over-weights the
+    rows of the shorter shards.  Seeding each rank's backward with shard_weight() repairs that."""
+    rng = np.random.default_rng(11)
+    dims, batch, world = [12, 20, 6], 50, 4
+    ws = [rng.standard_normal((dims[i], dims[i + 1])) for i in range(2)]
+    bs = [rng.standard_normal(dims[i + 1]) for i in range(2)]
+    x, t = rng.standard_normal((batch, dims[0])), rng.standard_normal((batch, dims[-1]))
+    full = ora.mlp_step_f64(ws, bs, x, t)
+    shards = [ts.distributed.shard_rows(batch, r, world) for r in range(world)]
+    assert [b - a for a, b in shards] == [13, 13, 12, 12] and shards[0][0] == 0 and shards[-1][1] == batch
+    weights = [ts.distributed.shard_weight(batch, r, world) for r in range(world)]
+    assert abs(sum(weights) - world) < 1e-12
+    plain = [np.zeros_like(w) for w in ws]
+    weighted = [np.zeros_like(w) for w in ws]
+    for (a, b), wgt in zip(shards, weights):
+        g = ora.mlp_step_f64(ws, bs, x[a:b], t[a:b])["gw"]
+        for l in range(2):
+            plain[l] += g[l] / world
+            weighted[l] += wgt * g[l] / world
+    for l in range(2):
+        np.testing.assert_allclose(weighted[l], full["gw"][l], rtol=1e-12, atol=1e-14)
+        assert np.abs(plain[l] - full["gw"][l]).max() > 1e-4 * np.abs(full["gw"][l]).max()   # the unweighted sum is measurably off
+    assert ts.distributed.shard_weight(64, 1, 4) == 1.0

@@ -12,6 +12,8 @@ that the library's allocator did not reach the driver, that the largest plan thi
 produce fits the built-in scratch, and that bad pointers are refused.  The file name sorts last so that a run stopping
 at the first failure has already been through every other test.
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -31,10 +33,34 @@ def test_static_scratch_colsum_matches_regular_entry_point_twice(gpu):
         bufs.append((rows, cols, g, DevBuf(gpu, g), DevBuf(gpu, n=cols), DevBuf(gpu, n=cols),
                      DevBuf(gpu, n=int(lib.ts_colsum_scratch_elems(rows, cols)))))
     gpu.synchronize()
-    before = gpu.allocator_stats()
+
+    def free_bytes():
+        f = C.c_ulonglong()
+        chk(lib.ts_device_memory_info(C.byref(f), None), "memory info")
+        return int(f.value)
+
+    # The first call on a device resolves the built-in array's address; that look-up is part of set-up, so the
+    # claim "takes no device memory" is checked around the calls that follow it: free memory as the driver reports
+    # it must not move, with the library's per-kernel event profiling switched on as well (creating an event would
+    # allocate, so this entry point must not bracket its launches).
+    # (Each shape is also run once beforehand: the CUDA runtime loads a kernel's code onto the device at its first
+    # launch, which is the runtime's allocation, not this entry point's.)
     for rows, cols, g, dg, out_static, out_ref, scratch in bufs:
-        chk(lib.launch_colsum_kernel_static_scratch(dg.ptr, out_static.ptr, rows, cols, None), "static scratch")
+        chk(lib.launch_colsum_kernel_static_scratch(dg.ptr, out_static.ptr, rows, cols, None), "static scratch, first call")
+    gpu.synchronize()
+    before, free_before = gpu.allocator_stats(), free_bytes()
+    lib.ts_profile_reset()
+    lib.ts_profile_enable(1)
+    try:
+        for rows, cols, g, dg, out_static, out_ref, scratch in bufs:
+            chk(lib.launch_colsum_kernel_static_scratch(dg.ptr, out_static.ptr, rows, cols, None), "static scratch")
+        gpu.synchronize()
+        free_after = free_bytes()
+    finally:
+        lib.ts_profile_enable(0)
+        lib.ts_profile_reset()
     after = gpu.allocator_stats()
+    assert free_after == free_before, f"device memory moved by {free_before - free_after} bytes across calls that must not allocate"
     assert after["driver_allocations"] == before["driver_allocations"]
     assert after["bytes_reserved"] == before["bytes_reserved"] and after["bytes_in_use"] == before["bytes_in_use"]
     for rows, cols, g, dg, out_static, out_ref, scratch in bufs:

@@ -50,6 +50,7 @@ SIGNATURES = {
     "ts_allocator_get_stats": (C.c_bool, [C.POINTER(AllocatorStats)]),
     "ts_allocator_release_cached": (None, []),
     "ts_allocator_set_limit": (None, [u64]),
+    "ts_device_memory_info": (C.c_bool, [u64p, u64p]),
     "ts_event_create": (vp, []),
     "ts_event_destroy": (None, [vp]),
     "ts_event_record": (C.c_bool, [vp, vp]),

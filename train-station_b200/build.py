@@ -26,13 +26,28 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; the library cannot be built (there is no CPU fallback)")
 
 
-def needs_build() -> bool:
-    if not os.path.exists(LIB):
-        return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [
+STAMP = LIB + ".stamp"
+
+
+def _source_digest() -> str:
+    """Hash of everything the library is made from.  Contents, not timestamps: a copy of the tree to another
+    machine keeps the binary valid whatever it does to modification times."""
+    import hashlib
+    h = hashlib.sha256()
+    deps = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)) + [
         os.path.join(HERE, "..", "include", "train_station_b200.h"), os.path.abspath(__file__)]
-    return any(os.path.getmtime(d) > t for d in deps)
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
+        return True
+    with open(STAMP) as f:
+        return f.read().strip() != _source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -41,26 +56,43 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    procs = []
+    import hashlib
+    shared = b""
+    for dep in (os.path.join(CSRC, "common.h"), os.path.join(HERE, "..", "include", "train_station_b200.h"), os.path.abspath(__file__)):
+        with open(dep, "rb") as f:
+            shared += f.read()
+    procs, objs = [], []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        objs.append(obj)
+        with open(os.path.join(CSRC, src), "rb") as f:
+            digest = hashlib.sha256(shared + f.read()).hexdigest()
+        stamp = obj + ".stamp"
+        if not force and not verbose and os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read().strip() == digest:
+            continue   # this translation unit and everything it includes are unchanged
         cmd = [nvcc, *ARCH, *CFLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
-        procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-    objs = []
-    for src, obj, p in procs:
+        procs.append((src, stamp, digest, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = None
+    for src, stamp, digest, p in procs:
         out, _ = p.communicate()
         if p.returncode != 0:
-            raise RuntimeError(f"nvcc failed on {src}:\n{out}")
+            failed = failed or f"nvcc failed on {src}:\n{out}"
+            continue
         if verbose and out:
             print(out)
-        objs.append(obj)
+        with open(stamp, "w") as f:
+            f.write(digest + "\n")
+    if failed:
+        raise RuntimeError(failed)
     # NCCL is opened with dlopen when data parallelism is first used (see engine.cu), so it is not linked here
     link = [nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-ldl", "-Xcompiler", "-fPIC"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
+    with open(STAMP, "w") as f:
+        f.write(_source_digest() + "\n")
     return LIB
 
 

@@ -78,6 +78,14 @@ struct ProfScope {
     double work;
 };
 
+// While one of these is alive on a thread, ProfScope only counts launches: it creates and records no events even
+// when profiling is on.  For entry points that promise not to allocate (event creation allocates).
+struct ProfSuspend {
+    ProfSuspend();
+    ~ProfSuspend();
+    bool was_on;
+};
+
 int matmul_precision();
 bool fusion_enabled();
 

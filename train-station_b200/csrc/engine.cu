@@ -1942,20 +1942,27 @@ TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
 TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad_scale) {
     if (!o || (n > 0 && !params)) { set_error("adam step: null argument"); return false; }
     DeviceCtx* c = o->c;
-    o->step_count += 1;   // adam/mod.rs:1037
+    // Everything is validated before any counter moves: a call that fails leaves step_count and the per-parameter
+    // steps where they were, so later bias corrections are not shifted by it.
+    for (int i = 0; i < n; ++i) {
+        if (!params[i]) { set_error("adam step: null parameter at index %d", i); return false; }
+        const TensorP& p = params[i]->t;
+        if (!o->states.count(p->id)) {   // adam/mod.rs:489-492 asserts
+            set_error("adam step: parameter %llu is not linked to the optimizer; call add_parameter first", (unsigned long long)p->id);
+            return false;
+        }
+        TensorP g = grad_lookup(p->id);
+        if (g && g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
+    }
     std::vector<k::AdamTensor> tab;
     std::vector<unsigned long long> sizes;
     std::vector<StorageP> touched;
     std::vector<uint64_t> tab_ids;
     std::string skipped;
+    std::vector<AdamState*> stepped;
     for (int i = 0; i < n; ++i) {
-        if (!params[i]) { set_error("adam step: null parameter at index %d", i); return false; }
         TensorP p = params[i]->t;
         auto it = o->states.find(p->id);
-        if (it == o->states.end()) {   // adam/mod.rs:489-492 asserts
-            set_error("adam step: parameter %llu is not linked to the optimizer; call add_parameter first", (unsigned long long)p->id);
-            return false;
-        }
         TensorP g = grad_lookup(p->id);
         if (!g) {   // adam/mod.rs:494-497, 1039-1042: reported and skipped
             skipped += (skipped.empty() ? "" : ", ") + std::to_string(p->id);
@@ -1964,8 +1971,7 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         const float* gp = rptr(g);
         float* pp = const_cast<float*>(rptr(p));
         if (!gp || !pp) return false;
-        if (g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
-        it->second.step += 1;
+        stepped.push_back(&it->second);
         tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size,
                                     o->amsgrad ? it->second.vmax->ptr : nullptr});
         sizes.push_back(p->size);
@@ -1973,6 +1979,8 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         tab_ids.push_back(p->id);
     }
     if (tab.empty() && !dp_join(c)) return false;
+    o->step_count += 1;   // adam/mod.rs:1037
+    for (AdamState* st : stepped) st->step += 1;
     if (!tab.empty()) {
         {   // deferred operations that read a parameter must see its value from before this step
             std::unordered_set<const Storage*> written;

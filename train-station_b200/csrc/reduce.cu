@@ -354,5 +354,8 @@ TS_API bool launch_colsum_kernel_static_scratch(const float* g, float* out, unsi
     }
     // Every partial the second stage reads is written by the first stage of the same call, so nothing in the
     // array has to start at zero and stale contents of an earlier call are never read.
+    // With ts_profile_enable(1) a launch is normally bracketed by two events, and creating an event allocates:
+    // here the launch is only counted.
+    ProfSuspend no_events;
     return k::colsum(g, out, rows, cols, scratch, s);
 }

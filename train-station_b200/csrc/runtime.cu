@@ -231,6 +231,9 @@ ProfScope::~ProfScope() {
     g_prof_pending.push_back(ProfRecord{start, end, cls, work});
 }
 
+ProfSuspend::ProfSuspend() : was_on(g_prof_on) { g_prof_on = false; }
+ProfSuspend::~ProfSuspend() { g_prof_on = was_on; }
+
 }  // namespace ts
 
 using namespace ts;
@@ -399,6 +402,14 @@ TS_API void ts_allocator_release_cached(void) {
     if (!c) return;
     cudaStreamSynchronize(c->compute);
     c->alloc.release_cached();
+}
+TS_API bool ts_device_memory_info(unsigned long long* free_bytes, unsigned long long* total_bytes) {
+    if (!ctx()) return false;
+    size_t f = 0, t = 0;
+    TS_CHECK(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return true;
 }
 TS_API void ts_allocator_set_limit(unsigned long long bytes) {
     DeviceCtx* c = ctx();

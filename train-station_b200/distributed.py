@@ -61,7 +61,23 @@ def register_parameters(params: Sequence[Tensor]) -> None:
 
 def shard_rows(n_rows: int, rank_: int, world: int) -> Tuple[int, int]:
     """Contiguous block [start, stop) of batch rows for a rank; the first n_rows % world
-    ranks get one extra row."""
+    ranks get one extra row (see shard_weight for what unequal shards need)."""
     base, extra = divmod(int(n_rows), int(world))
     start = rank_ * base + min(rank_, extra)
     return start, start + base + (1 if rank_ < extra else 0)
+
+
+def shard_weight(n_rows: int, rank_: int, world: int) -> float:
+    """Weight of a rank's mean loss in the mean over the whole batch, times `world`: rows_local * world / n_rows.
+
+    Each rank's loss is the mean over its own rows and Adam multiplies the summed gradients by 1 / world, which is the
+    gradient of the global mean only when every shard has the same number of rows.  With n_rows % world != 0 seed each
+    rank's backward with this weight (``loss.backward(Tensor.from_slice([w], [1]))``): the sum over ranks of
+    w_r * grad_r, divided by world, is then the gradient of the mean over all rows.  It is 1.0 for equal shards."""
+    a, b = shard_rows(n_rows, rank_, world)
+    return (b - a) * float(world) / float(n_rows)
+
+
+def describe() -> str:
+    """One line on how gradients are combined, for benchmark records."""
+    return "NCCL sum of parameter gradients on a communication stream, overlapped with backward; Adam scales by 1/world"
