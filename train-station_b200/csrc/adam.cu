@@ -1,5 +1,6 @@
 // Fused multi-tensor Adam: one launch updates every parameter tensor of the optimizer.
-// HBM-bound: 28 bytes per parameter (read p, g, m, v; write p, m, v).
+// HBM-bound: 28 bytes per parameter (read p, g, m, v; write p, m, v), 32 when the TF32-rounded copy of the
+// parameter that the tensor-core GEMMs read is written in the same pass.
 //
 // Arithmetic follows optimizers/adam/mod.rs operation by operation, each step rounded
 // separately (no FMA contraction), so that with identical gradients the updated
@@ -44,10 +45,16 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
     p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, mh), __fadd_rn(__fsqrt_rn(vh), sc.eps)));
 }
 
+__device__ __forceinline__ float rn_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
 // The tensor table travels in the kernel's parameters: the pointers are captured when the launch is
 // enqueued, so a host that runs steps ahead of the GPU cannot overwrite a table that a queued launch
 // has yet to read (a table staged in reused pinned memory did exactly that).
-constexpr int kMaxTensorsPerLaunch = 48;
+constexpr int kMaxTensorsPerLaunch = 40;   // 40 records of 56 bytes: inside the 4 KiB of kernel parameters with room to spare
 struct AdamTable { AdamTensor t[kMaxTensorsPerLaunch]; };
 
 template <bool AMS>
@@ -66,6 +73,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
     uintptr_t bits = reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
                      reinterpret_cast<uintptr_t>(t.v);
     if (AMS) bits |= reinterpret_cast<uintptr_t>(t.vmax);
+    bits |= reinterpret_cast<uintptr_t>(t.tf32_out);
     const bool vec = (bits & 15) == 0;
     float unused = 0.0f;
     if (vec) {
@@ -92,6 +100,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
             adam_one<AMS>(p0.w, g0.w, m0.w, w0.w, x0.w, e + 3 < body, sc);
             pp[i] = p0; mp[i] = m0; vp[i] = w0;
             if (AMS) xp[i] = x0;
+            if (t.tf32_out) reinterpret_cast<float4*>(t.tf32_out)[i] = make_float4(rn_tf32(p0.x), rn_tf32(p0.y), rn_tf32(p0.z), rn_tf32(p0.w));
             if (has2) {
                 e = j * 4;
                 adam_one<AMS>(p1.x, g1.x, m1.x, w1.x, x1.x, e < body, sc);
@@ -100,6 +109,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
                 adam_one<AMS>(p1.w, g1.w, m1.w, w1.w, x1.w, e + 3 < body, sc);
                 pp[j] = p1; mp[j] = m1; vp[j] = w1;
                 if (AMS) xp[j] = x1;
+                if (t.tf32_out) reinterpret_cast<float4*>(t.tf32_out)[j] = make_float4(rn_tf32(p1.x), rn_tf32(p1.y), rn_tf32(p1.z), rn_tf32(p1.w));
             }
         }
         for (unsigned long long i = v1 * 4 + threadIdx.x; i < end; i += kThreads) {
@@ -107,6 +117,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
             adam_one<AMS>(p, t.g[i], m, v, x, i < body, sc);
             t.p[i] = p; t.m[i] = m; t.v[i] = v;
             if (AMS) t.vmax[i] = x;
+            if (t.tf32_out) t.tf32_out[i] = rn_tf32(p);
         }
     } else {
         for (unsigned long long i = start + threadIdx.x; i < end; i += kThreads) {
@@ -114,6 +125,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ 
             adam_one<AMS>(p, t.g[i], m, v, x, i < body, sc);
             t.p[i] = p; t.m[i] = m; t.v[i] = v;
             if (AMS) t.vmax[i] = x;
+            if (t.tf32_out) t.tf32_out[i] = rn_tf32(p);
         }
     }
 }
@@ -155,16 +167,17 @@ bool adam_launch_range(const AdamTensor* tensors, int first, int last, const voi
         AdamTable tab;
         memset(&tab, 0, sizeof(tab));
         int n_chunks = 0;
-        double elems = 0;
+        double elems = 0, tf32_elems = 0;
         for (int i = 0; i < cnt; ++i) {
             tab.t[i] = tensors[t0 + i];
             n_chunks += (int)((tensors[t0 + i].n + kChunk - 1) / kChunk);
             elems += (double)tensors[t0 + i].n;
+            if (tensors[t0 + i].tf32_out) tf32_elems += (double)tensors[t0 + i].n;
         }
         if (n_chunks > 0) {
             // every tensor of one optimizer has a running maximum, or none has
             const bool ams = tab.t[0].vmax != nullptr;
-            ProfScope prof(kProfAdam, s, (ams ? 36.0 : 28.0) * elems);
+            ProfScope prof(kProfAdam, s, (ams ? 36.0 : 28.0) * elems + 4.0 * tf32_elems);
             DeviceCtx* c = ctx();
             const int want = 2 * (c ? c->sm_count : 148);
             int split_log2 = 0;

@@ -148,6 +148,7 @@ struct AdamTensor {
     float* v;
     unsigned long long n;
     float* vmax = nullptr;   // AMSGrad: running maximum of the bias-corrected second moment; null = plain Adam
+    float* tf32_out = nullptr;   // when set: also receives the updated parameter rounded to the nearest TF32 value
 };
 int adam_chunk_count(const unsigned long long* sizes, int n);
 size_t adam_chunk_bytes(int n_chunks);

@@ -296,14 +296,20 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
+    bool fake = false;   // an in-process stand-in installed by ts_dp_install_fake_nccl (host-side failure tests)
 };
+static NcclApi g_nccl;
+static std::mutex g_nccl_mu;
 static NcclApi* nccl_api() {
-    static NcclApi api;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lk(mu);
+    NcclApi& api = g_nccl;
+    std::lock_guard<std::mutex> lk(g_nccl_mu);
     if (api.ok) return &api;
     void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
     if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
@@ -311,9 +317,14 @@ static NcclApi* nccl_api() {
     api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
     api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
     api.AllReduce = (decltype(api.AllReduce))dlsym(h, "ncclAllReduce");
+    api.ReduceScatter = (decltype(api.ReduceScatter))dlsym(h, "ncclReduceScatter");
+    api.AllGather = (decltype(api.AllGather))dlsym(h, "ncclAllGather");
+    api.CommGetAsyncError = (decltype(api.CommGetAsyncError))dlsym(h, "ncclCommGetAsyncError");
+    api.CommAbort = (decltype(api.CommAbort))dlsym(h, "ncclCommAbort");
     api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
     api.GetErrorString = (decltype(api.GetErrorString))dlsym(h, "ncclGetErrorString");
-    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString) {
+    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.ReduceScatter || !api.AllGather || !api.CommGetAsyncError ||
+        !api.CommAbort || !api.CommDestroy || !api.GetErrorString) {
         set_error("data parallelism needs NCCL: a required symbol is missing from libnccl.so.2");
         return nullptr;
     }
@@ -322,48 +333,151 @@ static NcclApi* nccl_api() {
 }
 
 // ------------------------------------------------------------------ data-parallel state
+// The cross-rank sum of one registered parameter's gradient since the last zero_grad.  Large tensors are
+// reduce-scattered: this rank then holds the sum only for elements [lo, lo + cnt), runs Adam on that slice alone and
+// the updated parameters are all-gathered, so that neither the optimizer's 28 bytes per parameter nor its arithmetic
+// are replicated on every GPU.  Small or oddly sized tensors are all-reduced and updated on every rank.
+struct DpGrad {
+    TensorP buf;             // full-size buffer
+    bool sliced = false;     // produced by a reduce-scatter: [lo, lo + cnt) holds the sum over ranks
+    bool gathered = false;   // ... and the other ranks' slices have since been all-gathered into it (grad_by_value)
+    size_t lo = 0, cnt = 0;
+};
 struct DpState {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     std::unordered_set<uint64_t> params;
-    cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
-    bool comm_outstanding = false;
-    // per-parameter completion of the gradient all-reduce, so that Adam can update each tensor as soon as its
-    // own sum has landed instead of waiting for the last one
-    std::unordered_map<uint64_t, cudaEvent_t> done_event;
-    std::vector<uint64_t> pending_order;   // parameter ids in the order their all-reduces were enqueued
+    cudaEvent_t ev_compute = nullptr, ev_comm = nullptr, ev_grads = nullptr;
+    bool comm_outstanding = false;    // work on the communication stream that the compute stream has not been ordered after
+    bool grads_outstanding = false;   // ... some of which reads or writes gradient buffers (ev_grads marks its end)
+    std::unordered_map<uint64_t, DpGrad> red;
+    std::unordered_map<uint64_t, cudaEvent_t> done_event;   // per parameter: its gradient's sum has landed
+    std::vector<TensorP> retired;     // buffers the communication stream may still read; released at the next join
+    bool failed = false;              // the communicator reported an asynchronous error and was aborted
 };
 static thread_local DpState g_dp;
 
-static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n, uint64_t param_id = 0) {
-    if (!g_dp.comm || g_dp.world <= 1) return true;
-    if (!g_dp.ev_compute) {
-        TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_compute, cudaEventDisableTiming));
-        TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_comm, cudaEventDisableTiming));
-    }
-    TS_CHECK(cudaEventRecord(g_dp.ev_compute, c->compute));
-    TS_CHECK(cudaStreamWaitEvent(c->comm, g_dp.ev_compute, 0));
+// Tensors below this size, or whose size is not a multiple of 8 * world, keep the all-reduce and the replicated update
+// (a slice must start on a multiple of 8 elements so that Adam's 8-wide body / tail association, adam/mod.rs:761-772,
+// is the one the whole tensor would get).
+constexpr size_t kMinShardElems = size_t(1) << 16;
+static bool dp_shard_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TS_DP_SHARD"); v = (e && e[0] == '0') ? 0 : 1; }   // TS_DP_SHARD=0: all-reduce everything
+    return v == 1;
+}
+
+static bool dp_nccl_ok(NcclApi* nc, ncclResult_t r, const char* what) {
+    if (r == ncclSuccess) return true;
+    set_error("%s failed: %s", what, nc->GetErrorString(r));
+    return false;
+}
+// Polls the communicator for an asynchronous error (a peer that died, a transport fault).  On error the
+// communicator is aborted, so that no later call can block on it, and every later collective is refused.
+static bool dp_healthy() {
+    if (g_dp.failed) { set_error("data parallelism: the communicator was aborted after an asynchronous NCCL error"); return false; }
+    if (!g_dp.comm) return true;
     NcclApi* nc = nccl_api();
     if (!nc) return false;
-    ncclResult_t r = nc->AllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm);
-    if (r != ncclSuccess) { set_error("ncclAllReduce failed: %s", nc->GetErrorString(r)); return false; }
-    g_dp.comm_outstanding = true;
-    if (param_id) {
-        cudaEvent_t& ev = g_dp.done_event[param_id];
-        if (!ev) TS_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-        TS_CHECK(cudaEventRecord(ev, c->comm));
-        g_dp.pending_order.push_back(param_id);
-    }
+    ncclResult_t async = ncclSuccess;
+    ncclResult_t r = nc->CommGetAsyncError(g_dp.comm, &async);
+    if (r == ncclSuccess && (async == ncclSuccess || async == ncclInProgress)) return true;
+    const ncclResult_t shown = r != ncclSuccess ? r : async;
+    nc->CommAbort(g_dp.comm);
+    g_dp.comm = nullptr;
+    g_dp.failed = true;
+    set_error("data parallelism: NCCL reported an asynchronous error (%s); the communicator was aborted", nc->GetErrorString(shown));
+    return false;
+}
+static bool dp_events() {
+    if (g_dp.ev_compute) return true;
+    TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_compute, cudaEventDisableTiming));
+    TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_comm, cudaEventDisableTiming));
+    TS_CHECK(cudaEventCreateWithFlags(&g_dp.ev_grads, cudaEventDisableTiming));
     return true;
 }
-// The compute stream waits for every all-reduce enqueued so far.
+// The communication stream waits for everything enqueued on the compute stream so far.
+static bool dp_comm_after_compute(DeviceCtx* c) {
+    if (!dp_events()) return false;
+    TS_CHECK(cudaEventRecord(g_dp.ev_compute, c->compute));
+    TS_CHECK(cudaStreamWaitEvent(c->comm, g_dp.ev_compute, 0));
+    return true;
+}
+// Marks the end of the gradient-touching work enqueued on the communication stream so far.
+static bool dp_mark_grads(DeviceCtx* c) {
+    TS_CHECK(cudaEventRecord(g_dp.ev_grads, c->comm));
+    g_dp.comm_outstanding = g_dp.grads_outstanding = true;
+    return true;
+}
+
+static bool dp_all_reduce_async(DeviceCtx* c, float* data, size_t n) {
+    if (!g_dp.comm || g_dp.world <= 1) return true;
+    if (!dp_healthy() || !dp_comm_after_compute(c)) return false;
+    NcclApi* nc = nccl_api();
+    if (!nc || !dp_nccl_ok(nc, nc->AllReduce(data, data, n, ncclFloat32, ncclSum, g_dp.comm, c->comm), "ncclAllReduce")) return false;
+    return dp_mark_grads(c);
+}
+// The compute stream waits for everything enqueued on the communication stream so far.
 static bool dp_join(DeviceCtx* c) {
     if (!g_dp.comm_outstanding) return true;
     TS_CHECK(cudaEventRecord(g_dp.ev_comm, c->comm));
     TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.ev_comm, 0));
-    g_dp.comm_outstanding = false;
-    g_dp.pending_order.clear();
+    g_dp.comm_outstanding = g_dp.grads_outstanding = false;
+    g_dp.retired.clear();
+    return dp_healthy();
+}
+// The compute stream waits for the gradient-touching part only: what gradient buffers need before they are reused.
+// All-gathers of updated parameters that follow it on the communication stream keep running.
+static bool dp_join_grads(DeviceCtx* c) {
+    if (!g_dp.grads_outstanding) return true;
+    TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.ev_grads, 0));
+    g_dp.grads_outstanding = false;
+    g_dp.retired.clear();
     return true;
+}
+
+// Starts the cross-rank sum of a registered parameter's finished local gradient `lg` (which nothing else references)
+// on the communication stream and files it under the parameter's id.  A parameter that already holds a sum from an
+// earlier backward() since the last zero_grad gets the new sum added to it: sum(G1) + sum(G2), as the reference
+// accumulates G1 + G2 (gradtrack/engine.rs:514-524).
+static bool dp_reduce_leaf(DeviceCtx* c, uint64_t id, const TensorP& lg) {
+    NcclApi* nc = nccl_api();
+    if (!nc || !dp_healthy() || !dp_comm_after_compute(c)) return false;
+    const size_t n = lg->size;
+    const size_t world = (size_t)g_dp.world;
+    auto have = g_dp.red.find(id);
+    bool slice = dp_shard_enabled() && n >= kMinShardElems && n % (8 * world) == 0;
+    if (have != g_dp.red.end() && (!have->second.sliced || have->second.gathered)) slice = false;   // the earlier sum is held in full
+    float* p = lg->st->ptr;
+    const size_t cnt = slice ? n / world : n, lo = slice ? (size_t)g_dp.rank * cnt : 0;
+    if (slice) {
+        if (!dp_nccl_ok(nc, nc->ReduceScatter(p, p + lo, cnt, ncclFloat32, ncclSum, g_dp.comm, c->comm), "ncclReduceScatter")) return false;
+    } else {
+        if (!dp_nccl_ok(nc, nc->AllReduce(p, p, n, ncclFloat32, ncclSum, g_dp.comm, c->comm), "ncclAllReduce")) return false;
+    }
+    if (have == g_dp.red.end()) {
+        DpGrad g;
+        g.buf = lg; g.sliced = slice; g.lo = lo; g.cnt = cnt;
+        g_dp.red[id] = g;
+    } else {
+        float* acc = have->second.buf->st->ptr;
+        if (!k::binary(0, acc + lo, p + lo, acc + lo, cnt, c->comm)) return false;
+        g_dp.retired.push_back(lg);   // read by the add above: kept until the compute stream is ordered after it
+    }
+    cudaEvent_t& ev = g_dp.done_event[id];
+    if (!ev) TS_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    TS_CHECK(cudaEventRecord(ev, c->comm));
+    return dp_mark_grads(c);
+}
+// Makes a reduce-scattered gradient whole on every rank (for a caller that wants to read it).
+static bool dp_gather_grad(DeviceCtx* c, DpGrad& g) {
+    if (!g.sliced || g.gathered) return true;
+    NcclApi* nc = nccl_api();
+    if (!nc || !dp_healthy()) return false;
+    float* p = g.buf->st->ptr;
+    if (!dp_nccl_ok(nc, nc->AllGather(p + g.lo, p, g.cnt, ncclFloat32, g_dp.comm, c->comm), "ncclAllGather")) return false;
+    g.gathered = true;
+    return dp_mark_grads(c);
 }
 
 // ------------------------------------------------------------------ helpers
@@ -432,7 +546,9 @@ static std::vector<size_t> broadcast_strides(const std::vector<size_t>& own, con
 
 static TensorP grad_lookup(uint64_t id) {
     auto it = g_graph.grads.find(id);
-    return it == g_graph.grads.end() ? nullptr : it->second;
+    if (it != g_graph.grads.end()) return it->second;
+    auto r = g_dp.red.find(id);   // a registered parameter's gradient lives with the data-parallel state once its sum has started
+    return r == g_dp.red.end() ? nullptr : r->second.buf;
 }
 
 // gradtrack/engine.rs:514-524: existing + new into a fresh tensor.
@@ -989,26 +1105,28 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
 }
 
 // A leaf's gradient is final: launch the GEMM that produces it and, under data parallelism,
-// start its all-reduce on the communication stream while the rest of backward proceeds.
+// start its cross-rank sum on the communication stream while the rest of backward proceeds.
 static bool finalize_leaf(DeviceCtx* c, uint64_t id, std::unordered_set<uint64_t>& reduced) {
     TensorP lg = g_graph.grads[id];
     if (!rptr(lg)) return false;
     if (!g_dp.comm || !g_dp.params.count(id) || reduced.count(id)) return true;
-    if (lg->st.use_count() > 1) {
-        // the buffer is shared with another gradient: reduce a private copy
+    // The sum runs in place on the communication stream, so the buffer must belong to this gradient alone.  It does
+    // not when another gradient shares the storage, or the tensor object itself (Add hands the same object to both
+    // operands of equal shape, Sub hands the upstream gradient on, a deferred GEMM keeps its operands): two
+    // references are this function's and the gradient map's, any more is somebody else.
+    if (lg.use_count() > 2 || lg->st.use_count() > 1) {
         TensorP priv = new_tensor(c, lg->dims);
         if (!priv || !cuda_ok(cudaMemcpyAsync(priv->st->ptr, lg->st->ptr, lg->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "gradient copy")) return false;
-        g_graph.grads[id] = priv;
         lg = priv;
     }
     reduced.insert(id);
-    return dp_all_reduce_async(c, lg->st->ptr, lg->size, id);
+    g_graph.grads.erase(id);   // from here on the gradient is the data-parallel state's (grad_lookup finds it there)
+    return dp_reduce_leaf(c, id, lg);
 }
 
 static bool backward(const TensorP& root, const TensorP& grad_output) {
     DeviceCtx* c = ctx();
     if (!c) return false;
-    if (g_dp.comm_outstanding && !dp_join(c)) return false;   // earlier gradients may be accumulated into below
     // seed: gradtrack/engine.rs:964-978
     TensorP seed = grad_output;
     if (!seed) {
@@ -1075,7 +1193,19 @@ static bool backward(const TensorP& root, const TensorP& grad_output) {
 }
 
 // ------------------------------------------------------------------ Adam
-struct AdamState { StorageP m, v, vmax; uint64_t step = 0; size_t n = 0; };   // vmax only under amsgrad
+struct AdamState {
+    StorageP m, v, vmax;   // vmax only under amsgrad
+    uint64_t step = 0;
+    size_t n = 0;
+    // Data parallel, sharded update: since the last gather only elements [lo, lo + cnt) of m, v (vmax) are current on this rank
+    bool sharded = false;
+    size_t lo = 0, cnt = 0;
+};
+struct ChunkCache {          // the kernel's chunk map for one list of tensor sizes, kept on the device
+    std::vector<unsigned long long> sizes;
+    float* dev = nullptr;
+    int n = 0;
+};
 
 }  // namespace ts
 
@@ -1085,12 +1215,32 @@ struct ts_adam {
     uint64_t step_count = 0;
     std::unordered_map<uint64_t, ts::AdamState> states;
     std::vector<uint64_t> order;                 // insertion order, adam/mod.rs:201-206
-    // launch tables
-    std::vector<unsigned long long> cached_sizes;
-    float* chunks_dev = nullptr;
-    int n_chunks = 0;
+    ts::ChunkCache whole, sliced;                // launch tables of the replicated and of the sharded update
     ts::DeviceCtx* c = nullptr;
 };
+
+namespace ts {
+static thread_local std::unordered_set<ts_adam*> g_adams;   // live optimizers of this thread (their state may be sharded)
+
+// After sharded updates only this rank's slice of the moments is current: all-gather them in place.  A collective:
+// every rank must get here (reading optimizer state, a replicated update of the tensor, or ts_dp_finalize).
+static bool gather_adam_state(DeviceCtx* c, AdamState& st) {
+    if (!st.sharded) return true;
+    NcclApi* nc = nccl_api();
+    if (!nc || !g_dp.comm) {
+        set_error("Adam state of a parameter is sharded across ranks but the communicator is gone; gather it before ts_dp_finalize");
+        return false;
+    }
+    if (!dp_healthy() || !dp_comm_after_compute(c)) return false;
+    for (const StorageP& sp : {st.m, st.v, st.vmax}) {
+        if (!sp) continue;
+        if (!dp_nccl_ok(nc, nc->AllGather(sp->ptr + st.lo, sp->ptr, st.cnt, ncclFloat32, g_dp.comm, c->comm), "ncclAllGather")) return false;
+    }
+    g_dp.comm_outstanding = true;
+    st.sharded = false;
+    return dp_join(c);
+}
+}  // namespace ts
 
 using namespace ts;
 
@@ -1880,17 +2030,26 @@ TS_API ts_tensor* ts_tensor_grad_by_value(const ts_tensor* t) {
     TensorP g = grad_lookup(t->t->id);
     if (!g) return nullptr;
     if (!materialize(g)) return nullptr;
-    if (g_dp.comm_outstanding) {   // a gradient handed to the caller must be the all-reduced one
+    auto r = g_dp.red.find(t->t->id);
+    if (r != g_dp.red.end() || g_dp.comm_outstanding) {
+        // a gradient handed to the caller must be the sum over ranks, whole: a reduce-scattered one is gathered first
+        // (a collective: every rank has to ask for it)
         DeviceCtx* c = ctx();
-        if (!c || !dp_join(c)) return nullptr;
+        if (!c) return nullptr;
+        if (r != g_dp.red.end() && !dp_gather_grad(c, r->second)) return nullptr;
+        if (!dp_join(c)) return nullptr;
     }
     return wrap(reshaped_alias(g, t->t->dims));
 }
 TS_API void ts_clear_gradients(void) {
-    if (g_dp.comm_outstanding) {   // gradient buffers go back to the allocator below: no all-reduce may still write them
+    if (g_dp.grads_outstanding) {
+        // Gradient buffers go back to the allocator below and are reused in compute-stream order: the compute stream
+        // waits for the communication stream's last use of them (a sum, or the sharded Adam update).  The all-gathers
+        // of updated parameters that follow on the communication stream are not waited for here.
         DeviceCtx* c = ctx();
-        if (c) dp_join(c);
+        if (c) dp_join_grads(c);
     }
+    g_dp.red.clear();
     g_graph.ops.clear();
     g_graph.grads.clear();
     g_graph.bias_grad_ready.clear();
@@ -1907,6 +2066,7 @@ TS_API ts_adam* ts_adam_new(float lr, float beta1, float beta2, float eps, float
     ts_adam* o = new ts_adam();
     o->lr = lr; o->beta1 = beta1; o->beta2 = beta2; o->eps = eps; o->wd = weight_decay;
     o->c = c;
+    g_adams.insert(o);
     return o;
 }
 TS_API ts_adam* ts_adam_new_amsgrad(float lr, float beta1, float beta2, float eps, float weight_decay, int amsgrad) {
@@ -1916,7 +2076,12 @@ TS_API ts_adam* ts_adam_new_amsgrad(float lr, float beta1, float beta2, float ep
 }
 TS_API void ts_adam_free(ts_adam* o) {
     if (!o) return;
-    if (o->c) o->c->alloc.free(o->chunks_dev);
+    g_adams.erase(o);
+    if (o->c) {
+        if (g_dp.comm_outstanding) dp_join(o->c);   // the sharded update reads its chunk map on the communication stream
+        o->c->alloc.free(o->whole.dev);
+        o->c->alloc.free(o->sliced.dev);
+    }
     delete o;
 }
 TS_API bool ts_adam_add_parameter(ts_adam* o, const ts_tensor* p) {
@@ -1954,87 +2119,122 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         TensorP g = grad_lookup(p->id);
         if (g && g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
     }
-    std::vector<k::AdamTensor> tab;
-    std::vector<unsigned long long> sizes;
-    std::vector<StorageP> touched;
-    std::vector<uint64_t> tab_ids;
+    struct Item { TensorP p; AdamState* st; k::AdamTensor rec; bool from_dp = false, sliced = false; size_t lo = 0, cnt = 0; uint64_t id = 0; };
+    std::vector<Item> whole, sliced;
     std::string skipped;
-    std::vector<AdamState*> stepped;
+    const bool write_tf32 = matmul_precision() == 1;
     for (int i = 0; i < n; ++i) {
         TensorP p = params[i]->t;
-        auto it = o->states.find(p->id);
+        AdamState& st = o->states.find(p->id)->second;
         TensorP g = grad_lookup(p->id);
         if (!g) {   // adam/mod.rs:494-497, 1039-1042: reported and skipped
             skipped += (skipped.empty() ? "" : ", ") + std::to_string(p->id);
             continue;
         }
-        const float* gp = rptr(g);
+        auto red = g_dp.red.find(p->id);
+        const bool from_dp = red != g_dp.red.end() && g_graph.grads.find(p->id) == g_graph.grads.end();
+        // a gradient that is being summed on the communication stream is read there or behind its event: no wait here
+        const float* gp = from_dp ? red->second.buf->st->ptr : rptr(g);
         float* pp = const_cast<float*>(rptr(p));
         if (!gp || !pp) return false;
-        stepped.push_back(&it->second);
-        tab.push_back(k::AdamTensor{pp, gp, it->second.m->ptr, it->second.v->ptr, (unsigned long long)p->size,
-                                    o->amsgrad ? it->second.vmax->ptr : nullptr});
-        sizes.push_back(p->size);
-        touched.push_back(p->st);
-        tab_ids.push_back(p->id);
+        Item it;
+        it.p = p; it.st = &st; it.id = p->id; it.from_dp = from_dp;
+        it.sliced = from_dp && red->second.sliced;
+        if (it.sliced) { it.lo = red->second.lo; it.cnt = red->second.cnt; }
+        // TF32 mode: a parameter that feeds tensor-core GEMMs keeps a copy rounded to TF32 beside it; the update
+        // writes that copy too, so the next forward finds it current instead of running a rounding pass
+        float* tf = (write_tf32 && p->st->tf32_copy) ? p->st->tf32_copy : nullptr;
+        const size_t lo = it.lo, cnt = it.sliced ? it.cnt : p->size;
+        it.rec = k::AdamTensor{pp + lo, gp + lo, st.m->ptr + lo, st.v->ptr + lo, (unsigned long long)cnt,
+                               o->amsgrad ? st.vmax->ptr + lo : nullptr, tf ? tf + lo : nullptr};
+        (it.sliced ? sliced : whole).push_back(it);
     }
-    if (tab.empty() && !dp_join(c)) return false;
+    if (whole.empty() && sliced.empty() && !dp_join(c)) return false;
     o->step_count += 1;   // adam/mod.rs:1037
-    for (AdamState* st : stepped) st->step += 1;
-    if (!tab.empty()) {
+    // bias corrections in f64 from the f32-rounded betas, then to f32: adam/mod.rs:526-531, :793
+    const float stepf = (float)o->step_count;
+    const float bc1 = (float)(1.0 - std::pow((double)o->beta1, (double)stepf));
+    const float bc2 = (float)(1.0 - std::pow((double)o->beta2, (double)stepf));
+    const float f1 = 1.0f / bc1, f2 = 1.0f / bc2;
+    if (!whole.empty() || !sliced.empty()) {
         {   // deferred operations that read a parameter must see its value from before this step
             std::unordered_set<const Storage*> written;
-            for (auto& s : touched) written.insert(s.get());
+            for (auto& it : whole) written.insert(it.p->st.get());
+            for (auto& it : sliced) written.insert(it.p->st.get());
             if (!flush_pending(written)) return false;
         }
-        if (sizes != o->cached_sizes) {
-            int nc = k::adam_chunk_count(sizes.data(), (int)sizes.size());
-            size_t bytes = k::adam_chunk_bytes(nc);
+        // The pointer tables go to the kernel by value: the host may be several steps ahead of the GPU, and a table
+        // staged in reused host memory would be overwritten before the queued copy reads it.
+        auto chunks_for = [&](ChunkCache& cache, const std::vector<Item>& items) -> bool {
+            std::vector<unsigned long long> sizes;
+            for (auto& it : items) sizes.push_back(it.rec.n);
+            if (sizes == cache.sizes && cache.dev) return true;
+            const int nc = k::adam_chunk_count(sizes.data(), (int)sizes.size());
+            const size_t bytes = k::adam_chunk_bytes(nc);
             std::vector<char> host(bytes);
             k::adam_build_chunks(sizes.data(), (int)sizes.size(), host.data());
-            c->alloc.free(o->chunks_dev);
-            o->chunks_dev = c->alloc.alloc(bytes ? bytes : 16);
-            if (!o->chunks_dev) return false;
-            TS_CHECK(cudaMemcpyAsync(o->chunks_dev, host.data(), bytes, cudaMemcpyHostToDevice, c->compute));
+            if (g_dp.comm_outstanding && !dp_join(c)) return false;   // the old map may still be read on the communication stream
+            c->alloc.free(cache.dev);
+            cache.dev = c->alloc.alloc(bytes ? bytes : 16);
+            if (!cache.dev) return false;
+            TS_CHECK(cudaMemcpyAsync(cache.dev, host.data(), bytes, cudaMemcpyHostToDevice, c->compute));
             TS_CHECK(cudaStreamSynchronize(c->compute));
-            o->n_chunks = nc;
-            o->cached_sizes = sizes;
-        }
-        // The pointer table goes to the kernel by value: the host may be several steps ahead of the GPU, and a
-        // table staged in reused host memory would be overwritten before the queued copy reads it.
-        // bias corrections in f64 from the f32-rounded betas, then to f32: adam/mod.rs:526-531, :793
-        const float stepf = (float)o->step_count;
-        const float bc1 = (float)(1.0 - std::pow((double)o->beta1, (double)stepf));
-        const float bc2 = (float)(1.0 - std::pow((double)o->beta2, (double)stepf));
-        const float f1 = 1.0f / bc1, f2 = 1.0f / bc2;
-        if (g_dp.comm_outstanding && !g_dp.pending_order.empty()) {
-            // Data parallel: gradients are summed on the communication stream in the order backward produced them
-            // (last layer first).  Update each tensor as soon as its own sum has landed; the all-reduce of the first
-            // layer's gradient, which is enqueued last, then overlaps the updates of the other layers.
-            std::vector<char> launched(tab.size(), 0);
-            const std::vector<uint64_t> order = g_dp.pending_order;
-            for (uint64_t id : order) {
-                for (size_t i = 0; i < tab.size(); ++i) {
-                    if (tab_ids[i] != id || launched[i]) continue;
-                    TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.done_event[id], 0));
-                    if (!k::adam_launch_range(tab.data(), (int)i, (int)i + 1, o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd,
-                                              f1, f2, grad_scale, c->compute))
-                        return false;
-                    launched[i] = 1;
-                }
-            }
-            if (!dp_join(c)) return false;   // anything else that was outstanding
-            for (size_t i = 0; i < tab.size(); ++i)
-                if (!launched[i] && !k::adam_launch_range(tab.data(), (int)i, (int)i + 1, o->chunks_dev, o->lr, o->beta1, o->beta2,
-                                                          o->eps, o->wd, f1, f2, grad_scale, c->compute))
+            cache.n = nc;
+            cache.sizes = sizes;
+            return true;
+        };
+        auto table_of = [](const std::vector<Item>& items) {
+            std::vector<k::AdamTensor> t;
+            for (auto& it : items) t.push_back(it.rec);
+            return t;
+        };
+        if (!sliced.empty()) {
+            // Sharded update on the communication stream, behind the reduce-scatters that produce its gradients and
+            // behind everything the compute stream has queued so far (the backward GEMMs still read the parameters):
+            // one launch over this rank's slice of every tensor, then the all-gathers of the updated parameters in the
+            // order the next forward needs them.  Each parameter's storage carries an event that its next reader waits
+            // for, so the gathers of the later layers overlap the next forward's first GEMMs.
+            NcclApi* nc = nccl_api();
+            if (!nc || !dp_healthy() || !chunks_for(o->sliced, sliced) || !dp_comm_after_compute(c)) return false;
+            const std::vector<k::AdamTensor> tab = table_of(sliced);
+            if (!k::adam_launch(tab.data(), (int)tab.size(), o->sliced.dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
+                                c->comm))
+                return false;
+            if (!dp_mark_grads(c)) return false;     // the gradient buffers are free for reuse once this kernel has run
+            for (auto& it : sliced) {
+                Storage* ps = it.p->st.get();
+                if (!dp_nccl_ok(nc, nc->AllGather(ps->ptr + it.lo, ps->ptr, it.cnt, ncclFloat32, g_dp.comm, c->comm), "ncclAllGather")) return false;
+                if (it.rec.tf32_out &&
+                    !dp_nccl_ok(nc, nc->AllGather(ps->tf32_copy + it.lo, ps->tf32_copy, it.cnt, ncclFloat32, g_dp.comm, c->comm), "ncclAllGather"))
                     return false;
-        } else {
-            if (!dp_join(c)) return false;
-            if (!k::adam_launch(tab.data(), (int)tab.size(), o->chunks_dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
+                if (ps->ready) { cudaEventDestroy(ps->ready); ps->ready = nullptr; }   // rptr above already waited for it
+                TS_CHECK(cudaEventCreateWithFlags(&ps->ready, cudaEventDisableTiming));
+                TS_CHECK(cudaEventRecord(ps->ready, c->comm));
+                it.st->sharded = true; it.st->lo = it.lo; it.st->cnt = it.cnt;
+            }
+            g_dp.comm_outstanding = true;
+        }
+        if (!whole.empty()) {
+            // Replicated update on the compute stream, one launch for all of these tensors, behind the all-reduces of
+            // their own gradients only (the reduce-scatter of the first layer's weights, enqueued last, is not waited for).
+            if (!chunks_for(o->whole, whole)) return false;
+            for (auto& it : whole) {
+                if (it.from_dp) TS_CHECK(cudaStreamWaitEvent(c->compute, g_dp.done_event[it.id], 0));
+                if (it.st->sharded && !gather_adam_state(c, *it.st)) return false;   // earlier steps updated a slice only
+            }
+            const std::vector<k::AdamTensor> tab = table_of(whole);
+            if (!k::adam_launch(tab.data(), (int)tab.size(), o->whole.dev, o->lr, o->beta1, o->beta2, o->eps, o->wd, f1, f2, grad_scale,
                                 c->compute))
                 return false;
         }
-        for (auto& s : touched) { s->version++; s->tf32_clean = false; }
+        for (auto* items : {&whole, &sliced})
+            for (auto& it : *items) {
+                Storage* ps = it.p->st.get();
+                it.st->step += 1;
+                ps->version++;
+                ps->tf32_clean = false;
+                if (it.rec.tf32_out) ps->tf32_copy_version = ps->version;
+            }
     }
     if (!skipped.empty()) {
         set_error("adam step: parameter(s) %s have no gradient and were skipped", skipped.c_str());
@@ -2058,6 +2258,8 @@ static ts_tensor* state_view(const ts_adam* o, const ts_tensor* p, int which) {
     if (it == o->states.end()) return nullptr;
     StorageP st = which == 0 ? it->second.m : which == 1 ? it->second.v : it->second.vmax;
     if (!st) return nullptr;
+    // under data parallelism with sharded updates the moments are whole only after a gather (a collective call)
+    if (it->second.sharded && !gather_adam_state(o->c, const_cast<AdamState&>(it->second))) return nullptr;
     auto t = std::make_shared<TensorImpl>(p->t->dims);
     t->st = st;
     return wrap(t);
@@ -2109,15 +2311,25 @@ TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int ran
     return true;
 }
 TS_API void ts_dp_finalize(void) {
-    DeviceCtx* c = ctx();
+    DeviceCtx* c = ctx_if_initialized();
+    if (c && g_dp.comm && !g_dp.failed) {
+        // optimizer moments that are current on their owner's slice only are made whole while the ranks can still talk
+        for (ts_adam* o : g_adams)
+            for (auto& kv : o->states)
+                if (kv.second.sharded) gather_adam_state(c, kv.second);
+    }
     if (c) { cudaStreamSynchronize(c->comm); cudaStreamSynchronize(c->compute); }
     if (g_dp.comm) { if (NcclApi* nc = nccl_api()) nc->CommDestroy(g_dp.comm); g_dp.comm = nullptr; }
-    if (g_dp.ev_compute) { cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); g_dp.ev_compute = g_dp.ev_comm = nullptr; }
+    if (g_dp.ev_compute) {
+        cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); cudaEventDestroy(g_dp.ev_grads);
+        g_dp.ev_compute = g_dp.ev_comm = g_dp.ev_grads = nullptr;
+    }
     for (auto& kv : g_dp.done_event) cudaEventDestroy(kv.second);
     g_dp.done_event.clear();
-    g_dp.pending_order.clear();
+    g_dp.red.clear();
+    g_dp.retired.clear();
     g_dp.params.clear();
-    g_dp.rank = 0; g_dp.world = 1; g_dp.comm_outstanding = false;
+    g_dp.rank = 0; g_dp.world = 1; g_dp.comm_outstanding = g_dp.grads_outstanding = g_dp.failed = false;
 }
 TS_API int ts_dp_world_size(void) { return g_dp.world; }
 TS_API int ts_dp_rank(void) { return g_dp.rank; }

@@ -1,7 +1,9 @@
-"""Data parallelism over the batch: every rank holds all parameters, runs forward and
-backward on its contiguous block of batch rows, and the parameter gradients are summed
-with one NCCL all-reduce per tensor (overlapped with the rest of backward) before Adam
-divides by the world size.  The reference has no multi-device code; this module is the
+"""Data parallelism over the batch: every rank holds all parameters and runs forward and
+backward on its contiguous block of batch rows.  During backward each parameter gradient is
+summed across ranks on a communication stream as soon as it is final: large tensors by a
+reduce-scatter, after which Adam updates only this rank's slice (its moments are sharded) and
+the updated parameters are all-gathered while the next forward starts; small tensors by an
+all-reduce followed by the same update on every rank.  Adam divides by the world size.  The reference has no multi-device code; this module is the
 host side of section 5 of the C ABI.
 
 Rendezvous (who is rank 0, how the NCCL id reaches the others) is the caller's business:
@@ -80,4 +82,5 @@ def shard_weight(n_rows: int, rank_: int, world: int) -> float:
 
 def describe() -> str:
     """One line on how gradients are combined, for benchmark records."""
-    return "NCCL sum of parameter gradients on a communication stream, overlapped with backward; Adam scales by 1/world"
+    return ("NCCL on a communication stream, overlapped with backward: large gradients reduce-scattered, Adam on each rank's "
+            "slice, parameters all-gathered under the next forward; small gradients all-reduced; Adam scales by 1/world")
