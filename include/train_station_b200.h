@@ -73,6 +73,15 @@ const char* ts_last_error(void);
 /* Blocks until `stream` (NULL: the compute stream) is idle, then reports any deferred
  * device-side error (for example a bounded wait inside a kernel that gave up). */
 bool ts_sync_stream(void* stream);
+/* The device word (one int, device memory) in which a kernel records that one of its bounded waits gave up; zero when
+ * all is well.  ts_sync_stream copies it back, reports a non-zero value as an error and clears it.  Exposed so that a
+ * host can poll or clear it with its own copies, and so that a test can exercise the reporting with a plain write. */
+int* ts_device_error_word(void);
+/* Cycle budget of the main-loop waits of the next one-CTA tensor-core GEMM launches (negative: back to the default of
+ * about two seconds).  For tests of the abort path only: with a budget of 0 the first wait that is not already
+ * satisfied gives up, the kernel records an error code (101..104), drains its own copies with the full bound, frees
+ * its tensor memory and returns; nothing faults and the context stays usable.  The two-CTA kernel ignores it. */
+void ts_debug_set_gemm_wait_budget(long long cycles);
 /* The per-device compute stream as a cudaStream_t, for callers that time with events. */
 void* ts_compute_stream(void);
 /* Page-locked host memory for uploads that overlap compute (size in f32 elements). */
@@ -431,6 +440,18 @@ bool ts_adam_set_param_step(ts_adam* opt, const ts_tensor* p, unsigned long long
 /* Rank 0 creates the id; the caller broadcasts the bytes to the other ranks by any means. */
 bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]);
 bool ts_dp_init(const unsigned char id[TS_DP_UNIQUE_ID_BYTES], int rank, int world_size);
+/* ts_dp_init waits at most TS_DP_INIT_TIMEOUT seconds (environment, default 300; 0 = for ever) for the other ranks:
+ * a rank that never joins costs a bounded wait and an error, not a hang. */
+bool ts_dp_init_with_timeout(const unsigned char id[TS_DP_UNIQUE_ID_BYTES], int rank, int world_size, double timeout_seconds);
+/* False once the communicator has reported an asynchronous error (a peer that died, a transport fault).  The
+ * communicator is then aborted, so that no later call can block on it, and every later collective call fails with a
+ * message.  Checked by the library at every collective it enqueues; a host may also poll it between steps. */
+bool ts_dp_healthy(void);
+/* Test hooks for the two above, usable without a GPU: mode 0..3 replaces NCCL by an in-process stand-in that moves no
+ * data (0: every call succeeds, 1: the rendezvous never completes, 2: collectives return an error, 3: an asynchronous
+ * remote error is reported); a negative mode removes it.  ts_dp_fake_nccl_aborts counts the stand-in's aborts. */
+void ts_dp_install_fake_nccl(int mode);
+int ts_dp_fake_nccl_aborts(void);
 void ts_dp_finalize(void);
 int ts_dp_world_size(void);   /* 1 when not initialised */
 int ts_dp_rank(void);

@@ -77,6 +77,43 @@ def test_two_cta_kernel_exact_on_small_integers(gpu, ora, m, n, k):
     assert np.array_equal(got3, exact), "3xTF32 on integers"
 
 
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 4096), (784, 1024, 4096), (200, 136, 2080), (128, 128, 16384), (256, 384, 2048)])
+@pytest.mark.parametrize("ta,tb", [(1, 0), (0, 0), (0, 1)])
+def test_split_k_products_are_exact_on_small_integers(gpu, m, n, k, ta, tb):
+    """Few output tiles and a long K: the tensor-core kernel splits K over otherwise idle SMs and a second kernel adds
+    the partial products.  On small integers every partial sum is exact, so any slip in the split ranges (a k-block
+    counted twice or dropped, a ragged last split, a wrong slab) shows as a wrong integer.  3xTF32 takes the same route."""
+    rng = np.random.default_rng(m + n + k + ta * 2 + tb)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    a_st = np.ascontiguousarray(a.T) if ta else a
+    b_st = np.ascontiguousarray(b.T) if tb else b
+    for precision in (1, 2):
+        got = _run(gpu, a_st, b_st, m, n, k, ta, tb, precision=precision)
+        assert np.array_equal(got, exact), (precision, int((got != exact).sum()))
+
+
+def test_split_k_products_on_real_data(gpu):
+    rng = np.random.default_rng(77)
+    m, n, k = 1024, 1024, 4096
+    a, b = rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((k, n), dtype=np.float32)
+    _check(_run(gpu, np.ascontiguousarray(a.T), b, m, n, k, 1, 0), a, b)
+    # the [1024 x 10] weight gradient of a 10-class output layer over a batch of 4096: not a tensor-core shape (row
+    # pitch of 40 bytes); in the TF32 modes the FP32 kernel splits K as a batched launch.  FP32-level accuracy.
+    m, n, k = 1024, 10, 4096
+    a, b = rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((k, n), dtype=np.float32)
+    a_st = np.ascontiguousarray(a.T)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    mag = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    for precision in (1, 2):
+        got = _run(gpu, a_st, b, m, n, k, 1, 0, precision=precision)
+        assert np.all(np.abs(got - exact) <= 2e-6 * mag), precision
+    # FP32 mode keeps the single chain over K, bit for bit the reference's order: split results may differ from it in the last bits
+    chain = _run(gpu, a_st, b, m, n, k, 1, 0, precision=0)
+    assert np.all(np.abs(chain - exact) <= 4e-6 * mag)
+
+
 def test_tf32_gemm_epilogues(gpu, ora):
     rng = np.random.default_rng(5)
     m, n, k = 300, 384, 200

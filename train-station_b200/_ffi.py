@@ -44,6 +44,8 @@ SIGNATURES = {
     "ts_last_error": (C.c_char_p, []),
     "ts_sync_stream": (C.c_bool, [vp]),
     "ts_compute_stream": (vp, []),
+    "ts_device_error_word": (vp, []),
+    "ts_debug_set_gemm_wait_budget": (None, [C.c_longlong]),
     "ts_host_alloc_pinned": (vp, [u64]),
     "ts_host_free_pinned": (None, [vp]),
     "ts_memcpy_async": (C.c_bool, [vp, vp, u64, C.c_int, vp]),
@@ -175,6 +177,10 @@ SIGNATURES = {
     # 5. data parallelism
     "ts_dp_get_unique_id": (C.c_bool, [C.c_char_p]),
     "ts_dp_init": (C.c_bool, [C.c_char_p, C.c_int, C.c_int]),
+    "ts_dp_init_with_timeout": (C.c_bool, [C.c_char_p, C.c_int, C.c_int, C.c_double]),
+    "ts_dp_healthy": (C.c_bool, []),
+    "ts_dp_install_fake_nccl": (None, [C.c_int]),
+    "ts_dp_fake_nccl_aborts": (C.c_int, []),
     "ts_dp_finalize": (None, []),
     "ts_dp_world_size": (C.c_int, []),
     "ts_dp_rank": (C.c_int, []),

@@ -110,6 +110,8 @@ bool mul_bwd(const float* a, const float* b, const float* go, float* ga, float* 
 bool div_bwd(const float* a, const float* b, const float* go, float* ga, float* gb, size_t n, cudaStream_t s);
 bool scale(const float* x, float alpha, float* o, size_t n, cudaStream_t s);
 bool fill(float* o, float v, size_t n, cudaStream_t s);
+// out[i] = part[i] + part[n + i] + ... + part[(slabs - 1) * n + i], added in that order (split-K partial products)
+bool sum_slabs(const float* part, float* out, size_t n, size_t slabs, cudaStream_t s);
 bool fill_from_scalar(float* o, const float* scalar, float scale, size_t n, cudaStream_t s);
 bool sqdiff(const float* a, const float* b, float* o, size_t n, cudaStream_t s);   // (a - b)^2, both steps rounded
 // gi = (scale * (*upstream)) * (2 * x): ReduceMean / ReduceSum backward followed by PowScalar(2) backward.

@@ -455,6 +455,46 @@ bool scale(const float* x, float alpha, float* o, size_t n, cudaStream_t s) {
     return launch_ew(Ptrs<1, 1>{{x}, {o}}, n, ScaleF{alpha}, s);
 }
 bool fill(float* o, float v, size_t n, cudaStream_t s) { return launch_ew(Ptrs<0, 1>{{nullptr}, {o}}, n, FillF{v}, s); }
+
+namespace {
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) sum_slabs_kernel(const float* __restrict__ part, float* __restrict__ out, size_t n, int slabs) {
+    const size_t step = (size_t)gridDim.x * kThreads;
+    if (VEC) {
+        const size_t nv = n / 4;
+        for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < nv; i += step) {
+            float4 acc = __ldcs(reinterpret_cast<const float4*>(part) + i);
+            for (int s = 1; s < slabs; ++s) {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(part + (size_t)s * n) + i);
+                acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+            }
+            reinterpret_cast<float4*>(out)[i] = acc;
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += step) {
+            float acc = part[i];
+            for (int s = 1; s < slabs; ++s) acc = __fadd_rn(acc, part[(size_t)s * n + i]);
+            out[i] = acc;
+        }
+    }
+}
+}  // namespace
+
+bool sum_slabs(const float* part, float* out, size_t n, size_t slabs, cudaStream_t s) {
+    if (n == 0) return true;
+    if (!part || !out || slabs == 0) { set_error("sum_slabs: bad arguments"); return false; }
+    DeviceCtx* c = ctx();
+    if (!c) return false;
+    ProfScope prof(kProfElementwise, s, 4.0 * (double)n * (double)(slabs + 1));
+    const bool vec = n % 4 == 0 && aligned16(part) && aligned16(out);
+    const size_t work = vec ? n / 4 : n;
+    size_t grid = (work + kThreads - 1) / kThreads;
+    const size_t cap = (size_t)c->sm_count * 8;
+    if (grid > cap) grid = cap;
+    if (vec) sum_slabs_kernel<true><<<(unsigned)grid, kThreads, 0, s>>>(part, out, n, (int)slabs);
+    else sum_slabs_kernel<false><<<(unsigned)grid, kThreads, 0, s>>>(part, out, n, (int)slabs);
+    return cuda_ok(cudaGetLastError(), "sum_slabs launch");
+}
 bool fill_from_scalar(float* o, const float* scalar, float sc, size_t n, cudaStream_t s) {
     if (!scalar) { set_error("fill_from_scalar: null scalar"); return false; }
     return launch_ew(Ptrs<0, 1>{{nullptr}, {o}}, n, FillFromScalarF{scalar, sc}, s);

@@ -20,7 +20,10 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cmath>
+#include <condition_variable>
+#include <thread>
 #include <cstring>
 #include <ctime>
 #include <memory>
@@ -307,6 +310,32 @@ struct NcclApi {
 };
 static NcclApi g_nccl;
 static std::mutex g_nccl_mu;
+// ---- an in-process stand-in for NCCL, for host-side tests of the failure handling (no GPU, no second process).
+// It moves no data.  mode 0: every call succeeds; 1: ncclCommInitRank never returns (a peer that never joins);
+// 2: the collectives return an error; 3: ncclCommGetAsyncError reports a remote error (a peer that died).
+static std::atomic<int> g_fake_mode{0}, g_fake_aborts{0};
+static ncclResult_t fake_get_unique_id(ncclUniqueId* id) { memset(id, 0x5a, sizeof(*id)); return ncclSuccess; }
+static ncclResult_t fake_comm_init_rank(ncclComm_t* comm, int, ncclUniqueId, int) {
+    if (g_fake_mode.load() == 1) {
+        std::mutex m;
+        std::condition_variable never;
+        std::unique_lock<std::mutex> lk(m);
+        never.wait(lk, [] { return false; });
+    }
+    *comm = reinterpret_cast<ncclComm_t>(uintptr_t(0x1));
+    return ncclSuccess;
+}
+static ncclResult_t fake_collective() { return g_fake_mode.load() == 2 ? ncclInternalError : ncclSuccess; }
+static ncclResult_t fake_all_reduce(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) { return fake_collective(); }
+static ncclResult_t fake_reduce_scatter(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) { return fake_collective(); }
+static ncclResult_t fake_all_gather(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) { return fake_collective(); }
+static ncclResult_t fake_async_error(ncclComm_t, ncclResult_t* out) { *out = g_fake_mode.load() == 3 ? ncclRemoteError : ncclSuccess; return ncclSuccess; }
+static ncclResult_t fake_abort(ncclComm_t) { g_fake_aborts.fetch_add(1); return ncclSuccess; }
+static ncclResult_t fake_destroy(ncclComm_t) { return ncclSuccess; }
+static const char* fake_error_string(ncclResult_t r) {
+    return r == ncclSuccess ? "no error" : r == ncclRemoteError ? "remote process exited or there was a network error" : "internal error";
+}
+
 static NcclApi* nccl_api() {
     NcclApi& api = g_nccl;
     std::lock_guard<std::mutex> lk(g_nccl_mu);
@@ -2295,21 +2324,75 @@ TS_API bool ts_dp_get_unique_id(unsigned char id_out[TS_DP_UNIQUE_ID_BYTES]) {
     memcpy(id_out, &id, sizeof(id));
     return true;
 }
-TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int rank, int world) {
-    DeviceCtx* c = ctx();
-    if (!c) return false;
-    if (!id_in || world < 1 || rank < 0 || rank >= world) { set_error("ts_dp_init: bad arguments (rank %d, world %d)", rank, world); return false; }
-    if (g_dp.comm) { set_error("ts_dp_init: already initialised on this thread"); return false; }
-    g_dp.rank = rank; g_dp.world = world;
-    if (world == 1) return true;
+// ncclCommInitRank blocks until every rank has called it.  It runs on a helper thread so that a rank that never joins
+// costs a bounded wait and an error instead of a hang; a helper that is still blocked when the wait runs out is left
+// behind (there is no communicator yet to abort) and cleans up after itself should it ever return.
+struct InitState {
+    std::mutex mu;
+    std::condition_variable cv;
+    bool done = false, abandoned = false;
+    ncclResult_t result = ncclSuccess;
+    ncclComm_t comm = nullptr;
+};
+TS_API bool ts_dp_init_with_timeout(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int rank, int world, double timeout_seconds) {
     NcclApi* nc = nccl_api();
     if (!nc) return false;
+    DeviceCtx* c = nc->fake ? nullptr : ctx();
+    if (!nc->fake && !c) return false;
+    if (!id_in || world < 1 || rank < 0 || rank >= world) { set_error("ts_dp_init: bad arguments (rank %d, world %d)", rank, world); return false; }
+    if (g_dp.comm) { set_error("ts_dp_init: already initialised on this thread"); return false; }
+    g_dp.rank = rank; g_dp.world = world; g_dp.failed = false;
+    if (world == 1) return true;
     ncclUniqueId id;
     memcpy(&id, id_in, sizeof(id));
-    ncclResult_t r = nc->CommInitRank(&g_dp.comm, world, id, rank);
-    if (r != ncclSuccess) { g_dp.comm = nullptr; set_error("ncclCommInitRank failed: %s", nc->GetErrorString(r)); return false; }
+    auto st = std::make_shared<InitState>();
+    const int device = c ? c->device : -1;
+    std::thread([st, nc, id, rank, world, device] {
+        if (device >= 0) cudaSetDevice(device);
+        ncclComm_t comm = nullptr;
+        ncclResult_t r = nc->CommInitRank(&comm, world, id, rank);
+        std::lock_guard<std::mutex> lk(st->mu);
+        if (st->abandoned) { if (r == ncclSuccess && comm) nc->CommAbort(comm); return; }
+        st->result = r; st->comm = comm; st->done = true;
+        st->cv.notify_all();
+    }).detach();
+    std::unique_lock<std::mutex> lk(st->mu);
+    const bool in_time = timeout_seconds <= 0 ? (st->cv.wait(lk, [&] { return st->done; }), true)
+                                              : st->cv.wait_for(lk, std::chrono::duration<double>(timeout_seconds), [&] { return st->done; });
+    if (!in_time) {
+        st->abandoned = true;
+        g_dp.rank = 0; g_dp.world = 1;
+        set_error("ts_dp_init: the rendezvous of %d ranks did not complete within %.1f s (rank %d waited; a rank never joined)", world,
+                  timeout_seconds, rank);
+        return false;
+    }
+    if (st->result != ncclSuccess) {
+        g_dp.rank = 0; g_dp.world = 1;
+        set_error("ncclCommInitRank failed: %s", nc->GetErrorString(st->result));
+        return false;
+    }
+    g_dp.comm = st->comm;
     return true;
 }
+TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int rank, int world) {
+    double t = 300.0;   // TS_DP_INIT_TIMEOUT (seconds; 0 = wait for ever)
+    if (const char* e = getenv("TS_DP_INIT_TIMEOUT")) t = atof(e);
+    return ts_dp_init_with_timeout(id_in, rank, world, t);
+}
+// True while the communicator reports no asynchronous error.  On an error (a peer that died, a transport fault) the
+// communicator is aborted, so that nothing can block on it any more, and this and every later collective call fail.
+TS_API bool ts_dp_healthy(void) { return dp_healthy(); }
+// Test hook: replaces NCCL by an in-process stand-in that moves no data (see the modes above); mode < 0 removes it.
+TS_API void ts_dp_install_fake_nccl(int mode) {
+    std::lock_guard<std::mutex> lk(g_nccl_mu);
+    if (mode < 0) { g_nccl = NcclApi(); return; }
+    g_fake_mode.store(mode);
+    g_nccl.GetUniqueId = fake_get_unique_id; g_nccl.CommInitRank = fake_comm_init_rank; g_nccl.AllReduce = fake_all_reduce;
+    g_nccl.ReduceScatter = fake_reduce_scatter; g_nccl.AllGather = fake_all_gather; g_nccl.CommGetAsyncError = fake_async_error;
+    g_nccl.CommAbort = fake_abort; g_nccl.CommDestroy = fake_destroy; g_nccl.GetErrorString = fake_error_string;
+    g_nccl.ok = g_nccl.fake = true;
+}
+TS_API int ts_dp_fake_nccl_aborts(void) { return g_fake_aborts.load(); }
 TS_API void ts_dp_finalize(void) {
     DeviceCtx* c = ctx_if_initialized();
     if (c && g_dp.comm && !g_dp.failed) {

@@ -24,6 +24,8 @@
 // No TMA load in this file uses cluster multicast: each CTA fetches its own tiles.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "../../include/train_station_b200.h"
 #include "common.h"
 
@@ -38,6 +40,7 @@ constexpr int UMMA_K = 8;        // K of one tcgen05.mma.kind::tf32
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;
 constexpr long long kWaitCycles = 4000000000ll;   // about two seconds at 1.9 GHz
+std::atomic<long long> g_wait_budget{kWaitCycles};  // host side: what the next one-CTA launch gets as its main-loop budget
 
 enum ErrCode { kErrFullWait = 101, kErrEmptyWait = 102, kErrAccFullWait = 103, kErrAccEmptyWait = 104, kErrDrain = 105 };
 
@@ -64,16 +67,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when it gave up or when another thread of the CTA already had.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait.  Returns false when it gave up or when another thread of the CTA already had.  `budget` is in clock
+// cycles; the abort flag and the clock are looked at on the first failed poll and then every 256 polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long budget = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t it = 0;; ++it) {
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+            if (clock64() - t0 >= budget) { *abort_flag = 1; return false; }
         }
+        if (mbar_try_wait(bar, parity)) return true;
     }
 }
 
@@ -175,6 +179,13 @@ struct KernelArgs {
     int passes;                 // 1 = TF32, 3 = 3xTF32 (hi/lo split operands)
     uint32_t m, n, k;
     int* error_flag;
+    // Split along K (one-CTA kernel only): work item = (tile, split); split s covers k-blocks
+    // [s * kb_per_split, min((s + 1) * kb_per_split, num_kb)) and writes its partial product to c + s * m * n.
+    uint32_t splits, kb_per_split;
+    // Cycle budget of the main-loop waits of the one-CTA kernel (the drains before a CTA retires always keep the full
+    // bound, so that no bulk copy is in flight when it does).  Normally kWaitCycles; a host test shortens it to see
+    // the abort path run: error word set, tensor memory freed, kernel returns, context usable.
+    long long wait_budget;
 };
 
 __device__ __forceinline__ float rn_tf32(float x) {
@@ -205,9 +216,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (args.k + BK - 1) / BK;
+    // Work items: every tile once per K split, split-major so that the items running together share their panels.
+    const uint32_t num_items = num_tiles * args.splits;
     // 3xTF32: with a = a_hi + a_lo and b = b_hi + b_lo (each part exact in TF32), the accumulator receives
-    // a_lo.b_hi, then a_hi.b_lo, then a_hi.b_hi: three sweeps over K into the same tensor-memory tile.
-    const uint32_t total_kb = num_kb * (uint32_t)args.passes;
+    // a_lo.b_hi, then a_hi.b_lo, then a_hi.b_hi: three sweeps over the item's k-blocks into the same tensor-memory tile.
+    auto item_kb = [&](uint32_t item, uint32_t& kb_begin, uint32_t& kb_cnt) {
+        kb_begin = (item / num_tiles) * args.kb_per_split;
+        const uint32_t left = num_kb - kb_begin;
+        kb_cnt = left < args.kb_per_split ? left : args.kb_per_split;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -244,15 +261,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int armed_parity[C::kStages];
 #pragma unroll
             for (int s = 0; s < C::kStages; ++s) armed_parity[s] = -1;
-            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                uint32_t tm, tn;
-                tile_coords(tile, tm, tn);
+            for (uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                uint32_t tm, tn, kb_begin, kb_cnt;
+                tile_coords(item % num_tiles, tm, tn);
+                item_kb(item, kb_begin, kb_cnt);
+                const uint32_t total_kb = kb_cnt * (uint32_t)args.passes;
                 const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
                 for (uint32_t vkb = 0; vkb < total_kb; ++vkb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); ok = false; break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.wait_budget)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); ok = false; break; }
                     const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
-                    const uint32_t pass = vkb / num_kb;
-                    const int k0 = (int)((vkb - pass * num_kb) * BK);
+                    const uint32_t pass = vkb / kb_cnt;
+                    const int k0 = (int)((kb_begin + vkb - pass * kb_cnt) * BK);
                     const CUtensorMap* pa = (args.passes == 3 && pass == 0) ? &tm_a_lo : &tm_a;
                     const CUtensorMap* pb = (args.passes == 3 && pass == 1) ? &tm_b_lo : &tm_b;
                     mbar_expect_tx(full_bar(stage), C::kStageBytes);
@@ -305,13 +324,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t idesc = make_idesc(A_MN, B_MN, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++it) {
+                uint32_t kb_begin, kb_cnt;
+                item_kb(item, kb_begin, kb_cnt);
+                const uint32_t total_kb = kb_cnt * (uint32_t)args.passes;
                 const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
-                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, args.wait_budget)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < total_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrFullWait); ok = false; break; }
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.wait_budget)) { atomicCAS(args.error_flag, 0, kErrFullWait); ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * C::kStageBytes, sb = sa + C::kABytes;
 #pragma unroll
@@ -345,15 +367,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const uint32_t lane_group = (uint32_t)(warp & 3);
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        for (uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++it) {
             uint32_t tm, tn;
-            tile_coords(tile, tm, tn);
+            tile_coords(item % num_tiles, tm, tn);
             const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
-            if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccFullWait); ok = false; break; }
+            if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, args.wait_budget)) { atomicCAS(args.error_flag, 0, kErrAccFullWait); ok = false; break; }
             tc_fence_after();
             const uint32_t row = tm * BM + lane_group * 32 + lane;
             const bool row_ok = row < args.m;
-            float* crow = args.c + (size_t)row * args.n;
+            float* crow = args.c + (size_t)(item / num_tiles) * args.m * args.n + (size_t)row * args.n;
             const float* mrow = args.mask ? args.mask + (size_t)row * args.n : nullptr;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
@@ -740,7 +762,7 @@ bool make_map_grouped(CUtensorMap* tm, const float* ptr, size_t rows, size_t col
 }
 
 template <int BN, bool A_MN, bool B_MN>
-bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits = 1, uint32_t kb_per_split = 0) {
     using Cf = Cfg<BN>;
     CUtensorMap tm_a, tm_b, tm_a_lo, tm_b_lo;
     // the grouped description is an optimisation: if the driver refuses it, the per-box maps still work
@@ -770,10 +792,11 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
         TS_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes));
         attr_set[c->device] = true;
     }
-    size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN);
+    size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN) * splits;
     int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
+    if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load()};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
@@ -812,7 +835,7 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     size_t pairs = (size_t)c->sm_count / 2;
     int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
@@ -824,6 +847,13 @@ bool launch_tc2_any(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     return b_mn ? launch_tc2<false, true>(g, c, s) : launch_tc2<false, false>(g, c, s);
 }
 
+// TS_GEMM_SPLITK=0 turns the K split off (for A/B measurements).
+bool split_k_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TS_GEMM_SPLITK"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v == 1;
+}
+
 // TS_GEMM_2CTA=0 keeps every GEMM on the one-CTA kernel (for A/B measurements).
 bool two_cta_enabled() {
     static int v = -1;
@@ -832,10 +862,10 @@ bool two_cta_enabled() {
 }
 
 template <int BN>
-bool launch_tc_bn(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+bool launch_tc_bn(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits = 1, uint32_t kb_per_split = 0) {
     const bool a_mn = g.trans_a, b_mn = !g.trans_b;
-    if (a_mn) return b_mn ? launch_tc<BN, true, true>(g, c, s) : launch_tc<BN, true, false>(g, c, s);
-    return b_mn ? launch_tc<BN, false, true>(g, c, s) : launch_tc<BN, false, false>(g, c, s);
+    if (a_mn) return b_mn ? launch_tc<BN, true, true>(g, c, s, splits, kb_per_split) : launch_tc<BN, true, false>(g, c, s, splits, kb_per_split);
+    return b_mn ? launch_tc<BN, false, true>(g, c, s, splits, kb_per_split) : launch_tc<BN, false, false>(g, c, s, splits, kb_per_split);
 }
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -875,13 +905,60 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
     size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
     if (two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)c->sm_count / 2) return launch_tc2_any(g, c, s);
     size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
-    if (g.n <= 128 || tiles256 < (size_t)c->sm_count) return launch_tc_bn<128>(g, c, s);
+    if (g.n <= 128 || tiles256 < (size_t)c->sm_count) {
+        // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
+        // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split: every (tile, split) pair is a
+        // work item of the same launch, the partial products land side by side in scratch and a second kernel adds them
+        // in split order, so the result does not depend on scheduling.  FP32 mode never comes here (its order is fixed).
+        const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
+        const size_t num_kb = (g.k + BK - 1) / BK;
+        if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && tiles128 * 2 <= (size_t)c->sm_count && num_kb >= 64 && split_k_enabled()) {
+            size_t splits = (size_t)c->sm_count / tiles128;
+            if (splits > num_kb / 32) splits = num_kb / 32;          // at least 1024 elements of K per split
+            if (splits > 16) splits = 16;
+            if (splits >= 2) {
+                const size_t kbps = (num_kb + splits - 1) / splits;
+                splits = (num_kb + kbps - 1) / kbps;                 // no empty split
+                const size_t mn = g.m * g.n;
+                float* part = c->alloc.alloc(splits * mn * sizeof(float));
+                if (!part) return false;
+                GemmArgs h = g;
+                h.c = part;
+                bool ok = launch_tc_bn<128>(h, c, s, (uint32_t)splits, (uint32_t)kbps) && sum_slabs(part, g.c, mn, splits, s);
+                if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
+                c->alloc.free(part);
+                return ok;
+            }
+        }
+        return launch_tc_bn<128>(g, c, s);
+    }
     return launch_tc_bn<256>(g, c, s);
 }
 
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
     if (precision < 0) precision = matmul_precision();
     if (precision >= 1 && gemm_tc_supported(g)) return gemm_tc(g, precision == 2, c, s);
+    // A shape the tensor-core kernel cannot take, in a mode that promises no summation order: when the result is small
+    // and K long (C4's [1024 x 10] weight gradient over K = 4096: 32 CTAs each walking the whole chain), K is split
+    // into equal parts that run as one batched launch of the FP32 kernel and are then added in split order.  This works
+    // on offsets alone when both operands are stored K-outermost (op(A) = A^T, op(B) = B: the weight-gradient layout).
+    if (precision >= 1 && g.trans_a && !g.trans_b && !g.bias && !g.relu && !g.mask && g.batch == 1 && g.k >= 2048 && c && split_k_enabled()) {
+        const size_t tiles32 = ((g.m + 31) / 32) * ((g.n + 31) / 32);
+        size_t splits = 0;
+        for (size_t cand = 32; cand >= 2; cand /= 2)
+            if (g.k % cand == 0 && g.k / cand >= 128 && tiles32 * cand <= (size_t)c->sm_count * 8) { splits = cand; break; }
+        if (splits >= 2 && tiles32 <= (size_t)c->sm_count) {
+            const size_t mn = g.m * g.n, ks = g.k / splits;
+            float* part = c->alloc.alloc(splits * mn * sizeof(float));
+            if (!part) return false;
+            GemmArgs h = g;
+            h.c = part; h.k = ks; h.batch = splits; h.batch_stride_a = ks * g.m; h.batch_stride_b = ks * g.n;
+            bool ok = sgemm(h, s) && sum_slabs(part, g.c, mn, splits, s);
+            if (s != c->compute) cudaStreamSynchronize(s);
+            c->alloc.free(part);
+            return ok;
+        }
+    }
     return sgemm(g, s);
 }
 
@@ -901,6 +978,10 @@ TS_API bool launch_gemm_kernel(const float* a, const float* b, float* cc, unsign
     if (m && n && (!cc || (kk && (!a || !b)))) { set_error("launch_gemm_kernel: null pointer"); return false; }
     k::GemmArgs g{a, b, cc, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0, bias, relu != 0, mask};
     return k::gemm(g, precision, c, s);
+}
+
+TS_API void ts_debug_set_gemm_wait_budget(long long cycles) {
+    k::g_wait_budget.store(cycles < 0 ? k::kWaitCycles : cycles);
 }
 
 TS_API bool launch_matmul_kernel(const float* a, const float* b, float* result, unsigned long long m, unsigned long long n,

@@ -380,6 +380,11 @@ TS_API bool ts_sync_stream(void* stream) {
     return true;
 }
 
+TS_API int* ts_device_error_word(void) {
+    DeviceCtx* c = ctx();
+    return c ? c->error_flag : nullptr;
+}
+
 TS_API float* ts_host_alloc_pinned(unsigned long long size) {
     if (!ctx()) return nullptr;
     void* p = nullptr;

@@ -487,7 +487,10 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
     DeviceCtx* c = ctx();
     const size_t sgy = (g.m + SM_T - 1) / SM_T;
     const size_t mgx = (g.n + MD_T - 1) / MD_T, mgy = (g.m + MD_T - 1) / MD_T;
-    if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && mgx * mgy * g.batch >= (size_t)c->sm_count / 2 && mgy <= 65535) {
+    // A result at most 32 columns wide (the 10-class output layer and its weight gradient) would be mostly padding in
+    // 128- or 64-wide tiles, however many of them there are: it goes straight to the 32- and 16-wide tilings below.
+    const bool narrow = g.n <= (size_t)SM_T;
+    if (!narrow && c && gx * gy * g.batch < (size_t)c->sm_count / 2 && mgx * mgy * g.batch >= (size_t)c->sm_count / 2 && mgy <= 65535) {
         // too few 128 x 128 tiles to occupy the GPU, enough 64 x 64 ones
         dim3 mgrid((unsigned)mgx, (unsigned)mgy, (unsigned)g.batch);
         if (g.trans_a) { if (g.trans_b) launch_mid<true, true>(g, mgrid, s); else launch_mid<true, false>(g, mgrid, s); }
@@ -504,7 +507,7 @@ bool sgemm(const GemmArgs& g, cudaStream_t s) {
         else { if (g.trans_b) launch_tiny<false, true>(g, tgrid, s); else launch_tiny<false, false>(g, tgrid, s); }
         return cuda_ok(cudaGetLastError(), "sgemm (16 x 16 tiles) launch");
     }
-    if (c && gx * gy * g.batch < (size_t)c->sm_count / 2 && sgy <= 65535) {
+    if (c && (narrow || gx * gy * g.batch < (size_t)c->sm_count / 2) && sgy <= 65535) {
         // too few even of those: 32 x 32 tiles, sixteen times as many CTAs as 128 x 128 ones
         dim3 sgrid((unsigned)((g.n + SM_T - 1) / SM_T), (unsigned)sgy, (unsigned)g.batch);
         if (g.trans_a) { if (g.trans_b) launch_small<true, true>(g, sgrid, s); else launch_small<true, false>(g, sgrid, s); }

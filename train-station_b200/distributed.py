@@ -27,10 +27,41 @@ def get_unique_id() -> bytes:
     return buf.raw
 
 
-def init(unique_id: bytes, rank: int, world_size: int) -> None:
+def init(unique_id: bytes, rank: int, world_size: int, timeout: float | None = None) -> None:
+    """Joins the communicator.  Blocks until every rank has called it, but at most `timeout` seconds (default: the
+    TS_DP_INIT_TIMEOUT environment variable, else 300): a rank that never joins raises instead of hanging the others."""
     assert len(unique_id) == UNIQUE_ID_BYTES
-    check(_ffi.lib().ts_dp_init(C.create_string_buffer(unique_id, UNIQUE_ID_BYTES), int(rank), int(world_size)),
-          "ts_dp_init")
+    buf = C.create_string_buffer(unique_id, UNIQUE_ID_BYTES)
+    if timeout is None:
+        check(_ffi.lib().ts_dp_init(buf, int(rank), int(world_size)), "ts_dp_init")
+    else:
+        check(_ffi.lib().ts_dp_init_with_timeout(buf, int(rank), int(world_size), float(timeout)), "ts_dp_init")
+
+
+def healthy() -> bool:
+    """False once NCCL has reported an asynchronous error (a peer that died, a transport fault); the communicator has
+    then been aborted and every later collective call fails with a message instead of blocking."""
+    return bool(_ffi.lib().ts_dp_healthy())
+
+
+def exchange_id_through_file(path: str, rank: int, timeout: float = 60.0) -> bytes:
+    """The simplest rendezvous: rank 0 creates the NCCL id and publishes it at `path` (written under another name and
+    renamed, so a reader never sees half a file); the other ranks wait for the file, at most `timeout` seconds."""
+    import os
+    import time
+    if rank == 0:
+        uid = get_unique_id()
+        with open(path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(path + ".tmp", path)
+        return uid
+    t0 = time.monotonic()
+    while not os.path.exists(path):
+        if time.monotonic() - t0 > timeout:
+            raise TimeoutError(f"rank 0 did not publish the NCCL id at {path} within {timeout:g} s")
+        time.sleep(0.02)
+    with open(path, "rb") as f:
+        return f.read()
 
 
 def init_from_torch_distributed() -> Tuple[int, int]:
