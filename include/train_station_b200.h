@@ -287,6 +287,13 @@ bool launch_relu_backward_colsum_kernel(const float* ref, const float* grad_out,
 bool launch_gemm_kernel(const float* a, const float* b, float* c, unsigned long long m,
                         unsigned long long n, unsigned long long k, int trans_a, int trans_b,
                         const float* bias, int relu, const float* mask, int precision, void* stream);
+/* launch_gemm_kernel that also writes colsum_out[j] = sum_i C[i,j] of the stored result (after bias / ReLU / mask): the
+ * bias gradient (reductions/sum.rs:225-306 on the pre-activation gradient, grad_fn/ops/add.rs:14-20) without reading
+ * the result back.  The tensor-core kernels produce per-32-row partial sums in their epilogue and a second small
+ * kernel adds them in row order (deterministic); the FP32 kernel is followed by the ordinary column sum. */
+bool launch_gemm_colsum_kernel(const float* a, const float* b, float* c, unsigned long long m, unsigned long long n,
+                               unsigned long long k, int trans_a, int trans_b, const float* bias, int relu,
+                               const float* mask, int precision, float* colsum_out, void* stream);
 
 /* Fused multi-tensor Adam (optimizers/adam/mod.rs:485-556, 635-1030): one launch updates
  * every tensor.  f1 = 1/bias_correction1, f2 = 1/bias_correction2 as computed on the host
@@ -334,6 +341,9 @@ unsigned long long ts_tensor_id(const ts_tensor* t);
 int ts_tensor_rank(const ts_tensor* t);
 unsigned long long ts_tensor_size(const ts_tensor* t);
 bool ts_tensor_dims(const ts_tensor* t, unsigned long long* dims_out);
+/* False for a transposed / permuted view (ts_tensor_transpose, ts_tensor_permute), which shares its source's storage:
+ * tensor/transform/transpose.rs:181-184.  ts_tensor_contiguous makes the copy. */
+bool ts_tensor_is_contiguous(const ts_tensor* t);
 bool ts_tensor_requires_grad(const ts_tensor* t);
 bool ts_tensor_set_requires_grad(ts_tensor* t, bool requires_grad); /* with_requires_grad */
 /* Device pointer of the tensor's data (forces any deferred kernel to run). */

@@ -86,7 +86,7 @@ def test_split_k_products_are_exact_on_small_integers(gpu, m, n, k, ta, tb):
     rng = np.random.default_rng(m + n + k + ta * 2 + tb)
     a = rng.integers(-3, 4, (m, k)).astype(np.float32)
     b = rng.integers(-3, 4, (k, n)).astype(np.float32)
-    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    exact = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)      # integers far below 2^53: exact
     a_st = np.ascontiguousarray(a.T) if ta else a
     b_st = np.ascontiguousarray(b.T) if tb else b
     for precision in (1, 2):
@@ -112,6 +112,29 @@ def test_split_k_products_on_real_data(gpu):
     # FP32 mode keeps the single chain over K, bit for bit the reference's order: split results may differ from it in the last bits
     chain = _run(gpu, a_st, b, m, n, k, 1, 0, precision=0)
     assert np.all(np.abs(chain - exact) <= 4e-6 * mag)
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 384, 200), (128, 128, 64), (4096, 4096, 96), (2308, 8196, 132), (1000, 264, 520), (33, 36, 40)])
+def test_column_sums_from_the_gemm_epilogue_are_exact_on_small_integers(gpu, m, n, k):
+    """The bias gradient from the epilogue of the GEMM that produces the pre-activation gradient: per-warp partial sums
+    (32 rows each) by a transposing butterfly, then a second kernel.  One-CTA and two-CTA kernels, edge tiles, with the
+    ReLU mask applied first, in TF32 and 3xTF32 mode; the FP32 mode falls back to the ordinary column sum."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    mask = rng.standard_normal((m, n), dtype=np.float32)
+    exact = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)      # integers far below 2^53: exact
+    lib = gpu._ffi.lib()
+    da, db, dm = DevBuf(gpu, a), DevBuf(gpu, b), DevBuf(gpu, mask)
+    for precision in (1, 2, 0):
+        for with_mask in (False, True):
+            dc, ds = DevBuf(gpu, n=m * n), DevBuf(gpu, -np.ones(n, np.float32))
+            gpu._ffi.check(lib.launch_gemm_colsum_kernel(da.ptr, db.ptr, dc.ptr, m, n, k, 0, 0, None, 0, dm.ptr if with_mask else None,
+                                                         precision, ds.ptr, None), "gemm + column sums")
+            gpu.synchronize()
+            want = np.where(mask > 0, exact, 0.0).astype(np.float32) if with_mask else exact
+            assert np.array_equal(dc.get().reshape(m, n), want), (precision, with_mask)
+            assert np.array_equal(ds.get(), want.sum(axis=0, dtype=np.float64).astype(np.float32)), (precision, with_mask)
 
 
 def test_tf32_gemm_epilogues(gpu, ora):

@@ -162,3 +162,32 @@ def test_adam_fields_round_trip(S):
     assert d["config"]["learning_rate"] == pytest.approx(1e-3) and d["insertion_order"] == [41, 17]
     # in the binary form a state's tensors are JSON-object fields (tag 14), as core/impls.rs:416-427 makes them
     assert b"\x0e" + struct.pack("<I", len(S.fields_to_json(S.tensor_fields(states[17]["m"], [4], False)))) in S.fields_to_binary(fields)
+
+
+def test_literals_the_reference_own_tests_hold(S):
+    """What the reference's serialization unit tests write out literally, replayed through this codec: the only
+    reference-held vectors there are for the format (no file written by the reference can be produced here).
+    JSON field text: serialization/json/structs.rs:457-472 (every scalar kind this codec writes) and :487-490 (string
+    escapes); compact object text: serialization/json/formatter.rs:336.  Binary primitives: an empty string is four zero
+    bytes and an absent optional one zero byte (binary/reader.rs:741-750), the magic number's first byte on disk is
+    0x42 (binary/header.rs:493, little endian) and the header is 24 bytes (binary/header.rs:519-523)."""
+    text = S.fields_to_json([("bool_field", S.fv_bool(True)), ("usize_field", S.fv_usize(42)), ("f32_field", S.fv_f32(np.float32(np.pi))),
+                             ("string_field", S.fv_string("Hello, World!")), ("json_field", S.fv_string('{"nested": "value"}'))])
+    for want in ('"bool_field":true', '"usize_field":42', '"f32_field":3.1415927', '"string_field":"Hello, World!"',
+                 '"json_field":"{\\"nested\\": \\"value\\"}"'):
+        assert want in text, want
+    text = S.fields_to_json([("quotes", S.fv_string('Hello "World"')), ("newlines", S.fv_string("Line1\nLine2")),
+                             ("tabs", S.fv_string("Tab\there")), ("backslashes", S.fv_string("Path\\to\\file"))])
+    for want in ('"quotes":"Hello \\"World\\""', '"newlines":"Line1\\nLine2"', '"tabs":"Tab\\there"', '"backslashes":"Path\\\\to\\\\file"'):
+        assert want in text, want
+    assert S.fields_to_json([("name", S.fv_string("test")), ("value", S.fv_usize(42))]) == '{"name":"test","value":42}'
+    # and read back to the same values
+    back = S.json_to_fields(text)
+    assert back["quotes"] == 'Hello "World"' and back["newlines"] == "Line1\nLine2" and back["backslashes"] == "Path\\to\\file"
+    # binary primitives
+    blob = S.fields_to_binary([("s", S.fv_string("")), ("o", S.fv_optional(None))])
+    assert len(blob) - 24 == struct.unpack("<Q", blob[12:20])[0] and blob[:4] == bytes([0x42, 0x5F, 0x53, 0x54])
+    body = blob[24:]
+    assert body == struct.pack("<Q", 2) + s_("s") + b"\x0c" + b"\x00\x00\x00\x00" + s_("o") + b"\x11" + b"\x00"
+    got = S.binary_to_fields(blob)
+    assert got["s"] == "" and got["o"] is None

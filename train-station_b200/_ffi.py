@@ -96,6 +96,7 @@ SIGNATURES = {
     "launch_colsum_kernel_static_scratch": (C.c_bool, [vp, vp, u64, u64, vp]),
     "launch_relu_backward_colsum_kernel": (C.c_bool, [vp, vp, vp, vp, u64, u64, vp, vp]),
     "launch_gemm_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, C.c_int, C.c_int, vp, C.c_int, vp, C.c_int, vp]),
+    "launch_gemm_colsum_kernel": (C.c_bool, [vp, vp, vp, u64, u64, u64, C.c_int, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp]),
     "launch_adam_multi_tensor_kernel": (C.c_bool, [C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u64p,
                                                    C.c_int, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float,
                                                    C.c_float, C.c_float, C.c_float, vp]),
@@ -116,6 +117,7 @@ SIGNATURES = {
     "ts_tensor_size": (u64, [vp]),
     "ts_tensor_dims": (C.c_bool, [vp, u64p]),
     "ts_tensor_requires_grad": (C.c_bool, [vp]),
+    "ts_tensor_is_contiguous": (C.c_bool, [vp]),
     "ts_tensor_set_requires_grad": (C.c_bool, [vp, C.c_bool]),
     "ts_tensor_data_ptr": (vp, [vp]),
     "ts_tensor_to_host": (C.c_bool, [vp, vp]),

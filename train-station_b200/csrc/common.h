@@ -140,6 +140,8 @@ bool sum(const float* x, float* out, size_t n, bool mean, float* scratch, cudaSt
 bool mse_loss(const float* y, const float* t, float* out, size_t n, float* scratch, cudaStream_t s);
 size_t colsum_scratch_elems(size_t rows, size_t cols);
 bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s);
+// out[j] = partial[0][j] + partial[1][j] + ... in that order: the second stage of a column sum on its own
+bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial_rows, cudaStream_t s);
 bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols,
                      float* scratch, cudaStream_t s);
 
@@ -174,6 +176,10 @@ struct GemmArgs {
     // 3xTF32: when both are set, a and b hold the TF32-exact high parts and these the low parts
     const float* a_lo = nullptr;
     const float* b_lo = nullptr;
+    // When set ([n], device): also receives the column sums of the stored result (after bias / ReLU / mask / rounding):
+    // from the tensor-core kernels' epilogue, or by a separate pass after an FP32-kernel product.
+    float* colsum_out = nullptr;
+    float* colsum_partial = nullptr;   // internal: the epilogue's per-32-row partial sums
     // FP32 kernel only: `batch` independent products in one launch (grid z); entry z reads a + z * batch_stride_a and
     // b + z * batch_stride_b (a stride of 0 repeats the operand) and writes c + z * m * n.  No bias / mask with batch > 1.
     size_t batch = 1, batch_stride_a = 0, batch_stride_b = 0;

@@ -69,6 +69,7 @@ struct PendingGemm {
     size_t m = 0, n = 0, k = 0;
     TensorP bias, mask;
     bool relu = false;
+    TensorP colsum;   // when set ([n]): receives the column sums of the result (a bias gradient), from the GEMM's epilogue
 };
 
 // An elementwise result that has been requested but not launched, so that the MSE spelling
@@ -93,6 +94,16 @@ struct TensorImpl {
     std::unique_ptr<PendingGemm> pending;
     std::unique_ptr<PendingEw> pending_ew;
     bool requires_grad = false;
+    // A transposed / permuted VIEW, as transpose() / t() / permute() return in the reference (transform/transpose.rs:181-184,
+    // core/allocation.rs:220-237): it shares `st` with the tensor it was taken from, and its axis i is axis view_perm[i] of
+    // the contiguous tensor of shape base_dims that st holds.  A write to either is seen through the other.  Empty
+    // view_perm: an ordinary contiguous tensor.  `contig` caches the elements in the view's own order for consumers that
+    // need them so (everything but a 2-D GEMM operand, which just flips its transposition flag); it is remade when
+    // the shared storage's version moves on.
+    std::vector<int> view_perm;
+    std::vector<size_t> base_dims;
+    StorageP contig;
+    uint64_t contig_version = 0;
     explicit TensorImpl(const std::vector<size_t>& d) : id(g_next_id.fetch_add(1)), dims(d) {
         for (size_t x : d) size *= x;
     }
@@ -123,7 +134,11 @@ static TensorP new_tensor(DeviceCtx* c, const std::vector<size_t>& dims) {
 // the deferred GEMM may store its result already rounded to TF32.
 static bool materialize(const TensorP& t, bool for_gemm = false);
 
-// Device pointer for reading on the compute stream (launches a deferred GEMM, waits for an upload).
+static bool is_view(const TensorP& t) { return !t->view_perm.empty(); }
+static bool view_refresh(const TensorP& t);
+
+// Device pointer for reading on the compute stream (launches a deferred GEMM, waits for an upload).  For a view:
+// the pointer to its elements in its own order (a cached permuted copy of the shared storage).
 static const float* rptr(const TensorP& t, bool for_gemm = false) {
     if (!materialize(t, for_gemm)) return nullptr;
     Storage* s = t->st.get();
@@ -132,14 +147,18 @@ static const float* rptr(const TensorP& t, bool for_gemm = false) {
         cudaEventDestroy(s->ready);
         s->ready = nullptr;
     }
+    if (is_view(t)) return view_refresh(t) ? t->contig->ptr : nullptr;
     return s->ptr;
 }
+// The storage that holds t's elements in t's own (logical, row-major) order: its own for an ordinary tensor, the
+// cached permuted copy for a view.  Call after rptr(t).
+static Storage* logical_storage(const TensorP& t) { return is_view(t) ? t->contig.get() : t->st.get(); }
 
 // The operand as the TF32 tensor core should see it: the data itself when it is already exactly
 // representable in TF32, otherwise a rounded-to-nearest copy cached beside it (refreshed when the
 // data's version changes; the forward and the two backward GEMMs of a layer share it).
 static const float* tf32_operand(DeviceCtx* c, const TensorP& t) {
-    Storage* s = t->st.get();
+    Storage* s = logical_storage(t);
     if (s->tf32_clean) return s->ptr;
     if (s->tf32_copy && s->tf32_copy_version == s->version) return s->tf32_copy;
     if (!s->tf32_copy) {
@@ -153,7 +172,7 @@ static const float* tf32_operand(DeviceCtx* c, const TensorP& t) {
 
 // 3xTF32 mode: the operand as a TF32-exact high part plus a TF32-exact low part, cached like the copy above.
 static bool tf32_split_operand(DeviceCtx* c, const TensorP& t, const float** hi, const float** lo) {
-    Storage* s = t->st.get();
+    Storage* s = logical_storage(t);
     const bool fresh = s->tf32_copy && s->tf32_lo && s->tf32_copy_version == s->version && s->tf32_lo_version == s->version;
     if (!fresh) {
         const size_t bytes = (s->n ? s->n : 1) * sizeof(float);
@@ -165,6 +184,38 @@ static bool tf32_split_operand(DeviceCtx* c, const TensorP& t, const float** hi,
     *hi = s->tf32_copy;
     *lo = s->tf32_lo;
     return true;
+}
+
+// (Re)makes a view's permuted copy when the shared storage has changed since it was made.  A copy that somebody else
+// holds by now (reshape of a view shares it) is left alone and a new one is made.
+static bool view_refresh(const TensorP& t) {
+    Storage* base = t->st.get();
+    if (t->contig && t->contig_version == base->version) return true;
+    if (!t->contig || t->contig.use_count() > 1) {
+        t->contig = new_storage(base->c, t->size);
+        if (!t->contig) return false;
+    }
+    if (t->size && !k::permute(base->ptr, t->contig->ptr, t->base_dims.data(), t->view_perm.data(), (int)t->view_perm.size(), base->c->compute))
+        return false;
+    t->contig->version++;
+    t->contig->tf32_clean = false;
+    t->contig_version = base->version;
+    return true;
+}
+// The contiguous tensor a view was taken from, as an operand: same storage, the storage's own shape.
+static TensorP view_base(const TensorP& t) {
+    auto b = std::make_shared<TensorImpl>(t->base_dims);
+    b->st = t->st;
+    return b;
+}
+// op(t) for a 2-D GEMM: a transposed view of a contiguous matrix is that matrix with the transposition flag flipped,
+// so x.t().matmul(w) and the w.t() of a backward cost no copy (the reference materialises them, matmul/mod.rs:586-595).
+static TensorP gemm_operand(const TensorP& t, bool* trans) {
+    if (t->view_perm.size() == 2 && t->view_perm[0] == 1 && t->view_perm[1] == 0 && t->st) {
+        *trans = !*trans;
+        return view_base(t);
+    }
+    return t;
 }
 
 static bool materialize(const TensorP& t, bool for_gemm) {
@@ -200,6 +251,7 @@ static bool materialize(const TensorP& t, bool for_gemm) {
     StorageP st = new_storage(c, t->size);
     if (!st) return false;
     k::GemmArgs g{a, b, st->ptr, p.m, p.n, p.k, p.ta, p.tb, bias, p.relu, mask};
+    if (p.colsum) g.colsum_out = p.colsum->st->ptr;
     if (matmul_precision() == 1 && k::gemm_tc_supported(g)) {
         g.a = tf32_operand(c, p.a);
         g.b = tf32_operand(c, p.b);
@@ -600,7 +652,12 @@ static TensorP reshaped_alias(const TensorP& t, const std::vector<size_t>& dims)
     if (t->dims == dims) return t;
     if (!materialize(t)) return nullptr;
     auto r = std::make_shared<TensorImpl>(dims);
-    r->st = t->st;
+    if (is_view(t)) {   // the elements in the view's order live in its permuted copy
+        if (!rptr(t)) return nullptr;
+        r->st = t->contig;
+    } else {
+        r->st = t->st;
+    }
     return r;
 }
 
@@ -701,7 +758,7 @@ static bool batched_gemm(DeviceCtx* c, const TensorP& ta, const std::vector<size
 // were 1 in the operand are summed with keepdim.
 static TensorP reduce_to_shape(DeviceCtx* c, const TensorP& g, const std::vector<size_t>& want) {
     if (g->dims == want) return g;
-    if (!materialize(g)) return nullptr;
+    if (!rptr(g)) return nullptr;
     if (g->size == 0) {                          // nothing to sum: zeros of the wanted shape
         TensorP z = new_tensor(c, want);
         if (z && z->size && !k::fill(z->st->ptr, 0.0f, z->size, c->compute)) return nullptr;
@@ -712,7 +769,7 @@ static TensorP reduce_to_shape(DeviceCtx* c, const TensorP& g, const std::vector
         TensorP o = new_tensor(c, od);
         float* scratch = o ? c->alloc.alloc(k::reduce_dims_scratch_elems() * sizeof(float)) : nullptr;
         if (!scratch) return nullptr;
-        bool ok = k::reduce_dims(0, cur->st->ptr, nullptr, o->st->ptr, cur->dims.data(), (int)cur->dims.size(), red.data(), scratch, c->compute);
+        bool ok = k::reduce_dims(0, rptr(cur), nullptr, o->st->ptr, cur->dims.data(), (int)cur->dims.size(), red.data(), scratch, c->compute);
         c->alloc.free(scratch);
         return ok ? o : nullptr;
     };
@@ -765,6 +822,18 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
                 // two backward GEMMs: let a deferred GEMM that produces it store TF32-rounded values.
                 auto other_prod = g_graph.ops.find(nd.inputs[1 - i]);
                 const bool feeds_gemm = other_prod != g_graph.ops.end() && other_prod->second.op == Op::MatMul;
+                if (fusion_enabled() && matmul_precision() != 0 && go->pending && !go->pending->colsum && cols > 1 &&
+                    go->pending->m == rows && go->pending->n == cols) {
+                    // The gradient is itself a deferred GEMM (the input gradient of the next layer, ReLU mask folded in):
+                    // its epilogue also produces the column sums, so the full-size gradient is not read back for them.
+                    // (The TF32 modes only: the FP32 kernels have no such epilogue and their column sums stay a pass of their own.)
+                    TensorP r = new_tensor(c, od);
+                    if (!r) return false;
+                    go->pending->colsum = r;
+                    if (!rptr(go, feeds_gemm)) return false;
+                    gin[i] = r;
+                    continue;
+                }
                 const float* gp = rptr(go, feeds_gemm);
                 if (!gp) return false;
                 TensorP r = new_tensor(c, od);
@@ -902,15 +971,20 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
             }
             const size_t m = nd.dims0.size() == 2 ? nd.dims0[0] : 1, kk = nd.dims0.back();
             const size_t n = nd.dims1.size() == 2 ? nd.dims1[1] : 1;
+            const bool mats = nd.dims0.size() == 2 && nd.dims1.size() == 2;   // saved transposed views stay flags here too
             if (nd.needs[0]) {
                 auto t = std::make_shared<TensorImpl>(nd.dims0);
-                t->pending.reset(new PendingGemm{go, nd.s1.t, false, true, m, kk, n, nullptr, nullptr, false});
+                bool tb = true;
+                TensorP ob = mats ? gemm_operand(nd.s1.t, &tb) : nd.s1.t;
+                t->pending.reset(new PendingGemm{go, ob, false, tb, m, kk, n, nullptr, nullptr, false});
                 register_pending(t);
                 gin[0] = t;
             }
             if (nd.needs[1]) {
                 auto t = std::make_shared<TensorImpl>(nd.dims1);
-                t->pending.reset(new PendingGemm{nd.s0.t, go, true, false, kk, n, m, nullptr, nullptr, false});
+                bool ta = true;
+                TensorP oa = mats ? gemm_operand(nd.s0.t, &ta) : nd.s0.t;
+                t->pending.reset(new PendingGemm{oa, go, ta, false, kk, n, m, nullptr, nullptr, false});
                 register_pending(t);
                 gin[1] = t;
             }
@@ -1400,6 +1474,7 @@ TS_API bool ts_tensor_dims(const ts_tensor* t, unsigned long long* out) {
     return true;
 }
 TS_API bool ts_tensor_requires_grad(const ts_tensor* t) { return t && t->t->requires_grad; }
+TS_API bool ts_tensor_is_contiguous(const ts_tensor* t) { return t && !is_view(t->t); }
 TS_API bool ts_tensor_set_requires_grad(ts_tensor* t, bool rg) {
     if (!t) { set_error("ts_tensor_set_requires_grad: null tensor"); return false; }
     t->t->requires_grad = rg;
@@ -1419,6 +1494,26 @@ TS_API bool ts_tensor_to_host(ts_tensor* t, float* out) {
 }
 TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
     if (!t || (!host && t->t->size)) { set_error("ts_tensor_copy_from_host: null argument"); return false; }
+    if (is_view(t->t)) {
+        // a write through a view lands in the shared storage: upload in the view's order, then scatter through the inverse permutation
+        const TensorP& v = t->t;
+        if (!materialize(v) || !flush_pending({v->st.get()})) return false;
+        Storage* st = v->st.get();
+        if (st->ready) { cudaStreamWaitEvent(st->c->compute, st->ready, 0); cudaEventDestroy(st->ready); st->ready = nullptr; }
+        const int rank = (int)v->view_perm.size();
+        std::vector<int> inv((size_t)rank);
+        for (int i = 0; i < rank; ++i) inv[v->view_perm[i]] = i;
+        float* tmp = st->c->alloc.alloc((v->size ? v->size : 1) * sizeof(float));
+        if (!tmp) return false;
+        bool ok = cuda_ok(cudaMemcpyAsync(tmp, host, v->size * sizeof(float), cudaMemcpyHostToDevice, st->c->compute), "upload") &&
+                  (v->size == 0 || k::permute(tmp, st->ptr, v->dims.data(), inv.data(), rank, st->c->compute)) &&
+                  cuda_ok(cudaStreamSynchronize(st->c->compute), "upload sync");
+        st->c->alloc.free(tmp);
+        if (!ok) return false;
+        st->version++;
+        st->tf32_clean = false;
+        return true;
+    }
     if (!rptr(t->t) || !flush_pending({t->t->st.get()})) return false;
     Storage* st = t->t->st.get();
     TS_CHECK(cudaMemcpyAsync(st->ptr, host, t->t->size * sizeof(float), cudaMemcpyHostToDevice, st->c->compute));
@@ -1429,7 +1524,8 @@ TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
 }
 TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
     if (!t) { set_error("ts_tensor_fill: null tensor"); return false; }
-    if (!rptr(t->t) || !flush_pending({t->t->st.get()})) return false;
+    // (a view covers every element of the storage it shares exactly once, so filling it fills the storage)
+    if (!rptr(is_view(t->t) ? view_base(t->t) : t->t) || !flush_pending({t->t->st.get()})) return false;
     Storage* st = t->t->st.get();
     if (!k::fill(st->ptr, v, t->t->size, st->c->compute)) return false;
     st->version++;
@@ -1551,7 +1647,9 @@ TS_API ts_tensor* ts_tensor_matmul(ts_tensor* ha, ts_tensor* hb) {
     if (ra == 2) od.push_back(m);
     if (rb == 2) od.push_back(n);   // 1-D . 1-D gives a rank-0 tensor with one element (matmul/mod.rs:88-98)
     auto out = std::make_shared<TensorImpl>(od);
-    out->pending.reset(new PendingGemm{a, b, false, false, m, n, ka, nullptr, nullptr, false});
+    bool ta = false, tb = false;
+    TensorP oa = ra == 2 ? gemm_operand(a, &ta) : a, ob = rb == 2 ? gemm_operand(b, &tb) : b;   // transposed views: flags, not copies
+    out->pending.reset(new PendingGemm{oa, ob, ta, tb, m, n, ka, nullptr, nullptr, false});
     if (fusion_enabled()) register_pending(out);
     else if (!materialize(out)) return nullptr;
     if (grad_on() && (a->requires_grad || b->requires_grad)) {
@@ -1701,7 +1799,12 @@ TS_API ts_tensor* ts_tensor_reshape(ts_tensor* hx, const long long* new_shape, i
     if (n != x->size) { set_error("Cannot reshape tensor of size %zu to a shape of size %zu", x->size, n); return nullptr; }   // reshape.rs:142-150
     if (!materialize(x)) return nullptr;
     auto out = std::make_shared<TensorImpl>(dims);
-    out->st = x->st;
+    if (is_view(x)) {   // reshape.rs: a non-contiguous tensor is made contiguous first, so the result does not alias it
+        if (!rptr(x)) return nullptr;
+        out->st = x->contig;
+    } else {
+        out->st = x->st;
+    }
     if (x->requires_grad) {
         Node nd;
         nd.op = Op::Reshape;
@@ -1713,15 +1816,27 @@ TS_API ts_tensor* ts_tensor_reshape(ts_tensor* hx, const long long* new_shape, i
     return wrap(out);
 }
 
+// transpose / t / permute (transform/transpose.rs:156-207, permute.rs): a view that shares the storage.  Nothing is
+// launched; whoever needs the elements in the new order gets a permuted copy then (see TensorImpl::contig), and a 2-D
+// GEMM operand needs none at all.
 static ts_tensor* permute_op(const TensorP& x, const std::vector<int>& perm) {
     DeviceCtx* c = ctx();
     if (!c) return nullptr;
     const int rank = (int)perm.size();
     std::vector<size_t> od((size_t)rank);
     for (int i = 0; i < rank; ++i) od[i] = x->dims[perm[i]];
-    const float* px = rptr(x);
-    TensorP out = px ? new_tensor(c, od) : nullptr;
-    if (!out || !k::permute(px, out->st->ptr, x->dims.data(), perm.data(), rank, c->compute)) return nullptr;
+    if (!materialize(x)) return nullptr;
+    auto out = std::make_shared<TensorImpl>(od);
+    out->st = x->st;
+    // relative to the contiguous tensor the storage holds: a view of a view composes the permutations
+    std::vector<int> composed((size_t)rank);
+    for (int i = 0; i < rank; ++i) composed[i] = is_view(x) ? x->view_perm[perm[i]] : perm[i];
+    bool identity = true;
+    for (int i = 0; i < rank; ++i) identity = identity && composed[i] == i;
+    if (!identity) {
+        out->view_perm = composed;
+        out->base_dims = is_view(x) ? x->base_dims : x->dims;
+    }
     if (x->requires_grad) {
         Node nd;
         nd.op = Op::Permute;
@@ -1793,9 +1908,17 @@ TS_API ts_tensor* ts_tensor_contiguous(ts_tensor* hx) {
     if (!c) return nullptr;
     TensorP x = hx->t;
     const float* px = rptr(x);
-    TensorP out = px ? new_tensor(c, x->dims) : nullptr;
-    if (!out) return nullptr;
-    if (x->size && !cuda_ok(cudaMemcpyAsync(out->st->ptr, px, x->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "contiguous")) return nullptr;
+    TensorP out;
+    if (px && is_view(x)) {
+        // contiguous.rs:138-160: the one copy a view costs; the view gives its permuted copy away and makes another if asked again
+        out = std::make_shared<TensorImpl>(x->dims);
+        out->st = x->contig;
+        x->contig.reset();
+    } else {
+        out = px ? new_tensor(c, x->dims) : nullptr;
+        if (!out) return nullptr;
+        if (x->size && !cuda_ok(cudaMemcpyAsync(out->st->ptr, px, x->size * sizeof(float), cudaMemcpyDeviceToDevice, c->compute), "contiguous")) return nullptr;
+    }
     if (x->requires_grad) {
         Node nd;
         nd.op = Op::Reshape;   // the gradient passes through unchanged (GradFn::Contiguous)
@@ -2147,6 +2270,7 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         }
         TensorP g = grad_lookup(p->id);
         if (g && g->size != p->size) { set_error("adam step: gradient and parameter sizes differ for %llu", (unsigned long long)p->id); return false; }
+        if (is_view(p)) { set_error("adam step: parameter %llu is a transposed view; optimise the tensor it was taken from", (unsigned long long)p->id); return false; }
     }
     struct Item { TensorP p; AdamState* st; k::AdamTensor rec; bool from_dp = false, sliced = false; size_t lo = 0, cnt = 0; uint64_t id = 0; };
     std::vector<Item> whole, sliced;

@@ -158,6 +158,23 @@ __host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
            ((uint32_t)(BM >> 4) << 24);
 }
 
+// Column sums over the 32 rows a warp holds (one row per lane, 32 columns per lane in v): a transposing butterfly.
+// Round `off` splits the columns a lane still holds in two halves, keeps the half its bit `off` selects and adds the
+// partner's values for that half, so after five rounds lane j holds the sum of column j.  31 shuffles, fixed order.
+__device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < off; ++i) {
+            const float send = upper ? v[i] : v[i + off];
+            const float keep = upper ? v[i + off] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    return v[0];
+}
+
 template <int BN>
 struct Cfg {
     static constexpr int kStages = BN == 256 ? 4 : 6;
@@ -186,6 +203,11 @@ struct KernelArgs {
     // bound, so that no bulk copy is in flight when it does).  Normally kWaitCycles; a host test shortens it to see
     // the abort path run: error word set, tensor memory freed, kernel returns, context usable.
     long long wait_budget;
+    // When set: column sums of the stored result (the bias gradient of the layer this result is the pre-activation
+    // gradient of).  Row r of `colsum_partial` ([ceil(m / 32)][n], rounded up to whole tiles) receives the sums over rows
+    // 32 r .. 32 r + 31; every element is written by exactly one warp, with no synchronisation between warps, and a
+    // second kernel adds the rows in order.
+    float* colsum_partial;
 };
 
 __device__ __forceinline__ float rn_tf32(float x) {
@@ -194,6 +216,34 @@ __device__ __forceinline__ float rn_tf32(float x) {
     return __uint_as_float(r);
 }
 
+// one 32-column chunk of one output row: bias, ReLU, mask, rounding, store; the stored values are left in vals[]
+// (zero for a row or a column outside the matrix) for the column sums
+__device__ __forceinline__ void store_chunk(const KernelArgs& args, const uint32_t (&r)[32], float (&vals)[32], bool row_ok, float* crow,
+                                            const float* mrow, uint32_t col0) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const uint32_t col = col0 + q * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row_ok && col < args.n) {   // n % 4 == 0: a float4 is either fully inside or fully outside
+            v = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                            __uint_as_float(r[q * 4 + 3]));
+            if (args.bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+            }
+            if (args.relu) {
+                v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f; v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
+            }
+            if (mrow) {
+                const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
+                v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
+            }
+            if (args.round_out) { v.x = rn_tf32(v.x); v.y = rn_tf32(v.y); v.z = rn_tf32(v.z); v.w = rn_tf32(v.w); }
+            *reinterpret_cast<float4*>(crow + col) = v;
+        }
+        vals[q * 4] = v.x; vals[q * 4 + 1] = v.y; vals[q * 4 + 2] = v.z; vals[q * 4 + 3] = v.w;
+    }
+}
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -380,31 +430,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
                 uint32_t r[32];
+                float vals[32];
                 tmem_ld32(tmem_base + ((lane_group * 32u) << 16) + acc * BN + ch * 32, r);
                 tmem_ld_wait();
-                const uint32_t col0 = tn * BN + ch * 32;
-                if (row_ok) {
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const uint32_t col = col0 + q * 4;
-                        if (col < args.n) {   // n % 4 == 0: a float4 is either fully inside or fully outside
-                            float4 v = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
-                                                   __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
-                            if (args.bias) {
-                                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
-                                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
-                            }
-                            if (args.relu) {
-                                v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f; v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
-                            }
-                            if (mrow) {
-                                const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
-                                v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
-                            }
-                            if (args.round_out) { v.x = rn_tf32(v.x); v.y = rn_tf32(v.y); v.z = rn_tf32(v.z); v.w = rn_tf32(v.w); }
-                            *reinterpret_cast<float4*>(crow + col) = v;
-                        }
-                    }
+                store_chunk(args, r, vals, row_ok, crow, mrow, tn * BN + ch * 32);
+                if (args.colsum_partial) {
+                    // this warp's 32 rows of these 32 columns: one 128-byte store into the warp's row of the partial sums
+                    const float t = warp_column_sums(vals, lane);
+                    const uint32_t col = tn * BN + ch * 32 + lane;
+                    if (col < args.n) args.colsum_partial[(size_t)(tm * (BM / 32) + lane_group) * args.n + col] = t;
                 }
             }
             tc_fence_before();
@@ -491,31 +525,6 @@ __device__ __forceinline__ void tmem2_dealloc(uint32_t taddr, uint32_t cols) {
 __host__ __device__ constexpr uint32_t make_idesc2(bool a_mn, bool b_mn) {   // M = 256 across the pair, N = 256
     return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(kBN2 >> 3) << 17) |
            ((uint32_t)(256 >> 4) << 24);
-}
-
-// one 32-column chunk of one output row: bias, ReLU, mask, rounding, store
-__device__ __forceinline__ void store_chunk(const KernelArgs& args, const uint32_t (&r)[32], float* crow, const float* mrow, uint32_t col0) {
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        const uint32_t col = col0 + q * 4;
-        if (col < args.n) {
-            float4 v = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
-                                   __uint_as_float(r[q * 4 + 3]));
-            if (args.bias) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
-                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
-            }
-            if (args.relu) {
-                v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f; v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
-            }
-            if (mrow) {
-                const float4 mk = __ldcs(reinterpret_cast<const float4*>(mrow + col));
-                v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f; v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
-            }
-            if (args.round_out) { v.x = rn_tf32(v.x); v.y = rn_tf32(v.y); v.z = rn_tf32(v.z); v.w = rn_tf32(v.w); }
-            *reinterpret_cast<float4*>(crow + col) = v;
-        }
-    }
 }
 
 template <bool A_MN, bool B_MN>
@@ -690,9 +699,15 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll 1
             for (int ch = 0; ch < kBN2 / 32; ++ch) {
                 uint32_t r[32];
+                float vals[32];
                 tmem_ld32(tmem_base + ((lane_group * 32u) << 16) + acc * kBN2 + ch * 32, r);
                 tmem_ld_wait();
-                if (row_ok) store_chunk(args, r, crow, mrow, tn * kBN2 + ch * 32);
+                store_chunk(args, r, vals, row_ok, crow, mrow, tn * kBN2 + ch * 32);
+                if (args.colsum_partial) {
+                    const float t = warp_column_sums(vals, lane);
+                    const uint32_t col = tn * kBN2 + ch * 32 + lane;
+                    if (col < args.n) args.colsum_partial[(size_t)((tm * 2 + rank) * 4 + lane_group) * args.n + col] = t;
+                }
             }
             tc_fence_before();
             mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));   // the leader's MMA thread owns the accumulators' reuse
@@ -796,7 +811,7 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
     int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
     if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load()};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
@@ -835,7 +850,7 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     size_t pairs = (size_t)c->sm_count / 2;
     int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
@@ -903,7 +918,21 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
     if (!split3 && (g.a_lo || g.b_lo)) { set_error("gemm: low parts given without the 3xTF32 mode"); return false; }
     // Large problems: pairs of CTAs on 256 x 256 tiles, as long as every pair gets at least one tile.
     size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
-    if (two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)c->sm_count / 2) return launch_tc2_any(g, c, s);
+    const bool pairs = two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)c->sm_count / 2;
+    if (g.colsum_out && !g.colsum_partial) {
+        // Column sums of the result from the epilogue: one partial row per 32 result rows of every tile the chosen
+        // kernel walks (rows past m contribute zeros), in scratch, then one small launch that adds them in order.
+        const size_t prow = pairs ? ((g.m + 255) / 256) * 8 : ((g.m + BM - 1) / BM) * 4;
+        float* part = c->alloc.alloc(prow * g.n * sizeof(float));
+        if (!part) return false;
+        GemmArgs h = g;
+        h.colsum_partial = part;
+        bool ok = gemm_tc(h, split3, c, s) && colsum_finish(part, g.colsum_out, g.n, prow, s);
+        if (s != c->compute) cudaStreamSynchronize(s);
+        c->alloc.free(part);
+        return ok;
+    }
+    if (pairs) return launch_tc2_any(g, c, s);
     size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
     if (g.n <= 128 || tiles256 < (size_t)c->sm_count) {
         // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
@@ -912,7 +941,7 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
         // in split order, so the result does not depend on scheduling.  FP32 mode never comes here (its order is fixed).
         const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
         const size_t num_kb = (g.k + BK - 1) / BK;
-        if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && tiles128 * 2 <= (size_t)c->sm_count && num_kb >= 64 && split_k_enabled()) {
+        if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && !g.colsum_partial && tiles128 * 2 <= (size_t)c->sm_count && num_kb >= 64 && split_k_enabled()) {
             size_t splits = (size_t)c->sm_count / tiles128;
             if (splits > num_kb / 32) splits = num_kb / 32;          // at least 1024 elements of K per split
             if (splits > 16) splits = 16;
@@ -938,6 +967,17 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
     if (precision < 0) precision = matmul_precision();
     if (precision >= 1 && gemm_tc_supported(g)) return gemm_tc(g, precision == 2, c, s);
+    if (g.colsum_out) {   // the FP32 kernels have no such epilogue: the product first, then the ordinary column sum
+        GemmArgs h = g;
+        h.colsum_out = nullptr;
+        if (!gemm(h, precision, c, s)) return false;
+        float* scratch = c->alloc.alloc(colsum_scratch_elems(g.m, g.n) * sizeof(float));
+        if (!scratch) return false;
+        bool ok = colsum(g.c, g.colsum_out, g.m, g.n, scratch, s);
+        if (s != c->compute) cudaStreamSynchronize(s);
+        c->alloc.free(scratch);
+        return ok;
+    }
     // A shape the tensor-core kernel cannot take, in a mode that promises no summation order: when the result is small
     // and K long (C4's [1024 x 10] weight gradient over K = 4096: 32 CTAs each walking the whole chain), K is split
     // into equal parts that run as one batched launch of the FP32 kernel and are then added in split order.  This works
@@ -977,6 +1017,19 @@ TS_API bool launch_gemm_kernel(const float* a, const float* b, float* cc, unsign
     if (precision < -1 || precision > 2) { set_error("launch_gemm_kernel: precision %d out of range", precision); return false; }
     if (m && n && (!cc || (kk && (!a || !b)))) { set_error("launch_gemm_kernel: null pointer"); return false; }
     k::GemmArgs g{a, b, cc, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0, bias, relu != 0, mask};
+    return k::gemm(g, precision, c, s);
+}
+
+TS_API bool launch_gemm_colsum_kernel(const float* a, const float* b, float* cc, unsigned long long m, unsigned long long n,
+                                      unsigned long long kk, int trans_a, int trans_b, const float* bias, int relu, const float* mask,
+                                      int precision, float* colsum_out, void* stream) {
+    cudaStream_t s = pick_stream(stream);
+    DeviceCtx* c = ctx();
+    if (!s || !c) return false;
+    if (precision < -1 || precision > 2) { set_error("launch_gemm_colsum_kernel: precision %d out of range", precision); return false; }
+    if (m && n && (!cc || !colsum_out || (kk && (!a || !b)))) { set_error("launch_gemm_colsum_kernel: null pointer"); return false; }
+    k::GemmArgs g{a, b, cc, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0, bias, relu != 0, mask};
+    g.colsum_out = colsum_out;
     return k::gemm(g, precision, c, s);
 }
 

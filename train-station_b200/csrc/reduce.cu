@@ -227,6 +227,34 @@ __global__ void __launch_bounds__(kThreads) colsum_stage2(const float* __restric
     out[col] = v;
 }
 
+// Adds the rows of a [rows][cols] matrix of partial sums (thousands of rows when they come from a GEMM epilogue: one per
+// 32 result rows).  One CTA per 32 columns, so that 8192 columns occupy the whole GPU instead of 32 CTAs: lane = column
+// (a warp reads 128 contiguous bytes per row), the 8 warps take rows w, w + 8, ... with four loads in flight, and the 8
+// warp totals are added in warp order.  The order of additions is fixed, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) colsum_rows_kernel(const float* __restrict__ part, float* __restrict__ out, size_t cols, int rows) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const size_t col = (size_t)blockIdx.x * 32 + lane;
+    __shared__ float sm[8][32];
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (col < cols) {
+        int r = w;
+        for (; r + 24 < rows; r += 32) {
+            const float v0 = __ldcs(part + (size_t)r * cols + col), v1 = __ldcs(part + (size_t)(r + 8) * cols + col);
+            const float v2 = __ldcs(part + (size_t)(r + 16) * cols + col), v3 = __ldcs(part + (size_t)(r + 24) * cols + col);
+            a0 += v0; a1 += v1; a2 += v2; a3 += v3;
+        }
+        for (; r < rows; r += 8) a0 += __ldcs(part + (size_t)r * cols + col);
+    }
+    sm[w][lane] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (w == 0 && col < cols) {
+        float t = sm[0][lane];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) t += sm[i][lane];
+        out[col] = t;
+    }
+}
+
 template <bool FUSED>
 bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
     if (cols == 0) return true;
@@ -266,6 +294,13 @@ size_t colsum_scratch_elems(size_t rows, size_t cols) {
 }
 bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
     return colsum_impl<false>(g, nullptr, nullptr, out, rows, cols, scratch, s);
+}
+bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial_rows, cudaStream_t s) {
+    if (cols == 0) return true;
+    if (!partial || !out || partial_rows == 0 || partial_rows > 0x7fffffff) { set_error("colsum_finish: bad arguments"); return false; }
+    ProfScope prof(kProfReduce, s, 4.0 * (double)cols * (double)(partial_rows + 1));
+    colsum_rows_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, out, cols, (int)partial_rows);
+    return cuda_ok(cudaGetLastError(), "colsum_finish launch");
 }
 bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols, float* scratch,
                      cudaStream_t s) {

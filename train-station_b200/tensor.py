@@ -297,8 +297,12 @@ class Tensor:
         dims.insert(dim, 1)
         return self.reshape(dims)
 
+    def is_contiguous(self) -> bool:
+        """False for a transposed / permuted view, which shares its source's storage."""
+        return bool(_ffi.lib().ts_tensor_is_contiguous(self._h))
+
     def transpose(self, dim0: int, dim1: int) -> "Tensor":
-        """transpose.rs:156-200; the permuted copy is contiguous here (the reference returns a strided view)."""
+        """transpose.rs:156-200: a view that shares the storage; contiguous() makes the copy."""
         if dim0 < 0 or dim1 < 0:
             raise TrainStationError("transpose axes are unsigned")
         return Tensor(_ffi.lib().ts_tensor_transpose(self._h, int(dim0), int(dim1)))
@@ -325,9 +329,6 @@ class Tensor:
     def clone(self) -> "Tensor":
         """Clone (tensor/core/mod.rs:344-378): a copy of the values with no gradient history."""
         return Tensor(_ffi.lib().ts_tensor_clone(self._h))
-
-    def is_contiguous(self) -> bool:
-        return True
 
     # joining and splitting (tensor/transform/{cat,stack,split}.rs)
     @staticmethod
