@@ -501,7 +501,7 @@ def run_gpu(args, d: Dist):
             "loss": final_loss, "hidden_nonzero_fraction": alive, "roofline": roof, "other_kernels": other, "e2e": e2e, "gpu_launches": launches,
             "launches_per_step": launches / args.steps, "clocks": clocks, "peak_device_bytes": stats["peak_bytes_in_use"]}
 
-    if d.world > 1:
+    if d.world > 1 and not args.no_dp_check:
         line["dp_check"] = dp_check(ts, d, W, B, params, forward, X, T)
     if d.world == 1 and not args.no_extras:
         extras = {}
@@ -1001,6 +1001,7 @@ def main():
                     help="BASELINE configuration; c5 (default) is the headline data-parallel MLP, the others run on one GPU")
     ap.add_argument("--lr", type=float, default=C5_LR, help="Adam learning rate of the C5 run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dp-check", action="store_true", help="N > 1: skip the replica and gradient checks after the timed steps")
     ap.add_argument("--no-extras", action="store_true", help="C5 only: skip the short runs of the other configurations and the vendor TF32 yardstick")
     args = ap.parse_args()
     if args.micro:

@@ -51,6 +51,7 @@ private:
 struct DeviceCtx {
     int device = -1;
     int sm_count = 0;
+    int sm_reserved = 0;              // SMs the persistent GEMM kernels leave free (for NCCL's CTAs under data parallelism)
     cudaStream_t compute = nullptr;   // every engine kernel runs here
     cudaStream_t copy = nullptr;      // asynchronous uploads
     cudaStream_t comm = nullptr;      // NCCL

@@ -448,6 +448,16 @@ static bool dp_shard_enabled() {
     return v == 1;
 }
 
+// Sharded update in TF32 mode: only the parameters are all-gathered and every rank then rounds its own TF32 copy
+// (default), or the slices' owners also write the rounded copies and those are all-gathered too (TS_DP_GATHER_TF32=1:
+// no rounding pass, but half as much traffic again on NVLink beside the next forward's GEMMs).  Measured on 4 GPUs
+// (C5): 18.8 ms per step against 20.3, because collectives that run beside the persistent GEMM kernels slow those down.
+static bool dp_gather_tf32_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TS_DP_GATHER_TF32"); v = (e && e[0] == '1') ? 1 : 0; }
+    return v == 1;
+}
+
 static bool dp_nccl_ok(NcclApi* nc, ncclResult_t r, const char* what) {
     if (r == ncclSuccess) return true;
     set_error("%s failed: %s", what, nc->GetErrorString(r));
@@ -2297,6 +2307,7 @@ TS_API bool ts_adam_step(ts_adam* o, ts_tensor* const* params, int n, float grad
         // TF32 mode: a parameter that feeds tensor-core GEMMs keeps a copy rounded to TF32 beside it; the update
         // writes that copy too, so the next forward finds it current instead of running a rounding pass
         float* tf = (write_tf32 && p->st->tf32_copy) ? p->st->tf32_copy : nullptr;
+        if (it.sliced && !dp_gather_tf32_enabled()) tf = nullptr;   // the rounded copy is then remade locally after the gather
         const size_t lo = it.lo, cnt = it.sliced ? it.cnt : p->size;
         it.rec = k::AdamTensor{pp + lo, gp + lo, st.m->ptr + lo, st.v->ptr + lo, (unsigned long long)cnt,
                                o->amsgrad ? st.vmax->ptr + lo : nullptr, tf ? tf + lo : nullptr};
@@ -2496,6 +2507,16 @@ TS_API bool ts_dp_init_with_timeout(const unsigned char id_in[TS_DP_UNIQUE_ID_BY
         return false;
     }
     g_dp.comm = st->comm;
+    if (c) {
+        // NCCL's kernels need SMs of their own: the GEMM kernels are persistent, one CTA per SM with all of its shared
+        // memory, so a collective that starts beside one would wait for a whole CTA to retire (or, started first, make
+        // GEMM CTAs queue behind it and stretch that launch by a wave).  TS_DP_RESERVE_SMS SMs are kept out of the GEMM grids.
+        int reserve = 0;
+        if (const char* e = getenv("TS_DP_RESERVE_SMS")) reserve = atoi(e);
+        if (reserve < 0) reserve = 0;
+        if (reserve > c->sm_count / 2) reserve = c->sm_count / 2;
+        c->sm_reserved = reserve & ~1;   // the two-CTA kernel takes SMs in pairs
+    }
     return true;
 }
 TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int rank, int world) {
@@ -2527,6 +2548,7 @@ TS_API void ts_dp_finalize(void) {
     }
     if (c) { cudaStreamSynchronize(c->comm); cudaStreamSynchronize(c->compute); }
     if (g_dp.comm) { if (NcclApi* nc = nccl_api()) nc->CommDestroy(g_dp.comm); g_dp.comm = nullptr; }
+    if (c) c->sm_reserved = 0;
     if (g_dp.ev_compute) {
         cudaEventDestroy(g_dp.ev_compute); cudaEventDestroy(g_dp.ev_comm); cudaEventDestroy(g_dp.ev_grads);
         g_dp.ev_compute = g_dp.ev_comm = g_dp.ev_grads = nullptr;

@@ -808,7 +808,8 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
         attr_set[c->device] = true;
     }
     size_t tiles = ((g.m + BM - 1) / BM) * ((g.n + BN - 1) / BN) * splits;
-    int grid = (int)(tiles < (size_t)c->sm_count ? tiles : (size_t)c->sm_count);
+    const size_t sms = (size_t)(c->sm_count - c->sm_reserved);
+    int grid = (int)(tiles < sms ? tiles : sms);
     if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
                   (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial};
@@ -847,7 +848,7 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
         attr_set[c->device] = true;
     }
     size_t tiles = ((g.m + 255) / 256) * ((g.n + kBN2 - 1) / kBN2);
-    size_t pairs = (size_t)c->sm_count / 2;
+    size_t pairs = (size_t)(c->sm_count - c->sm_reserved) / 2;
     int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
                   (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial};
