@@ -173,3 +173,12 @@ def test_sharded_and_replicated_updates_agree_bit_for_bit(gpu, tmp_path):
     a, b = np.load(da / "rank0_of2.npz"), np.load(db / "rank0_of2.npz")
     for k in a.files:
         assert np.array_equal(a[k], b[k]), k
+    # TF32 mode: every rank rounding its own copies after the gather (default) against gathering the copies the
+    # slices' owners wrote (TS_DP_GATHER_TF32=1): the same values by either route
+    dc, dd = tmp_path / "round_locally", tmp_path / "gather_rounded"
+    dc.mkdir(); dd.mkdir()
+    _run(2, dc, "mlp_tf32")
+    _run(2, dd, "mlp_tf32", {"TS_DP_GATHER_TF32": "1"})
+    a, b = np.load(dc / "rank0_of2.npz"), np.load(dd / "rank0_of2.npz")
+    for k in a.files:
+        assert np.array_equal(a[k], b[k]), k
