@@ -82,6 +82,10 @@ int* ts_device_error_word(void);
  * satisfied gives up, the kernel records an error code (101..104), drains its own copies with the full bound, frees
  * its tensor memory and returns; nothing faults and the context stays usable.  The two-CTA kernel ignores it. */
 void ts_debug_set_gemm_wait_budget(long long cycles);
+/* The two-CTA tensor-core GEMM hands its tiles out from a counter (1, the default) or by a fixed stride per CTA pair (0);
+ * negative: back to the default / the TS_GEMM_DYNAMIC environment variable.  For A/B measurements and for tests that
+ * run both schedules. */
+void ts_debug_set_gemm_dynamic(int enabled);
 /* The per-device compute stream as a cudaStream_t, for callers that time with events. */
 void* ts_compute_stream(void);
 /* Page-locked host memory for uploads that overlap compute (size in f32 elements). */

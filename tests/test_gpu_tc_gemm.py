@@ -59,8 +59,16 @@ def test_tf32_gemm_exact_on_small_integers(gpu):
         assert np.array_equal(got, exact), (ta, tb, int((got != exact).sum()))
 
 
+@pytest.fixture(params=["tiles from a counter", "fixed stride"])
+def tile_schedule(request, gpu):
+    """The two-CTA kernel hands tiles out from a counter by default; the fixed stride per CTA pair stays as a switch."""
+    gpu._ffi.lib().ts_debug_set_gemm_dynamic(1 if request.param == "tiles from a counter" else 0)
+    yield request.param
+    gpu._ffi.lib().ts_debug_set_gemm_dynamic(-1)
+
+
 @pytest.mark.parametrize("m,n,k", [(4096, 4096, 96), (2308, 8196, 132)])
-def test_two_cta_kernel_exact_on_small_integers(gpu, ora, m, n, k):
+def test_two_cta_kernel_exact_on_small_integers(gpu, ora, m, n, k, tile_schedule):
     """Problems with at least 74 tiles of 256 x 256 run on CTA pairs (cta_group::2): every layout, edge tiles, epilogues."""
     rng = np.random.default_rng(m + k)
     a = rng.integers(-4, 5, (m, k)).astype(np.float32)

@@ -46,6 +46,7 @@ SIGNATURES = {
     "ts_compute_stream": (vp, []),
     "ts_device_error_word": (vp, []),
     "ts_debug_set_gemm_wait_budget": (None, [C.c_longlong]),
+    "ts_debug_set_gemm_dynamic": (None, [C.c_int]),
     "ts_host_alloc_pinned": (vp, [u64]),
     "ts_host_free_pinned": (None, [vp]),
     "ts_memcpy_async": (C.c_bool, [vp, vp, u64, C.c_int, vp]),

@@ -57,6 +57,7 @@ struct DeviceCtx {
     cudaStream_t comm = nullptr;      // NCCL
     Allocator alloc;
     float* reduce_scratch = nullptr;  // partial sums of sum()/mean()
+    int* tile_counter = nullptr;      // device word: the next tile of a GEMM whose tiles are handed out dynamically
     int* error_flag = nullptr;        // device word set by kernels whose bounded waits gave up
     int* error_flag_host = nullptr;   // pinned mirror
 };

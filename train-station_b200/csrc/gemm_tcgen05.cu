@@ -208,6 +208,10 @@ struct KernelArgs {
     // 32 r .. 32 r + 31; every element is written by exactly one warp, with no synchronisation between warps, and a
     // second kernel adds the rows in order.
     float* colsum_partial;
+    // Two-CTA kernel: when set, tiles are handed out from this counter (zeroed before the launch) instead of by a fixed
+    // stride: concurrently running pairs then stay on neighbouring tiles (shared panels stay in L2), and a pair that
+    // starts late or runs slowly takes fewer tiles instead of stretching the whole launch.
+    int* tile_counter;
 };
 
 __device__ __forceinline__ float rn_tf32(float x) {
@@ -491,6 +495,32 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Wait whose acquire covers writes made by the other CTA of the pair (a tile index published into this CTA's shared memory).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 >= kWaitCycles) { *abort_flag = 1; return false; }
+        }
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    }
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 // TMA copies whose completion is signalled on an mbarrier that may live in the other CTA of the pair
 __device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y) {
     asm volatile(
@@ -540,8 +570,12 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages2 + a); };
     auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages2 + 2 + a); };
     const uint32_t drain_bar = bar_base + 8u * (2 * kStages2 + 4);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages2 * kStageBytes2 + 8 * (2 * kStages2 + 5));
+    auto tile_full_bar = [&](int t) { return bar_base + 8u * (2 * kStages2 + 5 + t); };     // a tile index has been published (both CTAs)
+    auto tile_empty_bar = [&](int t) { return bar_base + 8u * (2 * kStages2 + 7 + t); };    // ... and read by all ten readers (leader only)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages2 * kStageBytes2 + 8 * (2 * kStages2 + 9));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);               // [2]
+    const bool dynamic = args.tile_counter != nullptr;
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t rank = cluster_ctarank();                 // 0 = leader
@@ -555,6 +589,8 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         for (int s = 0; s < kStages2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 2 * kEpiThreads); }
         mbar_init(drain_bar, 1);
+        // readers of a published tile index: the leader's MMA thread and four epilogue warps, the peer's producer and four epilogue warps
+        for (int t = 0; t < 2; ++t) { mbar_init(tile_full_bar(t), 1); mbar_init(tile_empty_bar(t), 10); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -575,6 +611,32 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         tm = first + r % gsz;
         tn = r / gsz;
     };
+    // Which tile iteration `it` of this pair works on; false when there is none left (or the CTA is aborting).
+    // Static: a fixed stride.  Dynamic: the leader's producer thread draws an index from the global counter and publishes
+    // it, through a two-slot ring guarded by the tile_full / tile_empty barriers, to the nine other readers of the pair.
+    auto publish_tile = [&](uint32_t it, int& tile) -> bool {           // the leader's producer thread only
+        const int sl = (int)(it & 1u);
+        if (!mbar_wait(tile_empty_bar(sl), ((it >> 1) & 1u) ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrEmptyWait); return false; }
+        const int t = atomicAdd(args.tile_counter, 1);
+        tile = t < (int)num_tiles ? t : -1;
+        tile_slot[sl] = tile;
+        st_shared_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(tile_slot + sl)), 1), (uint32_t)tile);
+        mbar_arrive_cluster(map_to_cta(tile_full_bar(sl), 0));          // release: the two stores above are visible to whoever waits
+        mbar_arrive_cluster(map_to_cta(tile_full_bar(sl), 1));
+        return tile >= 0;
+    };
+    auto read_tile = [&](uint32_t it, int& tile) -> bool {              // one thread per reader
+        const int sl = (int)(it & 1u);
+        if (!mbar_wait_cluster(tile_full_bar(sl), (it >> 1) & 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrFullWait); tile = -1; return false; }
+        tile = tile_slot[sl];
+        mbar_arrive_cluster(map_to_cta(tile_empty_bar(sl), 0));
+        return tile >= 0;
+    };
+    auto static_tile = [&](uint32_t it, int& tile) -> bool {
+        const uint32_t t = pair + it * num_pairs;
+        tile = t < num_tiles ? (int)t : -1;
+        return tile >= 0;
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -586,9 +648,11 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             int armed_parity[kStages2];
 #pragma unroll
             for (int s = 0; s < kStages2; ++s) armed_parity[s] = -1;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+            for (uint32_t it = 0; ok; ++it) {
+                int tile;
+                if (!(dynamic ? (rank == 0 ? publish_tile(it, tile) : read_tile(it, tile)) : static_tile(it, tile))) break;
                 uint32_t tm, tn;
-                tile_coords(tile, tm, tn);
+                tile_coords((uint32_t)tile, tm, tn);
                 const int m0 = (int)(tm * 256 + rank * 128);          // this CTA's rows of A
                 const int n0 = (int)(tn * kBN2 + rank * 128);         // this CTA's columns of B
                 for (uint32_t vkb = 0; vkb < total_kb; ++vkb) {
@@ -647,7 +711,9 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             constexpr uint32_t idesc = make_idesc2(A_MN, B_MN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+            for (; ok; ++it) {
+                int tile;
+                if (!(dynamic ? read_tile(it, tile) : static_tile(it, tile))) break;
                 const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
                 if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccEmptyWait); ok = false; break; }
                 tc_fence_after();
@@ -686,9 +752,17 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         const uint32_t lane_group = (uint32_t)(warp & 3);
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        for (; ok; ++it) {
+            int tile = -1;
+            if (dynamic) {
+                if (lane == 0) read_tile(it, tile);          // one reader per warp; the others get the index by shuffle
+                tile = __shfl_sync(0xffffffffu, tile, 0);
+            } else {
+                static_tile(it, tile);
+            }
+            if (tile < 0) break;
             uint32_t tm, tn;
-            tile_coords(tile, tm, tn);
+            tile_coords((uint32_t)tile, tm, tn);
             const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
             if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) { atomicCAS(args.error_flag, 0, kErrAccFullWait); ok = false; break; }
             tc_fence_after();
@@ -812,10 +886,18 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
     int grid = (int)(tiles < sms ? tiles : sms);
     if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
+}
+
+// TS_GEMM_DYNAMIC=0 (or ts_debug_set_gemm_dynamic(0)) goes back to the fixed stride, for A/B measurements and tests.
+std::atomic<int> g_dynamic_tiles{-1};
+bool dynamic_tiles(const DeviceCtx* c) {
+    int v = g_dynamic_tiles.load();
+    if (v < 0) { const char* e = getenv("TS_GEMM_DYNAMIC"); v = (e && e[0] == '0') ? 0 : 1; g_dynamic_tiles.store(v); }
+    return c->tile_counter && v == 1;
 }
 
 // Two-CTA kernel: 256 x 256 tiles, each CTA of the pair loads 128 rows of A and 128 columns of B per stage.
@@ -850,8 +932,15 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     size_t tiles = ((g.m + 255) / 256) * ((g.n + kBN2 - 1) / kBN2);
     size_t pairs = (size_t)(c->sm_count - c->sm_reserved) / 2;
     int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+    // Tiles from a counter instead of a fixed stride.  The CTA pairs then always work on the most recently drawn, i.e.
+    // neighbouring, tiles, whose panels they share in L2; with a fixed stride pairs drift apart over the hundred tiles
+    // each walks and the shared panels fall out of L2 (C5 step, same GPU: 79.6 -> 72.1 ms, at a higher clock under the
+    // same power cap).  And a pair whose SMs a collective's CTAs hold for a while takes fewer tiles instead of
+    // stretching the launch.  The one counter belongs to the compute stream's launches.
+    int* counter = (dynamic_tiles(c) && s == c->compute) ? c->tile_counter : nullptr;
+    if (counter) TS_CHECK(cudaMemsetAsync(counter, 0, sizeof(int), s));
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial, counter};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
@@ -1033,6 +1122,8 @@ TS_API bool launch_gemm_colsum_kernel(const float* a, const float* b, float* cc,
     g.colsum_out = colsum_out;
     return k::gemm(g, precision, c, s);
 }
+
+TS_API void ts_debug_set_gemm_dynamic(int enabled) { k::g_dynamic_tiles.store(enabled < 0 ? -1 : (enabled ? 1 : 0)); }
 
 TS_API void ts_debug_set_gemm_wait_budget(long long cycles) {
     k::g_wait_budget.store(cycles < 0 ? k::kWaitCycles : cycles);

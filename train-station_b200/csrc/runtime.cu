@@ -164,6 +164,7 @@ DeviceCtx* ctx() {
               cuda_ok(cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking), "cudaStreamCreate") &&
               cuda_ok(cudaMalloc(&c->reduce_scratch, k::kReduceScratchElems * sizeof(float)), "cudaMalloc scratch") &&
               cuda_ok(cudaMalloc(&c->error_flag, sizeof(int)), "cudaMalloc flag") &&
+              cuda_ok(cudaMalloc(&c->tile_counter, sizeof(int)), "cudaMalloc counter") &&
               cuda_ok(cudaMemset(c->error_flag, 0, sizeof(int)), "cudaMemset flag") &&
               cuda_ok(cudaMallocHost(&c->error_flag_host, sizeof(int)), "cudaMallocHost flag");
     if (!ok) { delete c; return nullptr; }
