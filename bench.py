@@ -860,7 +860,11 @@ def run_micro(args):
         return
     if name.startswith("gemm"):
         m = nn = k = n or 8192
-        a, b, c = dev(rng.standard_normal((m, k), dtype=np.float32)), dev(rng.standard_normal((k, nn), dtype=np.float32)), empty(m * nn)
+        if args.shape:      # M,N,K of a rectangular case, e.g. the C5 layer products 65536,8192,8192 (nn, nt) and 8192,8192,65536 (tn)
+            m, nn, k = (int(v) for v in args.shape.split(","))
+        block = rng.standard_normal(1 << 24, dtype=np.float32)     # large operands repeat a 2^24-element block of random data
+        fill = lambda count: np.resize(block, count)
+        a, b, c = dev(fill(m * k)), dev(fill(k * nn)), empty(m * nn)
         ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0), "gemm_nn_tf32x3": (0, 0)}[name]
         prec = 0 if name.endswith("fp32") else 2 if name.endswith("x3") else 1
         launch = lambda: chk(lib.launch_gemm_kernel(a, b, c, m, nn, k, ta, tb, None, 0, None, prec, None), name)
@@ -992,6 +996,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, choices=MICRO_CASES, help="time one kernel on a small standalone case")
     ap.add_argument("--micro-size", type=int, default=0)
+    ap.add_argument("--shape", default="", help="--micro gemm_*: M,N,K of a rectangular case")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)

@@ -212,6 +212,8 @@ struct KernelArgs {
     // stride: concurrently running pairs then stay on neighbouring tiles (shared panels stay in L2), and a pair that
     // starts late or runs slowly takes fewer tiles instead of stretching the whole launch.
     int* tile_counter;
+    uint32_t group;        // two-CTA kernel: row tiles that sweep the columns together (tile order)
+    uint32_t l2_hints;     // two-CTA kernel: 0 none; 1 A evict_last + B evict_first; 2 both evict_first; 3 A evict_first + B evict_last
 };
 
 __device__ __forceinline__ float rn_tf32(float x) {
@@ -534,6 +536,24 @@ __device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* tm
         ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+__device__ __forceinline__ uint64_t l2_policy(int kind) {   // 1 evict_first, 2 evict_last
+    uint64_t p;
+    if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    else asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma2_load_2d_hint(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(x), "r"(y), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d_hint(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster, int x, int y, int z, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"(tm), "r"(bar_cluster), "r"(x), "r"(y), "r"(z), "l"(pol)
+        : "memory");
+}
 __device__ __forceinline__ void umma2_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -602,7 +622,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    constexpr uint32_t kGroup = 8;                             // 8 row-tiles of 256 share their B panels in L2
+    const uint32_t kGroup = args.group;                        // row-tiles of 256 that share their B panels in L2 (8 by default)
     auto tile_coords = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
         const uint32_t per_group = kGroup * tiles_n;
         const uint32_t g = tile / per_group, r = tile % per_group;
@@ -645,6 +665,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint64_t pol_a = l2_policy(args.l2_hints == 1 ? 2 : 1), pol_b = l2_policy(args.l2_hints == 3 ? 2 : 1);
             int armed_parity[kStages2];
 #pragma unroll
             for (int s = 0; s < kStages2; ++s) armed_parity[s] = -1;
@@ -664,6 +685,22 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     const CUtensorMap* pb = (args.passes == 3 && pass == 1) ? &tm_b_lo : &tm_b;
                     const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kStageBytes2);   // the bytes of both CTAs
+                    if (args.l2_hints) {
+                        if (A_MN) {
+                            if (args.a_grouped) tma2_load_3d_hint(sa, pa, lead_full, 0, k0, m0 / 32, pol_a);
+                            else {
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) tma2_load_2d_hint(sa + b * 4096, pa, lead_full, m0 + 32 * b, k0, pol_a);
+                            }
+                        } else tma2_load_2d_hint(sa, pa, lead_full, k0, m0, pol_a);
+                        if (B_MN) {
+                            if (args.b_grouped) tma2_load_3d_hint(sb, pb, lead_full, 0, k0, n0 / 32, pol_b);
+                            else {
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) tma2_load_2d_hint(sb + b * 4096, pb, lead_full, n0 + 32 * b, k0, pol_b);
+                            }
+                        } else tma2_load_2d_hint(sb, pb, lead_full, k0, n0, pol_b);
+                    } else {
                     if (A_MN) {
                         if (args.a_grouped) {
                             tma2_load_3d(sa, pa, lead_full, 0, k0, m0 / 32);
@@ -683,6 +720,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         }
                     } else {
                         tma2_load_2d(sb, pb, lead_full, k0, n0);
+                    }
                     }
 #pragma unroll
                     for (int s = 0; s < kStages2; ++s)
@@ -818,6 +856,13 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
+int env_int(const char* name, int dflt, int lo, int hi);
+CUtensorMapL2promotion l2_promotion() {
+    const int v = env_int("TS_GEMM_L2_PROMOTION", 256, 0, 256);
+    return v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+         : v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
+
 // 2-D row-major f32 matrix [rows][cols]; box = box_cols (inner) x box_rows.
 bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows, bool mn_major) {
     EncodeTiledFn enc = get_encode();
@@ -828,7 +873,7 @@ bool make_map(CUtensorMap* tm, const float* ptr, size_t rows, size_t cols, uint3
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     l2_promotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("gemm: cuTensorMapEncodeTiled failed with code %d (rows %zu cols %zu box %u x %u)", (int)r, rows, cols, box_cols, box_rows); return false; }
     return true;
 }
@@ -845,7 +890,7 @@ bool make_map_grouped(CUtensorMap* tm, const float* ptr, size_t rows, size_t col
     cuuint32_t box[3] = {32, box_rows, box_groups};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, l2_promotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("gemm: cuTensorMapEncodeTiled (grouped) failed with code %d (rows %zu cols %zu)", (int)r, rows, cols); return false; }
     return true;
 }
@@ -886,10 +931,24 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
     int grid = (int)(tiles < sms ? tiles : sms);
     if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr, 0u, 0u};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
+}
+
+// Tuning switches read once from the environment (defaults are the measured best).
+int env_int(const char* name, int dflt, int lo, int hi) {
+    static std::map<std::string, int> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(name);
+    if (it != cache.end()) return it->second;
+    int v = dflt;
+    if (const char* e = getenv(name)) v = atoi(e);
+    if (v < lo || v > hi) v = dflt;
+    cache[name] = v;
+    return v;
 }
 
 // TS_GEMM_DYNAMIC=0 (or ts_debug_set_gemm_dynamic(0)) goes back to the fixed stride, for A/B measurements and tests.
@@ -940,7 +999,8 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     int* counter = (dynamic_tiles(c) && s == c->compute) ? c->tile_counter : nullptr;
     if (counter) TS_CHECK(cudaMemsetAsync(counter, 0, sizeof(int), s));
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial, counter};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial, counter,
+                  (uint32_t)env_int("TS_GEMM_GROUP", 8, 1, 64), (uint32_t)env_int("TS_GEMM_L2_HINTS", 0, 0, 3)};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
