@@ -42,7 +42,7 @@ inline void require(bool ok, const char* what) {
 inline std::vector<unsigned long long> ull(const std::vector<size_t>& v) { return std::vector<unsigned long long>(v.begin(), v.end()); }
 }  // namespace detail
 
-// shape.rs: the dims of a tensor (tensors on this path are always contiguous)
+// shape.rs: the dims of a tensor (strides are implied: a transposed / permuted view keeps its axis order internally)
 struct Shape {
     std::vector<size_t> dims;
     size_t rank() const { return dims.size(); }
@@ -160,6 +160,8 @@ public:
     }
     Tensor permute(const std::vector<size_t>& order) const { auto o = detail::ull(order); return wrap(ts_tensor_permute(get(), o.data(), (int)o.size()), "permute"); }
     Tensor contiguous() const { return wrap(ts_tensor_contiguous(get()), "contiguous"); }
+    // false for the views transpose / t / permute return: they share this tensor's storage (transpose.rs:181-184)
+    bool is_contiguous() const { return ts_tensor_is_contiguous(get()); }
     Tensor clone() const { return wrap(ts_tensor_clone(get()), "clone"); }
     static Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
         std::vector<ts_tensor*> hs;
