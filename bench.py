@@ -46,9 +46,10 @@ GLOBAL_BATCH = 65536
 SEED = 4
 BLOCK_ROWS = 8192     # the synthetic batch is generated in blocks of rows, so that it is the same global batch for every N
 METRIC = "fwd+bwd+Adam steps/s (MLP 4096-8192-8192-4096, global batch 65536)"
-# DRAM bytes per flop of the tcgen05 GEMM, from one ncu capture of the 8192^3 case of the same kernel
-# (dram__bytes_read.sum + dram__bytes_write.sum per launch, divided by 2 * 8192^3 flop)
-GEMM_DRAM_BYTES_PER_FLOP_8192 = 3.04e9 / 1.0995e12
+# DRAM bytes per flop of the tcgen05 GEMM, from an ncu capture of a 16384 x 8192 x 8192 product of the same kernel, a quarter of
+# a C5 layer product (dram__bytes_read.sum + dram__bytes_write.sum = 4.64 + 0.53 GB per launch, divided by its 2.199e12 flop;
+# the 8192^3 case gives the same ratio, 2.55 GB per 1.0995e12 flop, so traffic grows in proportion to the flop)
+GEMM_DRAM_BYTES_PER_FLOP_8192 = 5.17e9 / 2.199e12
 # Learning rates.  BASELINE.json fixes one for C1 only (1e-3, the reference's default).  On the wide networks that default
 # kills the workload: Adam's first steps are sign-like, so every pre-activation of an 8192-wide layer moves by about
 # 8192 * 1e-3 * E|h| = +-4 at once, and with random targets (best prediction: zero) the ReLUs of the second hidden layer
@@ -414,9 +415,10 @@ def run_gpu(args, d: Dist):
         roof["frac"] = roof["achieved"] / roof["peak"]
     if cls == 0 and gl:
         roof["traffic"] = GEMM_DRAM_BYTES_PER_FLOP_8192 * (gwork / gl)
-        roof["traffic_note"] = ("scaled, not measured in this run: DRAM bytes per flop from one ncu capture of the 8192^3 case of the "
-                                "same kernel (dram__bytes_read.sum + dram__bytes_write.sum = 3.04 GB for 1.0995e12 flop) times the "
-                                "flop of an average launch here; the bench's GEMMs are too large to capture under ncu")
+        roof["traffic_note"] = ("scaled, not measured in this run: DRAM bytes per flop from an ncu capture of a 16384 x 8192 x 8192 "
+                                "product of the same kernel (dram__bytes_read.sum + dram__bytes_write.sum = 5.17 GB for 2.199e12 flop; "
+                                "8192^3 gives the same ratio) times the flop of an average launch here; the bench's own GEMMs are too "
+                                "large to capture under ncu; algorithmic bytes (operands and result once) are about a quarter of it")
     al, ams, awork = _prof(lib, 4)
     el, ems, ework = _prof(lib, 2)
     rl, rms, rwork = _prof(lib, 3)
