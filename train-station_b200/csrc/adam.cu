@@ -155,7 +155,7 @@ bool adam_launch(const AdamTensor* tensors, int n, const void* chunks_dev, float
 }
 
 // Updates tensors [first, last) of the table only; chunks_dev is still the map of the WHOLE table, so the range's
-// chunks start after those of the tensors before it.  Used to update each tensor as soon as its gradient is ready.
+// chunks start after those of the tensors before it.
 bool adam_launch_range(const AdamTensor* tensors, int first, int last, const void* chunks_dev, float lr, float beta1, float beta2,
                        float eps, float wd, float f1, float f2, float grad_scale, cudaStream_t s) {
     Scalars sc{lr, beta1, beta2, eps, wd, f1, f2, grad_scale, 1.0f - beta1, 1.0f - beta2};

@@ -212,6 +212,7 @@ struct KernelArgs {
     // stride: concurrently running pairs then stay on neighbouring tiles (shared panels stay in L2), and a pair that
     // starts late or runs slowly takes fewer tiles instead of stretching the whole launch.
     int* tile_counter;
+    uint32_t stages;       // two-CTA kernel: depth of the shared-memory ring in use (stages of 32 KiB)
     uint32_t group;        // two-CTA kernel: row tiles that sweep the columns together (tile order)
     uint32_t l2_hints;     // two-CTA kernel: 0 none; 1 A evict_last + B evict_first; 2 both evict_first; 3 A evict_first + B evict_last
 };
@@ -475,7 +476,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 //     remote arrive).
 // No copy uses cluster multicast.  All waits are bounded exactly as in the one-CTA kernel; the two cluster
 // barriers (after set-up, before exit) complete because every thread of both CTAs reaches them.
-constexpr int kBN2 = 256, kStages2 = 6;
+constexpr int kBN2 = 256, kStages2 = 6;   // the ring's depth; KernelArgs::stages <= 6 of them are used (5, 6 and 7 measured the same)
 constexpr int kHalfBytes = BM * BK * 4;               // 16 KiB: 128 rows (or columns) x 32 k
 constexpr int kStageBytes2 = 2 * kHalfBytes;          // A half-tile + B half-tile
 constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 256 + 1024;
@@ -725,7 +726,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll
                     for (int s = 0; s < kStages2; ++s)
                         if (s == (int)stage) armed_parity[s] = (int)phase;
-                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
             }
             if ((!ok || *abort_flag) && rank == 0) {
@@ -770,7 +771,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     }
                     umma2_commit(map_to_cta(empty_bar(stage), 0));   // the stage is free in both CTAs once these MMAs have read it
                     umma2_commit(map_to_cta(empty_bar(stage), 1));
-                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma2_commit(map_to_cta(acc_full_bar(acc), 0));      // accumulators complete in both CTAs
@@ -931,7 +932,7 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
     int grid = (int)(tiles < sms ? tiles : sms);
     if (kb_per_split == 0) kb_per_split = (uint32_t)((g.k + BK - 1) / BK);
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
-                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr, 0u, 0u};
+                  (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr, 0u, 0u, 0u};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
     kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
@@ -1000,7 +1001,8 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     if (counter) TS_CHECK(cudaMemsetAsync(counter, 0, sizeof(int), s));
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
                   (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, 1u, 0u, kWaitCycles, g.colsum_partial, counter,
-                  (uint32_t)env_int("TS_GEMM_GROUP", 8, 1, 64), (uint32_t)env_int("TS_GEMM_L2_HINTS", 0, 0, 3)};
+                  (uint32_t)env_int("TS_GEMM_STAGES", 6, 2, kStages2), (uint32_t)env_int("TS_GEMM_GROUP", 8, 1, 64),
+                  (uint32_t)env_int("TS_GEMM_L2_HINTS", 0, 0, 3)};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
     kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
@@ -1068,7 +1070,7 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
     if (!split3 && (g.a_lo || g.b_lo)) { set_error("gemm: low parts given without the 3xTF32 mode"); return false; }
     // Large problems: pairs of CTAs on 256 x 256 tiles, as long as every pair gets at least one tile.
     size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
-    const bool pairs = two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)c->sm_count / 2;
+    const bool pairs = two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)env_int("TS_GEMM_2CTA_MIN_TILES", c->sm_count / 2, 1, 1 << 20);
     if (g.colsum_out && !g.colsum_partial) {
         // Column sums of the result from the epilogue: one partial row per 32 result rows of every tile the chosen
         // kernel walks (rows past m contribute zeros), in scratch, then one small launch that adds them in order.
