@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtrain_station_b200.so")
-SOURCES = ["runtime.cu", "elementwise.cu", "reduce.cu", "reduce_dims.cu", "softmax.cu", "transform.cu", "adam.cu", "sgemm.cu", "gemm_tcgen05.cu", "engine.cu"]
+SOURCES = ["runtime.cu", "elementwise.cu", "reduce.cu", "reduce_dims.cu", "softmax.cu", "transform.cu", "adam.cu", "sgemm.cu", "thin_gemm.cu", "gemm_tcgen05.cu", "engine.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 

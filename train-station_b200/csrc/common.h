@@ -194,6 +194,11 @@ bool sgemm(const GemmArgs& g, cudaStream_t s);                       // FFMA, re
 bool gemm_tc_supported(const GemmArgs& g);
 bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s);  // tcgen05 TF32 / 3xTF32
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s);   // dispatch
+// Products with one dimension of at most 16 (a 10-class output layer, its weight and input gradients) in the modes
+// without a fixed summation order: FFMA kernels laid out along the long dimensions (thin_gemm.cu).
+bool gemm_thin_supported(const GemmArgs& g);
+bool gemm_thin_rounds(const GemmArgs& g);   // ... and this one would honour round_tf32
+bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s);
 }  // namespace k
 
 }  // namespace ts

@@ -261,6 +261,10 @@ static bool materialize(const TensorP& t, bool for_gemm) {
     } else if (matmul_precision() == 2 && k::gemm_tc_supported(g)) {
         if (!tf32_split_operand(c, p.a, &g.a, &g.a_lo) || !tf32_split_operand(c, p.b, &g.b, &g.b_lo)) return false;
     }
+    if (matmul_precision() == 1 && for_gemm && !g.round_tf32 && k::gemm_thin_rounds(g)) {
+        g.round_tf32 = true;     // a thin product that feeds a tensor-core GEMM: rounded as it is stored, no pass of its own
+        st->tf32_clean = true;
+    }
     if (!k::gemm(g, -1, c, c->compute)) return false;
     t->st = st;
     t->pending.reset();   // releases the operand references

@@ -1118,6 +1118,7 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
 
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
     if (precision < 0) precision = matmul_precision();
+    if (precision >= 1 && c && gemm_thin_supported(g)) return gemm_thin(g, c, s);
     if (precision >= 1 && gemm_tc_supported(g)) return gemm_tc(g, precision == 2, c, s);
     if (g.colsum_out) {   // the FP32 kernels have no such epilogue: the product first, then the ordinary column sum
         GemmArgs h = g;

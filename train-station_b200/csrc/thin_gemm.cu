@@ -1,0 +1,354 @@
+// FFMA kernels for products with one very short dimension (at most 16): the 10-class output layer of an MLP, the
+// gradient of its weights and the gradient of its input.  For the modes that promise no summation order (TF32, 3xTF32)
+// only: the FP32 mode keeps the reference's chain order on the tiled kernel (sgemm.cu).
+//
+// Tiles of 32 or more columns are mostly padding on such a product and a tile's CTA walks the whole of the long
+// dimension alone; these three kernels are instead laid out along the long dimensions, read every operand once with
+// coalesced loads and keep the short dimension in registers, so each is bound by the memory it has to touch:
+//
+//   thin_n_nn   C[m x n] = A[m x k] . B[k x n],   n <= 16   (forward: activations times a narrow weight matrix)
+//   thin_n_tn   C[m x n] = A[k x m]^T . B[k x n], n <= 16   (weight gradient: activations^T times a narrow gradient)
+//   thin_k_nt   C[m x n] = A[m x k] . B[n x k]^T, k <= 16   (input gradient: a narrow gradient times the weights^T)
+//
+// The operands are used as given (FP32 products of FP32 values, FP32 accumulation), which is at least as accurate as
+// the tensor-core path these shapes cannot take; every sum is added in a fixed order, so results repeat bit for bit.
+#include "common.h"
+
+#include <cstdlib>
+
+namespace ts {
+namespace k {
+namespace {
+
+constexpr int kThin = 16;
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float rn_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// bias, ReLU, mask and rounding in the order every GEMM epilogue of this library applies them
+__device__ __forceinline__ float finish(const GemmArgs& g, float v, size_t row, size_t col) {
+    if (g.bias) v = __fadd_rn(v, __ldg(g.bias + col));
+    if (g.relu) v = v > 0.0f ? v : 0.0f;
+    if (g.mask) v = g.mask[row * g.n + col] > 0.0f ? v : 0.0f;
+    if (g.round_tf32) v = rn_tf32(v);
+    return v;
+}
+
+// ---- C[m x n] = A[m x k] . B[k x n], n <= NP.  A CTA takes 32 rows, a warp 4 of them at a time; the lanes split K
+// (lane l takes k = l, l + 32, ...: a warp reads 128 contiguous bytes of each row per step) and B sits in shared
+// memory in chunks of 512 rows, each row padded to a pitch that lets eight consecutive rows be read as float4 without
+// bank conflicts.  The 32 partial sums of every result are then added by a butterfly.
+template <int NP>
+__global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
+    constexpr int S = NP == 4 ? 4 : (NP == 16 ? 20 : 12);
+    constexpr int KC = 512;
+    constexpr int R = 4;
+    __shared__ __align__(16) float bs[KC * S];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t M = g.m, N = g.n, K = g.k;
+    const size_t row0 = (size_t)blockIdx.x * 32 + (size_t)warp * R;
+    const float* arow[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const size_t rr = row0 + r < M ? row0 + r : M - 1;   // rows past the end re-read the last one and are not stored
+        arow[r] = g.a + rr * K;
+    }
+    float acc[R][NP];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
+
+    for (size_t kc = 0; kc < K; kc += KC) {
+        const int kn = (int)(K - kc < (size_t)KC ? K - kc : (size_t)KC);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kn * NP; idx += kThreads) {
+            const int kk = idx / NP, j = idx % NP;
+            bs[kk * S + j] = (size_t)j < N ? __ldg(g.b + (kc + kk) * N + j) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int kk = lane; kk < kn; kk += 32) {
+            float av[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) av[r] = __ldg(arow[r] + kc + kk);
+            const float4* bp = reinterpret_cast<const float4*>(bs + kk * S);
+#pragma unroll
+            for (int q = 0; q < NP / 4; ++q) {
+                const float4 b = bp[q];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    acc[r][q * 4 + 0] = fmaf(av[r], b.x, acc[r][q * 4 + 0]);
+                    acc[r][q * 4 + 1] = fmaf(av[r], b.y, acc[r][q * 4 + 1]);
+                    acc[r][q * 4 + 2] = fmaf(av[r], b.z, acc[r][q * 4 + 2]);
+                    acc[r][q * 4 + 3] = fmaf(av[r], b.w, acc[r][q * 4 + 3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float mine = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+            float v = acc[r][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == j) mine = v;
+        }
+        const size_t row = row0 + r;
+        if (row < M && (size_t)lane < N) g.c[row * N + lane] = finish(g, mine, row, lane);
+    }
+}
+
+// ---- C[m x n] = sum over r of A[r][i] * B[r][j], A stored [k x m], B stored [k x n], n <= NP.  A thread owns one
+// column i of A (a warp reads 128 contiguous bytes of a row) and all n results of it; the grid's second axis cuts the k
+// rows into slabs whose partial results land side by side in `out` (slab s at out + s * m * n) for a second launch to
+// add in slab order.  B's rows are staged in shared memory, 64 at a time, and read by all threads at once (broadcast).
+template <int NP>
+__global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* out, unsigned rows_per_slab) {
+    constexpr int RC = 64;
+    __shared__ __align__(16) float bs[RC * NP];
+    const size_t M = g.m, N = g.n, K = g.k;
+    const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
+    const size_t r1 = r0 + rows_per_slab < K ? r0 + rows_per_slab : K;
+    float acc[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) acc[j] = 0.0f;
+    for (size_t rc = r0; rc < r1; rc += RC) {
+        const int rn = (int)(r1 - rc < (size_t)RC ? r1 - rc : (size_t)RC);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < rn * NP; idx += kThreads) {
+            const int rr = idx / NP, j = idx % NP;
+            bs[idx] = (size_t)j < N ? __ldg(g.b + (rc + rr) * N + j) : 0.0f;
+        }
+        __syncthreads();
+        if (i < M) {
+            const float* ap = g.a + rc * M + i;
+#pragma unroll 8
+            for (int rr = 0; rr < rn; ++rr) {
+                const float a = __ldg(ap + (size_t)rr * M);
+                const float4* bp = reinterpret_cast<const float4*>(bs + rr * NP);
+#pragma unroll
+                for (int q = 0; q < NP / 4; ++q) {
+                    const float4 b = bp[q];
+                    acc[q * 4 + 0] = fmaf(a, b.x, acc[q * 4 + 0]);
+                    acc[q * 4 + 1] = fmaf(a, b.y, acc[q * 4 + 1]);
+                    acc[q * 4 + 2] = fmaf(a, b.z, acc[q * 4 + 2]);
+                    acc[q * 4 + 3] = fmaf(a, b.w, acc[q * 4 + 3]);
+                }
+            }
+        }
+    }
+    if (i < M) {
+        float* o = out + (size_t)blockIdx.y * M * N + i * N;
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+            if ((size_t)j < N) o[j] = acc[j];
+    }
+}
+
+// ---- C[m x n] = A[m x k] . B[n x k]^T, k <= KP.  A thread owns four consecutive result columns and keeps their four
+// rows of B in registers; a CTA covers 32 result rows (A's 32 rows sit in shared memory and are read by all threads at
+// once) by 1024 columns.  Every result is finished (bias, ReLU, mask, rounding) and stored as it is made, a row of
+// 4 KiB per step of the CTA; the column sums of the stored values over the CTA's 32 rows go to row blockIdx.x of
+// g.colsum_partial when that is set.  VEC: n % 4 == 0 and C, the mask and the bias are 16-byte aligned.
+template <int KP, bool VEC>
+__global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
+    __shared__ __align__(16) float as[32 * KP];
+    const size_t M = g.m, N = g.n, K = g.k;
+    const size_t row0 = (size_t)blockIdx.x * 32;
+    const size_t j0 = ((size_t)blockIdx.y * kThreads + threadIdx.x) * 4;
+    for (int idx = threadIdx.x; idx < 32 * KP; idx += kThreads) {
+        const int rr = idx / KP, kk = idx % KP;
+        as[idx] = (row0 + rr < M && (size_t)kk < K) ? __ldg(g.a + (row0 + rr) * K + kk) : 0.0f;
+    }
+    float bw[4][KP];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int kk = 0; kk < KP; ++kk) bw[q][kk] = (j0 + q < N && (size_t)kk < K) ? __ldg(g.b + (j0 + q) * K + kk) : 0.0f;
+    __syncthreads();
+    if (j0 >= N) return;
+    float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float bias[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (g.bias) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (j0 + q < N) bias[q] = __ldg(g.bias + j0 + q);
+    }
+    const int rows = (int)(M - row0 < 32 ? M - row0 : 32);
+#pragma unroll 4
+    for (int rr = 0; rr < rows; ++rr) {
+        const size_t row = row0 + rr;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float4* ap = reinterpret_cast<const float4*>(as + rr * KP);
+#pragma unroll
+        for (int kq = 0; kq < KP / 4; ++kq) {
+            const float4 a = ap[kq];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                v[q] = fmaf(a.x, bw[q][kq * 4 + 0], v[q]);
+                v[q] = fmaf(a.y, bw[q][kq * 4 + 1], v[q]);
+                v[q] = fmaf(a.z, bw[q][kq * 4 + 2], v[q]);
+                v[q] = fmaf(a.w, bw[q][kq * 4 + 3], v[q]);
+            }
+        }
+        if (g.bias) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] = __fadd_rn(v[q], bias[q]);
+        }
+        if (g.relu) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] = v[q] > 0.0f ? v[q] : 0.0f;
+        }
+        if (VEC) {
+            if (g.mask) {
+                const float4 mk = __ldcs(reinterpret_cast<const float4*>(g.mask + row * N + j0));
+                v[0] = mk.x > 0.0f ? v[0] : 0.0f; v[1] = mk.y > 0.0f ? v[1] : 0.0f;
+                v[2] = mk.z > 0.0f ? v[2] : 0.0f; v[3] = mk.w > 0.0f ? v[3] : 0.0f;
+            }
+            if (g.round_tf32) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v[q] = rn_tf32(v[q]);
+            }
+            *reinterpret_cast<float4*>(g.c + row * N + j0) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (j0 + q < N) {
+                    if (g.mask) v[q] = g.mask[row * N + j0 + q] > 0.0f ? v[q] : 0.0f;
+                    if (g.round_tf32) v[q] = rn_tf32(v[q]);
+                    g.c[row * N + j0 + q] = v[q];
+                } else {
+                    v[q] = 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cs[q] += v[q];
+    }
+    if (g.colsum_partial) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (j0 + q < N) g.colsum_partial[(size_t)blockIdx.x * N + j0 + q] = cs[q];
+    }
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// 0: not a thin product; 1 thin_n_nn, 2 thin_n_tn, 3 thin_k_nt.  The long dimensions must be long enough for the layout
+// to pay; everything else stays on the tiled kernels.
+int thin_case(const GemmArgs& g) {
+    static const bool on = [] { const char* e = getenv("TS_GEMM_THIN"); return !(e && e[0] == '0'); }();   // TS_GEMM_THIN=0: tiled kernels only
+    if (!on) return 0;
+    if (g.batch != 1 || g.a_lo || g.b_lo || !g.a || !g.b || !g.c) return 0;
+    if (g.m == 0 || g.n == 0 || g.k == 0) return 0;
+    if (g.m >= (1ull << 31) || g.n >= (1ull << 31) || g.k >= (1ull << 31)) return 0;
+    if (!g.trans_a && !g.trans_b && g.n <= (size_t)kThin && g.m >= 256 && g.k >= 128) return 1;
+    if (g.trans_a && !g.trans_b && g.n <= (size_t)kThin && g.k >= 256 && g.m >= 64 && !g.bias && !g.relu && !g.mask && !g.round_tf32) return 2;
+    if (!g.trans_a && g.trans_b && g.k <= (size_t)kThin && g.m >= 256 && g.n >= 128 && (g.n + 1023) / 1024 <= 65535) return 3;
+    return 0;
+}
+
+template <int NP>
+bool launch_nn(const GemmArgs& g, cudaStream_t s) {
+    thin_n_nn_kernel<NP><<<(unsigned)((g.m + 31) / 32), kThreads, 0, s>>>(g);
+    return cuda_ok(cudaGetLastError(), "thin GEMM (NN) launch");
+}
+template <int NP>
+bool launch_tn(const GemmArgs& g, float* out, unsigned col_blocks, unsigned slabs, unsigned rows_per_slab, cudaStream_t s) {
+    thin_n_tn_kernel<NP><<<dim3(col_blocks, slabs), kThreads, 0, s>>>(g, out, rows_per_slab);
+    return cuda_ok(cudaGetLastError(), "thin GEMM (TN) launch");
+}
+template <int KP>
+bool launch_nt(const GemmArgs& g, cudaStream_t s) {
+    const dim3 grid((unsigned)((g.m + 31) / 32), (unsigned)((g.n + 1023) / 1024));
+    const bool vec = g.n % 4 == 0 && al16(g.c) && (!g.mask || al16(g.mask));
+    if (vec) thin_k_nt_kernel<KP, true><<<grid, kThreads, 0, s>>>(g);
+    else thin_k_nt_kernel<KP, false><<<grid, kThreads, 0, s>>>(g);
+    return cuda_ok(cudaGetLastError(), "thin GEMM (NT) launch");
+}
+
+}  // namespace
+
+bool gemm_thin_supported(const GemmArgs& g) { return thin_case(g) != 0; }
+bool gemm_thin_rounds(const GemmArgs& g) { const int t = thin_case(g); return t == 1 || t == 3; }
+
+bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
+    const int which = thin_case(g);
+    if (!which || !c) { set_error("gemm: not a thin product"); return false; }
+    if (g.colsum_out && !(which == 3 && g.colsum_partial)) {
+        if (which == 3) {
+            // column sums of the stored result: one partial row per 32 result rows from the kernel, added in row order
+            const size_t prow = (g.m + 31) / 32;
+            float* part = c->alloc.alloc(prow * g.n * sizeof(float));
+            if (!part) return false;
+            GemmArgs h = g;
+            h.colsum_partial = part;
+            bool ok = gemm_thin(h, c, s) && colsum_finish(part, g.colsum_out, g.n, prow, s);
+            if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
+            c->alloc.free(part);
+            return ok;
+        }
+        GemmArgs h = g;
+        h.colsum_out = nullptr;
+        if (!gemm_thin(h, c, s)) return false;
+        float* scratch = c->alloc.alloc(colsum_scratch_elems(g.m, g.n) * sizeof(float));
+        if (!scratch) return false;
+        bool ok = colsum(g.c, g.colsum_out, g.m, g.n, scratch, s);
+        if (s != c->compute) cudaStreamSynchronize(s);
+        c->alloc.free(scratch);
+        return ok;
+    }
+    const double flop = 2.0 * (double)g.m * (double)g.n * (double)g.k;
+    if (which == 1) {
+        ProfScope prof(kProfGemmFp32, s, flop);
+        const size_t np = (g.n + 3) / 4 * 4;
+        return np == 4 ? launch_nn<4>(g, s) : np == 8 ? launch_nn<8>(g, s) : np == 12 ? launch_nn<12>(g, s) : launch_nn<16>(g, s);
+    }
+    if (which == 3) {
+        ProfScope prof(kProfGemmFp32, s, flop);
+        const size_t kp = (g.k + 3) / 4 * 4;
+        return kp == 4 ? launch_nt<4>(g, s) : kp == 8 ? launch_nt<8>(g, s) : kp == 12 ? launch_nt<12>(g, s) : launch_nt<16>(g, s);
+    }
+    // weight-gradient layout: enough slabs of the long reduction to give every SM a few CTAs, at least 32 rows each
+    const size_t col_blocks = (g.m + kThreads - 1) / kThreads;
+    size_t slabs = ((size_t)c->sm_count * 2 + col_blocks - 1) / col_blocks;
+    if (slabs > g.k / 32) slabs = g.k / 32;
+    if (slabs > 65535) slabs = 65535;
+    if (slabs < 1) slabs = 1;
+    size_t rows_per_slab = (g.k + slabs - 1) / slabs;
+    rows_per_slab = (rows_per_slab + 7) / 8 * 8;
+    slabs = (g.k + rows_per_slab - 1) / rows_per_slab;   // no empty slab
+    const size_t mn = g.m * g.n;
+    const size_t np = (g.n + 3) / 4 * 4;
+    float* part = nullptr;
+    if (slabs > 1) {
+        part = c->alloc.alloc(slabs * mn * sizeof(float));
+        if (!part) return false;
+    }
+    float* out = part ? part : g.c;
+    bool ok;
+    {
+        ProfScope prof(kProfGemmFp32, s, flop);
+        ok = np == 4    ? launch_tn<4>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
+             : np == 8  ? launch_tn<8>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
+             : np == 12 ? launch_tn<12>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
+                        : launch_tn<16>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s);
+    }
+    if (part) {
+        ok = ok && sum_slabs(part, g.c, mn, slabs, s);
+        if (s != c->compute) cudaStreamSynchronize(s);
+        c->alloc.free(part);
+    }
+    return ok;
+}
+
+}  // namespace k
+}  // namespace ts
