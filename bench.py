@@ -542,12 +542,13 @@ def run_gpu(args, d: Dist):
 
 
 def _timed_steps(ts, lib, step_fn, warmup, steps, mode, flop, peaks):
-    """`steps` calls of step_fn between two events, with the GEMM class profiled: a compact record."""
+    """`steps` calls of step_fn between two events: a compact record.  The step time comes from a first pass without
+    instrumentation; a second pass of the same length brackets every GEMM launch with events for the GEMM rate and its
+    share of that pass (on steps of a few hundred microseconds the brackets themselves cost several per cent)."""
     for _ in range(warmup):
         step_fn()
     ts.synchronize()
     ev0, ev1 = lib.ts_event_create(), lib.ts_event_create()
-    lib.ts_profile_reset(); lib.ts_profile_enable(1)
     launches0 = int(lib.ts_launch_count())
     lib.ts_event_record(ev0, None)
     for _ in range(steps):
@@ -556,6 +557,13 @@ def _timed_steps(ts, lib, step_fn, warmup, steps, mode, flop, peaks):
     ts.synchronize()
     ms = float(lib.ts_event_elapsed_ms(ev0, ev1)) / steps
     launches = int(lib.ts_launch_count()) - launches0
+    lib.ts_profile_reset(); lib.ts_profile_enable(1)
+    lib.ts_event_record(ev0, None)
+    for _ in range(steps):
+        out = step_fn()
+    lib.ts_event_record(ev1, None)
+    ts.synchronize()
+    ms_profiled = float(lib.ts_event_elapsed_ms(ev0, ev1)) / steps
     lib.ts_profile_enable(0)
     ts._ffi.check(lib.ts_profile_collect(), "profile")
     tc_n, tc_ms, tc_w = _prof(lib, 0)
@@ -564,7 +572,8 @@ def _timed_steps(ts, lib, step_fn, warmup, steps, mode, flop, peaks):
     gemm_ms, gemm_w = tc_ms + fp_ms, tc_w + fp_w
     rec = {"steps": steps, "ms_per_step": ms, "steps_per_s": 1000.0 / ms, "step_tflops": flop / (ms * 1e-3) / 1e12,
            "gemm_tflops": gemm_w / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None,
-           "gemm_launches": {"tensor_core": tc_n, "fp32": fp_n}, "gemm_share_of_step": gemm_ms / (ms * steps) if ms > 0 else None,
+           "gemm_launches": {"tensor_core": tc_n, "fp32": fp_n}, "gemm_share_of_step": gemm_ms / (ms_profiled * steps) if ms_profiled > 0 else None,
+           "ms_per_step_with_gemm_brackets": ms_profiled,
            "launches_per_step": launches / steps, "peak_tflops": peak, "frac": None}
     if tc_ms > 0 and peak:
         rec["frac"] = tc_w / (tc_ms * 1e-3) / 1e12 / peak      # tensor-core launches only, against the derived peak

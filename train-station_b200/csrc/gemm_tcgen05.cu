@@ -1086,7 +1086,7 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
     }
     if (pairs) return launch_tc2_any(g, c, s);
     size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
-    if (g.n <= 128 || tiles256 < (size_t)c->sm_count) {
+    if (g.n <= 128 || tiles256 < (size_t)env_int("TS_GEMM_BN256_MIN_TILES", c->sm_count, 1, 1 << 20)) {
         // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
         // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split: every (tile, split) pair is a
         // work item of the same launch, the partial products land side by side in scratch and a second kernel adds them

@@ -22,6 +22,7 @@ namespace {
 
 constexpr int kThin = 16;
 constexpr int kThreads = 256;
+constexpr int kNtRows = 16;   // result rows per CTA of the short-reduction kernel
 
 __device__ __forceinline__ float rn_tf32(float x) {
     uint32_t r;
@@ -41,12 +42,14 @@ __device__ __forceinline__ float finish(const GemmArgs& g, float v, size_t row, 
 // ---- C[m x n] = A[m x k] . B[k x n], n <= NP.  A CTA takes 32 rows, a warp 4 of them at a time; the lanes split K
 // (lane l takes k = l, l + 32, ...: a warp reads 128 contiguous bytes of each row per step) and B sits in shared
 // memory in chunks of 512 rows, each row padded to a pitch that lets eight consecutive rows be read as float4 without
-// bank conflicts.  The 32 partial sums of every result are then added by a butterfly.
+// bank conflicts.  A chunk of B is fetched with all of a thread's loads in flight at once (one memory latency, not one
+// per element).  The 32 partial sums of every result are then added by a butterfly.
 template <int NP>
 __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
     constexpr int S = NP == 4 ? 4 : (NP == 16 ? 20 : 12);
     constexpr int KC = 512;
     constexpr int R = 4;
+    constexpr int PER = KC * NP / kThreads;   // elements of a B chunk per thread
     __shared__ __align__(16) float bs[KC * S];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t M = g.m, N = g.n, K = g.k;
@@ -65,13 +68,20 @@ __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
 
     for (size_t kc = 0; kc < K; kc += KC) {
         const int kn = (int)(K - kc < (size_t)KC ? K - kc : (size_t)KC);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < kn * NP; idx += kThreads) {
-            const int kk = idx / NP, j = idx % NP;
-            bs[kk * S + j] = (size_t)j < N ? __ldg(g.b + (kc + kk) * N + j) : 0.0f;
+        float stage[PER];
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+            const int idx = threadIdx.x + t * kThreads, kk = idx / NP, j = idx % NP;
+            stage[t] = (kk < kn && (size_t)j < N) ? __ldg(g.b + (kc + kk) * N + j) : 0.0f;
+        }
+        __syncthreads();   // the previous chunk has been consumed
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+            const int idx = threadIdx.x + t * kThreads, kk = idx / NP, j = idx % NP;
+            bs[kk * S + j] = stage[t];
         }
         __syncthreads();
-#pragma unroll 4
+#pragma unroll 8
         for (int kk = lane; kk < kn; kk += 32) {
             float av[R];
 #pragma unroll
@@ -105,16 +115,21 @@ __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
     }
 }
 
-// ---- C[m x n] = sum over r of A[r][i] * B[r][j], A stored [k x m], B stored [k x n], n <= NP.  A thread owns one
-// column i of A (a warp reads 128 contiguous bytes of a row) and all n results of it; the grid's second axis cuts the k
-// rows into slabs whose partial results land side by side in `out` (slab s at out + s * m * n) for a second launch to
-// add in slab order.  B's rows are staged in shared memory, 64 at a time, and read by all threads at once (broadcast).
+// ---- C[m x n] = sum over r of A[r][i] * B[r][j], A stored [k x m], B stored [k x n], n <= NP.  A CTA owns 32
+// columns i of A (a lane each: a warp reads 128 contiguous bytes of a row) over one slab of the k rows; its eight warps
+// take the slab's rows in turn (warp w: rows w, w + 8, ...) and their partial results are added through shared memory
+// in warp order.  The grid's second axis cuts the k rows into slabs whose results land side by side in `out` (slab s at
+// out + s * m * n) for a second launch to add in slab order.  B's rows are staged in shared memory, 512 at a time, and
+// a warp reads one of them at a time (broadcast).
 template <int NP>
 __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* out, unsigned rows_per_slab) {
-    constexpr int RC = 64;
+    constexpr int RC = 512;
+    constexpr int PER = RC * NP / kThreads;
     __shared__ __align__(16) float bs[RC * NP];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t M = g.m, N = g.n, K = g.k;
-    const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    const size_t i = (size_t)blockIdx.x * 32 + lane;
+    const size_t ic = i < M ? i : M - 1;   // columns past the end re-read the last one and are not stored
     const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
     const size_t r1 = r0 + rows_per_slab < K ? r0 + rows_per_slab : K;
     float acc[NP];
@@ -122,49 +137,60 @@ __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* 
     for (int j = 0; j < NP; ++j) acc[j] = 0.0f;
     for (size_t rc = r0; rc < r1; rc += RC) {
         const int rn = (int)(r1 - rc < (size_t)RC ? r1 - rc : (size_t)RC);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < rn * NP; idx += kThreads) {
-            const int rr = idx / NP, j = idx % NP;
-            bs[idx] = (size_t)j < N ? __ldg(g.b + (rc + rr) * N + j) : 0.0f;
-        }
-        __syncthreads();
-        if (i < M) {
-            const float* ap = g.a + rc * M + i;
-#pragma unroll 8
-            for (int rr = 0; rr < rn; ++rr) {
-                const float a = __ldg(ap + (size_t)rr * M);
-                const float4* bp = reinterpret_cast<const float4*>(bs + rr * NP);
+        float stage[PER];
 #pragma unroll
-                for (int q = 0; q < NP / 4; ++q) {
-                    const float4 b = bp[q];
-                    acc[q * 4 + 0] = fmaf(a, b.x, acc[q * 4 + 0]);
-                    acc[q * 4 + 1] = fmaf(a, b.y, acc[q * 4 + 1]);
-                    acc[q * 4 + 2] = fmaf(a, b.z, acc[q * 4 + 2]);
-                    acc[q * 4 + 3] = fmaf(a, b.w, acc[q * 4 + 3]);
-                }
+        for (int t = 0; t < PER; ++t) {
+            const int idx = threadIdx.x + t * kThreads, rr = idx / NP, j = idx % NP;
+            stage[t] = (rr < rn && (size_t)j < N) ? __ldg(g.b + (rc + rr) * N + j) : 0.0f;
+        }
+        __syncthreads();   // the previous chunk has been consumed
+#pragma unroll
+        for (int t = 0; t < PER; ++t) bs[threadIdx.x + t * kThreads] = stage[t];
+        __syncthreads();
+        const float* ap = g.a + rc * M + ic;
+#pragma unroll 8
+        for (int rr = warp; rr < rn; rr += 8) {
+            const float a = __ldg(ap + (size_t)rr * M);
+            const float4* bp = reinterpret_cast<const float4*>(bs + rr * NP);
+#pragma unroll
+            for (int q = 0; q < NP / 4; ++q) {
+                const float4 b = bp[q];
+                acc[q * 4 + 0] = fmaf(a, b.x, acc[q * 4 + 0]);
+                acc[q * 4 + 1] = fmaf(a, b.y, acc[q * 4 + 1]);
+                acc[q * 4 + 2] = fmaf(a, b.z, acc[q * 4 + 2]);
+                acc[q * 4 + 3] = fmaf(a, b.w, acc[q * 4 + 3]);
             }
         }
     }
-    if (i < M) {
-        float* o = out + (size_t)blockIdx.y * M * N + i * N;
+    __syncthreads();   // bs is reused for the warps' partial results: [warp][column][j]
+    float* red = bs;
 #pragma unroll
-        for (int j = 0; j < NP; ++j)
-            if ((size_t)j < N) o[j] = acc[j];
+    for (int j = 0; j < NP; ++j) red[(warp * 32 + lane) * NP + j] = acc[j];
+    __syncthreads();
+    // 32 columns x n results, added over the 8 warps in warp order and written as one contiguous run of the slab
+    float* o = out + (size_t)blockIdx.y * M * N + (size_t)blockIdx.x * 32 * N;
+    const size_t valid = (M - (size_t)blockIdx.x * 32 < 32 ? M - (size_t)blockIdx.x * 32 : 32) * N;
+    for (size_t e = threadIdx.x; e < valid; e += kThreads) {
+        const size_t col = e / N, j = e % N;
+        float v = red[col * NP + j];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) v += red[(w * 32 + col) * NP + j];
+        o[e] = v;
     }
 }
 
 // ---- C[m x n] = A[m x k] . B[n x k]^T, k <= KP.  A thread owns four consecutive result columns and keeps their four
-// rows of B in registers; a CTA covers 32 result rows (A's 32 rows sit in shared memory and are read by all threads at
+// rows of B in registers; a CTA covers 16 result rows (A's 16 rows sit in shared memory and are read by all threads at
 // once) by 1024 columns.  Every result is finished (bias, ReLU, mask, rounding) and stored as it is made, a row of
-// 4 KiB per step of the CTA; the column sums of the stored values over the CTA's 32 rows go to row blockIdx.x of
+// 4 KiB per step of the CTA; the column sums of the stored values over the CTA's 16 rows go to row blockIdx.x of
 // g.colsum_partial when that is set.  VEC: n % 4 == 0 and C, the mask and the bias are 16-byte aligned.
 template <int KP, bool VEC>
 __global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
-    __shared__ __align__(16) float as[32 * KP];
+    __shared__ __align__(16) float as[kNtRows * KP];
     const size_t M = g.m, N = g.n, K = g.k;
-    const size_t row0 = (size_t)blockIdx.x * 32;
+    const size_t row0 = (size_t)blockIdx.x * kNtRows;
     const size_t j0 = ((size_t)blockIdx.y * kThreads + threadIdx.x) * 4;
-    for (int idx = threadIdx.x; idx < 32 * KP; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < kNtRows * KP; idx += kThreads) {
         const int rr = idx / KP, kk = idx % KP;
         as[idx] = (row0 + rr < M && (size_t)kk < K) ? __ldg(g.a + (row0 + rr) * K + kk) : 0.0f;
     }
@@ -182,8 +208,8 @@ __global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
         for (int q = 0; q < 4; ++q)
             if (j0 + q < N) bias[q] = __ldg(g.bias + j0 + q);
     }
-    const int rows = (int)(M - row0 < 32 ? M - row0 : 32);
-#pragma unroll 4
+    const int rows = (int)(M - row0 < (size_t)kNtRows ? M - row0 : (size_t)kNtRows);
+#pragma unroll 8
     for (int rr = 0; rr < rows; ++rr) {
         const size_t row = row0 + rr;
         float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -268,7 +294,7 @@ bool launch_tn(const GemmArgs& g, float* out, unsigned col_blocks, unsigned slab
 }
 template <int KP>
 bool launch_nt(const GemmArgs& g, cudaStream_t s) {
-    const dim3 grid((unsigned)((g.m + 31) / 32), (unsigned)((g.n + 1023) / 1024));
+    const dim3 grid((unsigned)((g.m + kNtRows - 1) / kNtRows), (unsigned)((g.n + 1023) / 1024));
     const bool vec = g.n % 4 == 0 && al16(g.c) && (!g.mask || al16(g.mask));
     if (vec) thin_k_nt_kernel<KP, true><<<grid, kThreads, 0, s>>>(g);
     else thin_k_nt_kernel<KP, false><<<grid, kThreads, 0, s>>>(g);
@@ -285,8 +311,8 @@ bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     if (!which || !c) { set_error("gemm: not a thin product"); return false; }
     if (g.colsum_out && !(which == 3 && g.colsum_partial)) {
         if (which == 3) {
-            // column sums of the stored result: one partial row per 32 result rows from the kernel, added in row order
-            const size_t prow = (g.m + 31) / 32;
+            // column sums of the stored result: one partial row per CTA row of the kernel, added in row order
+            const size_t prow = (g.m + kNtRows - 1) / kNtRows;
             float* part = c->alloc.alloc(prow * g.n * sizeof(float));
             if (!part) return false;
             GemmArgs h = g;
@@ -317,10 +343,10 @@ bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
         const size_t kp = (g.k + 3) / 4 * 4;
         return kp == 4 ? launch_nt<4>(g, s) : kp == 8 ? launch_nt<8>(g, s) : kp == 12 ? launch_nt<12>(g, s) : launch_nt<16>(g, s);
     }
-    // weight-gradient layout: enough slabs of the long reduction to give every SM a few CTAs, at least 32 rows each
-    const size_t col_blocks = (g.m + kThreads - 1) / kThreads;
-    size_t slabs = ((size_t)c->sm_count * 2 + col_blocks - 1) / col_blocks;
-    if (slabs > g.k / 32) slabs = g.k / 32;
+    // weight-gradient layout: enough slabs of the long reduction to give every SM about two CTAs, at least 64 rows each
+    const size_t col_blocks = (g.m + 31) / 32;
+    size_t slabs = (size_t)c->sm_count * 2 / col_blocks;
+    if (slabs > g.k / 64) slabs = g.k / 64;
     if (slabs > 65535) slabs = 65535;
     if (slabs < 1) slabs = 1;
     size_t rows_per_slab = (g.k + slabs - 1) / slabs;
