@@ -1085,34 +1085,49 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
         return ok;
     }
     if (pairs) return launch_tc2_any(g, c, s);
-    size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
-    if (g.n <= 128 || tiles256 < (size_t)env_int("TS_GEMM_BN256_MIN_TILES", c->sm_count, 1, 1 << 20)) {
-        // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
-        // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split: every (tile, split) pair is a
-        // work item of the same launch, the partial products land side by side in scratch and a second kernel adds them
-        // in split order, so the result does not depend on scheduling.  FP32 mode never comes here (its order is fixed).
-        const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
-        const size_t num_kb = (g.k + BK - 1) / BK;
-        if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && !g.colsum_partial && tiles128 * 2 <= (size_t)c->sm_count && num_kb >= 64 && split_k_enabled()) {
-            size_t splits = (size_t)c->sm_count / tiles128;
-            if (splits > num_kb / 32) splits = num_kb / 32;          // at least 1024 elements of K per split
-            if (splits > 16) splits = 16;
-            if (splits >= 2) {
-                const size_t kbps = (num_kb + splits - 1) / splits;
-                splits = (num_kb + kbps - 1) / kbps;                 // no empty split
-                const size_t mn = g.m * g.n;
-                float* part = c->alloc.alloc(splits * mn * sizeof(float));
-                if (!part) return false;
-                GemmArgs h = g;
-                h.c = part;
-                bool ok = launch_tc_bn<128>(h, c, s, (uint32_t)splits, (uint32_t)kbps) && sum_slabs(part, g.c, mn, splits, s);
-                if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
-                c->alloc.free(part);
-                return ok;
-            }
+    const size_t sms = (size_t)c->sm_count;
+    const size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
+    const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
+    const size_t num_kb = (g.k + BK - 1) / BK;
+    // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
+    // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split: every (tile, split) pair is a
+    // work item of the same launch, the partial products land side by side in scratch and a second kernel adds them
+    // in split order, so the result does not depend on scheduling.  FP32 mode never comes here (its order is fixed).
+    // At this size a CTA is bound by what it pulls out of L2, (rows + columns of its tile) x its share of K, so of the
+    // two tile widths the one with the smaller such product is taken (1024 x 1024 over K = 4096: four splits of 128 x 256
+    // tiles move a quarter less than two splits of 128 x 128 tiles).
+    if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && !g.colsum_partial && tiles128 * 2 <= sms && num_kb >= 64 && split_k_enabled()) {
+        auto plan = [&](size_t tiles, size_t width, size_t* splits, size_t* kbps) {
+            size_t sp = sms / tiles;
+            if (sp > num_kb / 32) sp = num_kb / 32;          // at least 1024 elements of K per split
+            if (sp > 16) sp = 16;
+            if (sp < 1) sp = 1;
+            *kbps = (num_kb + sp - 1) / sp;
+            *splits = (num_kb + *kbps - 1) / *kbps;          // no empty split
+            return (BM + width) * *kbps;
+        };
+        size_t sp128, kb128, sp256, kb256;
+        const size_t cost128 = plan(tiles128, 128, &sp128, &kb128);
+        const size_t cost256 = g.n > 128 ? plan(tiles256, 256, &sp256, &kb256) : ~size_t(0);
+        const bool wide = cost256 < cost128;
+        const size_t splits = wide ? sp256 : sp128, kbps = wide ? kb256 : kb128;
+        if (splits >= 2) {
+            const size_t mn = g.m * g.n;
+            float* part = c->alloc.alloc(splits * mn * sizeof(float));
+            if (!part) return false;
+            GemmArgs h = g;
+            h.c = part;
+            bool ok = (wide ? launch_tc_bn<256>(h, c, s, (uint32_t)splits, (uint32_t)kbps) : launch_tc_bn<128>(h, c, s, (uint32_t)splits, (uint32_t)kbps)) &&
+                      sum_slabs(part, g.c, mn, splits, s);
+            if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
+            c->alloc.free(part);
+            return ok;
         }
-        return launch_tc_bn<128>(g, c, s);
     }
+    // 128 x 128 tiles while those fit in one wave (twice as many CTAs at work as 128 x 256 tiles would give); beyond
+    // that one wave of 128 x 256 tiles beats two of the narrow ones, because each CTA then pulls a third less through L2
+    // per flop (4096 x 1024 x 1024: 20.5 against 28.6 us).  TS_GEMM_BN256_MIN_TILES moves the switch-over.
+    if (g.n <= 128 || tiles256 < (size_t)env_int("TS_GEMM_BN256_MIN_TILES", (int)(sms / 2 + 1), 1, 1 << 20)) return launch_tc_bn<128>(g, c, s);
     return launch_tc_bn<256>(g, c, s);
 }
 
