@@ -60,6 +60,7 @@ struct AdamTable { AdamTensor t[kMaxTensorsPerLaunch]; };
 template <bool AMS>
 __global__ void __launch_bounds__(kThreads) adam_kernel(const __grid_constant__ AdamTable tab, const ChunkEntry* __restrict__ chunks,
                                                         int chunk_base, int tensor_base, int split_log2, Scalars sc) {
+    grid_dependency_sync();
     // 2^split_log2 CTAs share a chunk (each a 1024-element-aligned slice of it): small parameter sets, which would
     // otherwise run as a handful of CTAs making sixteen dependent trips each, spread over the SMs instead
     const ChunkEntry ce = chunks[chunk_base + (blockIdx.x >> split_log2)];
@@ -183,8 +184,8 @@ bool adam_launch_range(const AdamTensor* tensors, int first, int last, const voi
             int split_log2 = 0;
             while (split_log2 < 4 && (n_chunks << split_log2) < want) ++split_log2;
             const int grid = n_chunks << split_log2;
-            if (ams) adam_kernel<true><<<grid, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
-            else adam_kernel<false><<<grid, kThreads, 0, s>>>(tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
+            if (ams) launch_dep(adam_kernel<true>, dim3(grid), dim3(kThreads), 0, s, tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
+            else launch_dep(adam_kernel<false>, dim3(grid), dim3(kThreads), 0, s, tab, (const ChunkEntry*)chunks_dev, chunk_base, t0, split_log2, sc);
             if (!cuda_ok(cudaGetLastError(), "adam launch")) return false;
         }
         chunk_base += n_chunks;

@@ -91,6 +91,37 @@ struct ProfSuspend {
 int matmul_precision();
 bool fusion_enabled();
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A step of a small network is a chain of twenty-odd kernels of a few microseconds each, every one waiting for the one
+// before it; between two of them the GPU sits idle while the next grid is set up.  Kernels launched through launch_dep()
+// carry the programmatic-stream-serialization attribute: their CTAs may be placed on the SMs while the kernel before
+// them is still running, and they call grid_dependency_sync() before they touch global memory, which waits until
+// everything launched before them has completed and its writes are visible, so the order of the stream's results is
+// unchanged.  The same call then lets the grid behind them be set up in turn.  A kernel launched the ordinary way, or
+// following one that never makes the call, simply starts when its predecessor has finished.  TS_PDL=0 launches
+// everything the ordinary way.
+bool dependent_launch_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline void launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // the caller reads cudaGetLastError()
+}
+#endif
+
 // ---------------------------------------------------------------- kernels (device pointers)
 namespace k {
 constexpr size_t kReduceScratchElems = 4096;

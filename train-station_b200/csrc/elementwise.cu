@@ -33,6 +33,7 @@ struct Ptrs {
 
 template <int NIN, int NOUT, class F>
 __global__ void __launch_bounds__(kThreads) ew_vec_kernel(Ptrs<NIN, NOUT> p, size_t n_vec, size_t n, F f) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * kThreads * kUnroll;
     for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n_vec; base += stride) {
         float4 vin[kUnroll][NIN ? NIN : 1];
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(Ptrs<NIN, NOUT> p, siz
 // Fallback for pointers that are not 16-byte aligned (sub-buffers handed in through the raw ABI).
 template <int NIN, int NOUT, class F>
 __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(Ptrs<NIN, NOUT> p, size_t n, F f) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * kThreads;
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
         float xi[NIN == 0 ? 1 : NIN], xo[NOUT];
@@ -111,9 +113,9 @@ bool launch_ew(Ptrs<NIN, NOUT> p, size_t n, F f, cudaStream_t s) {
     ProfScope prof(kProfElementwise, s, 4.0 * (double)n * n_arrays);
     if (al) {
         size_t n_vec = n / 4;
-        ew_vec_kernel<NIN, NOUT, F><<<grid_for(n_vec, c->sm_count), kThreads, 0, s>>>(p, n_vec, n, f);
+        launch_dep(ew_vec_kernel<NIN, NOUT, F>, dim3(grid_for(n_vec, c->sm_count)), dim3(kThreads), 0, s, p, n_vec, n, f);
     } else {
-        ew_scalar_kernel<NIN, NOUT, F><<<grid_for((n + 3) / 4, c->sm_count), kThreads, 0, s>>>(p, n, f);
+        launch_dep(ew_scalar_kernel<NIN, NOUT, F>, dim3(grid_for((n + 3) / 4, c->sm_count)), dim3(kThreads), 0, s, p, n, f);
     }
     return cuda_ok(cudaGetLastError(), "elementwise launch");
 }
@@ -459,6 +461,7 @@ bool fill(float* o, float v, size_t n, cudaStream_t s) { return launch_ew(Ptrs<0
 namespace {
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads) sum_slabs_kernel(const float* __restrict__ part, float* __restrict__ out, size_t n, int slabs) {
+    grid_dependency_sync();
     const size_t step = (size_t)gridDim.x * kThreads;
     if (VEC) {
         const size_t nv = n / 4;
@@ -491,8 +494,8 @@ bool sum_slabs(const float* part, float* out, size_t n, size_t slabs, cudaStream
     size_t grid = (work + kThreads - 1) / kThreads;
     const size_t cap = (size_t)c->sm_count * 8;
     if (grid > cap) grid = cap;
-    if (vec) sum_slabs_kernel<true><<<(unsigned)grid, kThreads, 0, s>>>(part, out, n, (int)slabs);
-    else sum_slabs_kernel<false><<<(unsigned)grid, kThreads, 0, s>>>(part, out, n, (int)slabs);
+    if (vec) launch_dep(sum_slabs_kernel<true>, dim3((unsigned)grid), dim3(kThreads), 0, s, part, out, n, (int)slabs);
+    else launch_dep(sum_slabs_kernel<false>, dim3((unsigned)grid), dim3(kThreads), 0, s, part, out, n, (int)slabs);
     return cuda_ok(cudaGetLastError(), "sum_slabs launch");
 }
 bool fill_from_scalar(float* o, const float* scalar, float sc, size_t n, cudaStream_t s) {

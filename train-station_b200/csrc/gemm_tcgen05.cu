@@ -296,6 +296,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_sync();   // barriers and tensor memory are set up beside the tail of the kernel before; global memory from here on
 
     // grouped tile order: 16 row-tiles share their B panels in L2 while they sweep the columns
     constexpr uint32_t kGroup = 16;
@@ -622,6 +623,7 @@ gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     cluster_sync_all();                                        // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_sync();   // set-up runs beside the tail of the kernel before; global memory is touched from here on
 
     const uint32_t kGroup = args.group;                        // row-tiles of 256 that share their B panels in L2 (8 by default)
     auto tile_coords = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
@@ -934,7 +936,7 @@ bool launch_tc(const GemmArgs& g, DeviceCtx* c, cudaStream_t s, uint32_t splits 
     KernelArgs ka{g.c, g.bias, g.mask, g.relu ? 1 : 0, g.round_tf32 ? 1 : 0, a_grouped ? 1 : 0, b_grouped ? 1 : 0, split3 ? 3 : 1,
                   (uint32_t)g.m, (uint32_t)g.n, (uint32_t)g.k, c->error_flag, splits, kb_per_split, g_wait_budget.load(), g.colsum_partial, nullptr, 0u, 0u, 0u};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);   // algorithmic flop, whatever the pass count
-    kern<<<grid, kThreads, Cf::kSmemBytes, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
+    launch_dep(kern, dim3(grid), dim3(kThreads), Cf::kSmemBytes, s, tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 gemm launch");
 }
 
@@ -1004,7 +1006,7 @@ bool launch_tc2(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
                   (uint32_t)env_int("TS_GEMM_STAGES", 6, 2, kStages2), (uint32_t)env_int("TS_GEMM_GROUP", 8, 1, 64),
                   (uint32_t)env_int("TS_GEMM_L2_HINTS", 0, 0, 3)};
     ProfScope prof(kProfGemmTc, s, 2.0 * (double)g.m * (double)g.n * (double)g.k);
-    kern<<<grid, kThreads, kSmemBytes2, s>>>(tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
+    launch_dep(kern, dim3(grid), dim3(kThreads), kSmemBytes2, s, tm_a, tm_b, tm_a_lo, tm_b_lo, ka);
     return cuda_ok(cudaGetLastError(), "tcgen05 2-CTA gemm launch");
 }
 

@@ -40,6 +40,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads) sum_stage1(const float* __restrict__ x, const float* __restrict__ y,
                                                        float* __restrict__ partial, size_t n, int vec_ok, float* __restrict__ out,
                                                        float divisor) {
+    grid_dependency_sync();
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * kThreads;
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(kThreads) sum_stage1(const float* __restrict__
 
 __global__ void __launch_bounds__(kThreads) sum_stage2(const float* __restrict__ partial, int n_partial, float* __restrict__ out,
                                                        float divisor) {
+    grid_dependency_sync();
     float v = 0.0f;
     for (int i = threadIdx.x; i < n_partial; i += kThreads) v += partial[i];
     v = block_sum(v);
@@ -123,8 +125,8 @@ bool sum_impl(const float* x, const float* y, float* out, size_t n, bool mean, f
     int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && (MODE == 0 || (reinterpret_cast<uintptr_t>(y) & 15) == 0);
     const float divisor = mean ? (float)n : 0.0f;
     ProfScope prof(kProfReduce, s, 4.0 * (double)n * (MODE == 1 ? 2 : 1), grid == 1 ? 1 : 2);
-    sum_stage1<MODE><<<grid, kThreads, 0, s>>>(x, y, scratch, n, vec_ok, out, divisor);
-    if (grid > 1) sum_stage2<<<1, kThreads, 0, s>>>(scratch, grid, out, divisor);
+    launch_dep(sum_stage1<MODE>, dim3(grid), dim3(kThreads), 0, s, x, y, scratch, n, vec_ok, out, divisor);
+    if (grid > 1) launch_dep(sum_stage2, dim3(1), dim3(kThreads), 0, s, scratch, grid, out, divisor);
     return cuda_ok(cudaGetLastError(), "sum launch");
 }
 
@@ -158,6 +160,7 @@ template <bool FUSED, bool VEC>
 __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restrict__ g, const float* __restrict__ ref,
                                                           float* __restrict__ gi, float* __restrict__ partial, size_t rows,
                                                           size_t cols, size_t rows_per_split) {
+    grid_dependency_sync();
     const int cl = threadIdx.x % kColLanes, rl = threadIdx.x / kColLanes;
     const size_t r0 = (size_t)blockIdx.y * rows_per_split;
     size_t r1 = r0 + rows_per_split;
@@ -220,6 +223,7 @@ __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restric
 
 __global__ void __launch_bounds__(kThreads) colsum_stage2(const float* __restrict__ partial, float* __restrict__ out, size_t cols,
                                                           int splits) {
+    grid_dependency_sync();
     size_t col = (size_t)blockIdx.x * kThreads + threadIdx.x;
     if (col >= cols) return;
     float v = 0.0f;
@@ -232,6 +236,7 @@ __global__ void __launch_bounds__(kThreads) colsum_stage2(const float* __restric
 // (a warp reads 128 contiguous bytes per row), the 8 warps take rows w, w + 8, ... with four loads in flight, and the 8
 // warp totals are added in warp order.  The order of additions is fixed, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(256) colsum_rows_kernel(const float* __restrict__ part, float* __restrict__ out, size_t cols, int rows) {
+    grid_dependency_sync();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const size_t col = (size_t)blockIdx.x * 32 + lane;
     __shared__ float sm[8][32];
@@ -270,9 +275,9 @@ bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t
     float* partial = p.splits > 1 ? scratch : out;
     dim3 grid(p.col_tiles, p.splits);
     ProfScope prof(kProfReduce, s, 4.0 * (double)rows * (double)cols * (FUSED ? 3 : 1), p.splits > 1 ? 2 : 1);
-    if (p.vec) colsum_stage1<FUSED, true><<<grid, kThreads, 0, s>>>(g, ref, gi, partial, rows, cols, p.rows_per_split);
-    else colsum_stage1<FUSED, false><<<grid, kThreads, 0, s>>>(g, ref, gi, partial, rows, cols, p.rows_per_split);
-    if (p.splits > 1) colsum_stage2<<<(unsigned)((cols + kThreads - 1) / kThreads), kThreads, 0, s>>>(partial, out, cols, p.splits);
+    if (p.vec) launch_dep(colsum_stage1<FUSED, true>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split);
+    else launch_dep(colsum_stage1<FUSED, false>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split);
+    if (p.splits > 1) launch_dep(colsum_stage2, dim3((unsigned)((cols + kThreads - 1) / kThreads)), dim3(kThreads), 0, s, partial, out, cols, (int)p.splits);
     return cuda_ok(cudaGetLastError(), "colsum launch");
 }
 
@@ -299,7 +304,7 @@ bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial
     if (cols == 0) return true;
     if (!partial || !out || partial_rows == 0 || partial_rows > 0x7fffffff) { set_error("colsum_finish: bad arguments"); return false; }
     ProfScope prof(kProfReduce, s, 4.0 * (double)cols * (double)(partial_rows + 1));
-    colsum_rows_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, out, cols, (int)partial_rows);
+    launch_dep(colsum_rows_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(256), 0, s, partial, out, cols, (int)partial_rows);
     return cuda_ok(cudaGetLastError(), "colsum_finish launch");
 }
 bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols, float* scratch,

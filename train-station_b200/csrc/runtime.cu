@@ -188,6 +188,11 @@ cudaStream_t pick_stream(void* user_stream) {
     return c ? c->compute : nullptr;
 }
 
+bool dependent_launch_enabled() {
+    static const bool on = [] { const char* e = getenv("TS_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 int matmul_precision() {
     if (g_precision < 0) {
         const char* e = getenv("TS_MATMUL_PRECISION");

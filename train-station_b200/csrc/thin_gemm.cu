@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
     constexpr int R = 4;
     constexpr int PER = KC * NP / kThreads;   // elements of a B chunk per thread
     __shared__ __align__(16) float bs[KC * S];
+    grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t M = g.m, N = g.n, K = g.k;
     const size_t row0 = (size_t)blockIdx.x * 32 + (size_t)warp * R;
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* 
     constexpr int RC = 512;
     constexpr int PER = RC * NP / kThreads;
     __shared__ __align__(16) float bs[RC * NP];
+    grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t M = g.m, N = g.n, K = g.k;
     const size_t i = (size_t)blockIdx.x * 32 + lane;
@@ -187,6 +189,7 @@ __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* 
 template <int KP, bool VEC>
 __global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
     __shared__ __align__(16) float as[kNtRows * KP];
+    grid_dependency_sync();
     const size_t M = g.m, N = g.n, K = g.k;
     const size_t row0 = (size_t)blockIdx.x * kNtRows;
     const size_t j0 = ((size_t)blockIdx.y * kThreads + threadIdx.x) * 4;
@@ -284,20 +287,20 @@ int thin_case(const GemmArgs& g) {
 
 template <int NP>
 bool launch_nn(const GemmArgs& g, cudaStream_t s) {
-    thin_n_nn_kernel<NP><<<(unsigned)((g.m + 31) / 32), kThreads, 0, s>>>(g);
+    launch_dep(thin_n_nn_kernel<NP>, dim3((unsigned)((g.m + 31) / 32)), dim3(kThreads), 0, s, g);
     return cuda_ok(cudaGetLastError(), "thin GEMM (NN) launch");
 }
 template <int NP>
 bool launch_tn(const GemmArgs& g, float* out, unsigned col_blocks, unsigned slabs, unsigned rows_per_slab, cudaStream_t s) {
-    thin_n_tn_kernel<NP><<<dim3(col_blocks, slabs), kThreads, 0, s>>>(g, out, rows_per_slab);
+    launch_dep(thin_n_tn_kernel<NP>, dim3(col_blocks, slabs), dim3(kThreads), 0, s, g, out, rows_per_slab);
     return cuda_ok(cudaGetLastError(), "thin GEMM (TN) launch");
 }
 template <int KP>
 bool launch_nt(const GemmArgs& g, cudaStream_t s) {
     const dim3 grid((unsigned)((g.m + kNtRows - 1) / kNtRows), (unsigned)((g.n + 1023) / 1024));
     const bool vec = g.n % 4 == 0 && al16(g.c) && (!g.mask || al16(g.mask));
-    if (vec) thin_k_nt_kernel<KP, true><<<grid, kThreads, 0, s>>>(g);
-    else thin_k_nt_kernel<KP, false><<<grid, kThreads, 0, s>>>(g);
+    if (vec) launch_dep(thin_k_nt_kernel<KP, true>, grid, dim3(kThreads), 0, s, g);
+    else launch_dep(thin_k_nt_kernel<KP, false>, grid, dim3(kThreads), 0, s, g);
     return cuda_ok(cudaGetLastError(), "thin GEMM (NT) launch");
 }
 
