@@ -243,6 +243,7 @@ struct PowBwdF {
 template <bool RELU>
 __global__ void __launch_bounds__(kThreads) bias_act_vec_kernel(const float4* __restrict__ z, const float4* __restrict__ bias,
                                                                 float4* __restrict__ out, size_t n_vec, unsigned cols_vec) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * kThreads;
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec; i += stride) {
         float4 v = __ldcs(z + i);
@@ -258,6 +259,7 @@ __global__ void __launch_bounds__(kThreads) bias_act_vec_kernel(const float4* __
 template <bool RELU>
 __global__ void __launch_bounds__(kThreads) bias_act_scalar_kernel(const float* __restrict__ z, const float* __restrict__ bias,
                                                                    float* __restrict__ out, size_t n, size_t cols) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * kThreads;
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
         float v = __fadd_rn(z[i], __ldg(bias + (i % cols)));
@@ -285,6 +287,7 @@ struct BcastGeom {
 // are loaded before any is computed, as in ew_vec_kernel, so that several 128-bit loads are in flight per thread.
 template <int NIN, int NOUT, class F, int VEC, typename IDX>
 __global__ void __launch_bounds__(kThreads) bcast_kernel(Ptrs<NIN, NOUT> p, BcastGeom<NIN> g, size_t n_groups, F f) {
+    grid_dependency_sync();
     const size_t step = (size_t)gridDim.x * kThreads * kUnroll;
     const unsigned d0 = g.dims[0] / VEC;
     for (size_t base = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < n_groups; base += step) {
@@ -393,10 +396,10 @@ bool launch_bcast(Ptrs<NIN, NOUT> p, const size_t* dims, int rank, const size_t*
     const size_t n_groups = vec ? n / 4 : n;
     const int grid = grid_for(n_groups, c->sm_count);
     const bool small = n_groups <= 0xFFFFFFFFull;
-    if (vec && small) bcast_kernel<NIN, NOUT, F, 4, unsigned><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
-    else if (vec) bcast_kernel<NIN, NOUT, F, 4, size_t><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
-    else if (small) bcast_kernel<NIN, NOUT, F, 1, unsigned><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
-    else bcast_kernel<NIN, NOUT, F, 1, size_t><<<grid, kThreads, 0, s>>>(p, g, n_groups, f);
+    if (vec && small) launch_dep(bcast_kernel<NIN, NOUT, F, 4, unsigned>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+    else if (vec) launch_dep(bcast_kernel<NIN, NOUT, F, 4, size_t>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+    else if (small) launch_dep(bcast_kernel<NIN, NOUT, F, 1, unsigned>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+    else launch_dep(bcast_kernel<NIN, NOUT, F, 1, size_t>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
     return cuda_ok(cudaGetLastError(), "broadcast launch");
 }
 
@@ -586,13 +589,13 @@ bool bias_act(const float* z, const float* bias, float* o, size_t rows, size_t c
         size_t n_vec = n / 4;
         size_t want = (n_vec + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm * 2;
         int grid = (int)(want < cap ? want : cap);
-        if (relu_on) bias_act_vec_kernel<true><<<grid, kThreads, 0, s>>>((const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
-        else bias_act_vec_kernel<false><<<grid, kThreads, 0, s>>>((const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
+        if (relu_on) launch_dep(bias_act_vec_kernel<true>, dim3(grid), dim3(kThreads), 0, s, (const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
+        else launch_dep(bias_act_vec_kernel<false>, dim3(grid), dim3(kThreads), 0, s, (const float4*)z, (const float4*)bias, (float4*)o, n_vec, (unsigned)(cols / 4));
     } else {
         size_t want = (n + kThreads - 1) / kThreads, cap = (size_t)c->sm_count * kCtasPerSm * 2;
         int grid = (int)(want < cap ? want : cap);
-        if (relu_on) bias_act_scalar_kernel<true><<<grid, kThreads, 0, s>>>(z, bias, o, n, cols);
-        else bias_act_scalar_kernel<false><<<grid, kThreads, 0, s>>>(z, bias, o, n, cols);
+        if (relu_on) launch_dep(bias_act_scalar_kernel<true>, dim3(grid), dim3(kThreads), 0, s, z, bias, o, n, cols);
+        else launch_dep(bias_act_scalar_kernel<false>, dim3(grid), dim3(kThreads), 0, s, z, bias, o, n, cols);
     }
     return cuda_ok(cudaGetLastError(), "bias_act launch");
 }

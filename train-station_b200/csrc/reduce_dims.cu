@@ -70,6 +70,7 @@ __device__ __forceinline__ float combine(float acc, float t) {
 template <int OP>
 __global__ void __launch_bounds__(kThreads) reduce_kept_inner_kernel(const float* __restrict__ x, const float* __restrict__ aux,
                                                                      float* __restrict__ out, Plan p, size_t chunk) {
+    grid_dependency_sync();
     const size_t o = (size_t)blockIdx.x * kThreads + threadIdx.x;
     if (o >= p.n_out) return;
     const size_t base = radix_offset(o, p.kdim, p.kstr, p.nk);
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(kThreads) reduce_kept_inner_kernel(const float
 template <int OP>
 __global__ void __launch_bounds__(kThreads) reduce_kept_inner_vec4_kernel(const float* __restrict__ x, const float* __restrict__ aux,
                                                                           float* __restrict__ out, Plan p, size_t chunk) {
+    grid_dependency_sync();
     const size_t o = ((size_t)blockIdx.x * kThreads + threadIdx.x) * 4;
     if (o >= p.n_out) return;
     const size_t base = radix_offset(o, p.kdim, p.kstr, p.nk);
@@ -128,6 +130,7 @@ __global__ void __launch_bounds__(kThreads) reduce_kept_inner_vec4_kernel(const 
 template <int OP>
 __global__ void __launch_bounds__(kThreads) reduce_reduced_inner_kernel(const float* __restrict__ x, const float* __restrict__ aux,
                                                                         float* __restrict__ out, Plan p, size_t chunk, size_t splits) {
+    grid_dependency_sync();
     const int lane = threadIdx.x & 31;
     const size_t units = p.n_out * splits;
     for (size_t u = (size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); u < units; u += (size_t)gridDim.x * (kThreads / 32)) {
@@ -207,13 +210,13 @@ bool launch_forward(const float* x, const float* aux, float* out, const Plan& p,
     float* dst = splits > 1 ? scratch : out;
     if (reduced_inner) {
         const size_t units = p.n_out * splits, want = (units + 7) / 8, cap = (size_t)sm * 32;
-        reduce_reduced_inner_kernel<OP><<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(x, aux, dst, p, chunk, splits);
+        launch_dep(reduce_reduced_inner_kernel<OP>, dim3((unsigned)(want < cap ? want : cap)), dim3(kThreads), 0, s, x, aux, dst, p, chunk, splits);
     } else if (vec4) {
         dim3 grid((unsigned)((p.n_out / 4 + kThreads - 1) / kThreads), (unsigned)splits);
-        reduce_kept_inner_vec4_kernel<OP><<<grid, kThreads, 0, s>>>(x, aux, dst, p, chunk);
+        launch_dep(reduce_kept_inner_vec4_kernel<OP>, dim3(grid), dim3(kThreads), 0, s, x, aux, dst, p, chunk);
     } else {
         dim3 grid((unsigned)((p.n_out + kThreads - 1) / kThreads), (unsigned)splits);
-        reduce_kept_inner_kernel<OP><<<grid, kThreads, 0, s>>>(x, aux, dst, p, chunk);
+        launch_dep(reduce_kept_inner_kernel<OP>, dim3(grid), dim3(kThreads), 0, s, x, aux, dst, p, chunk);
     }
     if (!cuda_ok(cudaGetLastError(), "reduce_dims launch")) return false;
     if (splits > 1) {
@@ -226,10 +229,10 @@ bool launch_forward(const float* x, const float* aux, float* out, const Plan& p,
         if (splits > 32) {
             // many partials per output (few outputs): a warp per output instead of one thread walking them all
             const size_t want = (p.n_out + 7) / 8, cap = (size_t)sm * 32;
-            reduce_reduced_inner_kernel<OP2><<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(scratch, nullptr, out, q, splits, 1);
+            launch_dep(reduce_reduced_inner_kernel<OP2>, dim3((unsigned)(want < cap ? want : cap)), dim3(kThreads), 0, s, scratch, nullptr, out, q, splits, 1);
         } else {
             dim3 grid((unsigned)((p.n_out + kThreads - 1) / kThreads), 1);
-            reduce_kept_inner_kernel<OP2><<<grid, kThreads, 0, s>>>(scratch, nullptr, out, q, splits);
+            launch_dep(reduce_kept_inner_kernel<OP2>, dim3(grid), dim3(kThreads), 0, s, scratch, nullptr, out, q, splits);
         }
         if (!cuda_ok(cudaGetLastError(), "reduce_dims combine launch")) return false;
     }
@@ -248,6 +251,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads) reduce_bwd_kernel(const float* __restrict__ x, const float* __restrict__ a1, const float* __restrict__ a2,
                                                               const float* __restrict__ go, float* __restrict__ gi, size_t n, BwdPlan p,
                                                               int go_is_scalar, float scale) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * kThreads;
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
         const size_t o = radix_offset(i, p.dim, p.ostr, p.n);
@@ -359,12 +363,12 @@ bool reduce_dims_backward(int mode, const float* x, const float* a1, const float
     const unsigned grid = (unsigned)(want < cap ? want : cap);
     const int gs = go_is_scalar ? 1 : 0;
     switch (mode) {
-        case kBwdSum: reduce_bwd_kernel<kBwdSum><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
-        case kBwdScaled: reduce_bwd_kernel<kBwdScaled><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
-        case kBwdExtremum: reduce_bwd_kernel<kBwdExtremum><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
-        case kBwdNorm: reduce_bwd_kernel<kBwdNorm><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
-        case kBwdVar: reduce_bwd_kernel<kBwdVar><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
-        case kBwdStd: reduce_bwd_kernel<kBwdStd><<<grid, kThreads, 0, s>>>(x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdSum: launch_dep(reduce_bwd_kernel<kBwdSum>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdScaled: launch_dep(reduce_bwd_kernel<kBwdScaled>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdExtremum: launch_dep(reduce_bwd_kernel<kBwdExtremum>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdNorm: launch_dep(reduce_bwd_kernel<kBwdNorm>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdVar: launch_dep(reduce_bwd_kernel<kBwdVar>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
+        case kBwdStd: launch_dep(reduce_bwd_kernel<kBwdStd>, dim3(grid), dim3(kThreads), 0, s, x, a1, a2, go, gi, n, b, gs, scale); break;
         default: set_error("reduce_dims_backward: unknown mode %d", mode); return false;
     }
     return cuda_ok(cudaGetLastError(), "reduce_dims backward launch");

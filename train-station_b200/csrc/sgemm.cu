@@ -68,6 +68,7 @@ __device__ __forceinline__ void tile_store(float (*sm)[BM], const float (&r)[8])
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
+    grid_dependency_sync();
     g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
     g.b += (size_t)blockIdx.z * g.batch_stride_b;
     g.c += (size_t)blockIdx.z * g.m * g.n;
@@ -175,8 +176,8 @@ __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
 
 template <bool TA, bool TB>
 void launch(const GemmArgs& g, dim3 grid, cudaStream_t s) {
-    if (g.n % 8 != 0) sgemm_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
-    else sgemm_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+    if (g.n % 8 != 0) launch_dep(sgemm_kernel<TA, TB, true>, dim3(grid), dim3(kThreads), 0, s, g);
+    else launch_dep(sgemm_kernel<TA, TB, false>, dim3(grid), dim3(kThreads), 0, s, g);
 }
 
 // The same arithmetic on 32 x 32 tiles (2 x 2 outputs per thread, 32 k per stage) for results that would fill only a
@@ -195,6 +196,7 @@ __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gmem_src
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
+    grid_dependency_sync();
     g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
     g.b += (size_t)blockIdx.z * g.batch_stride_b;
     g.c += (size_t)blockIdx.z * g.m * g.n;
@@ -277,8 +279,8 @@ __global__ void __launch_bounds__(kThreads) sgemm_small_kernel(GemmArgs g) {
 
 template <bool TA, bool TB>
 void launch_small(const GemmArgs& g, dim3 grid, cudaStream_t s) {
-    if (g.n % 8 != 0) sgemm_small_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
-    else sgemm_small_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+    if (g.n % 8 != 0) launch_dep(sgemm_small_kernel<TA, TB, true>, dim3(grid), dim3(kThreads), 0, s, g);
+    else launch_dep(sgemm_small_kernel<TA, TB, false>, dim3(grid), dim3(kThreads), 0, s, g);
 }
 
 // The smallest tiling: 16 x 16 tiles, 64 threads, 2 x 2 outputs per thread, 64 k per stage, for results of fewer than
@@ -289,6 +291,7 @@ constexpr int TN_T = 16, TN_K = 64, TN_THREADS = 64, TN_PITCH = TN_T + 2;    // 
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(TN_THREADS) sgemm_tiny_kernel(GemmArgs g) {
+    grid_dependency_sync();
     g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
     g.b += (size_t)blockIdx.z * g.batch_stride_b;
     g.c += (size_t)blockIdx.z * g.m * g.n;
@@ -367,8 +370,8 @@ __global__ void __launch_bounds__(TN_THREADS) sgemm_tiny_kernel(GemmArgs g) {
 
 template <bool TA, bool TB>
 void launch_tiny(const GemmArgs& g, dim3 grid, cudaStream_t s) {
-    if (g.n % 8 != 0) sgemm_tiny_kernel<TA, TB, true><<<grid, TN_THREADS, 0, s>>>(g);
-    else sgemm_tiny_kernel<TA, TB, false><<<grid, TN_THREADS, 0, s>>>(g);
+    if (g.n % 8 != 0) launch_dep(sgemm_tiny_kernel<TA, TB, true>, dim3(grid), dim3(TN_THREADS), 0, s, g);
+    else launch_dep(sgemm_tiny_kernel<TA, TB, false>, dim3(grid), dim3(TN_THREADS), 0, s, g);
 }
 
 // Between the two: 64 x 64 tiles, 4 x 4 outputs per thread, 16 k per stage through the same ring of asynchronous
@@ -379,6 +382,7 @@ constexpr int MD_T = 64, MD_K = 16, MD_PITCH = MD_T + 4;     // rows stay 16-byt
 
 template <bool TA, bool TB, bool HAS_TAIL>
 __global__ void __launch_bounds__(kThreads) sgemm_mid_kernel(GemmArgs g) {
+    grid_dependency_sync();
     g.a += (size_t)blockIdx.z * g.batch_stride_a;     // one product per grid z (a batch of 1 has strides 0)
     g.b += (size_t)blockIdx.z * g.batch_stride_b;
     g.c += (size_t)blockIdx.z * g.m * g.n;
@@ -466,8 +470,8 @@ __global__ void __launch_bounds__(kThreads) sgemm_mid_kernel(GemmArgs g) {
 
 template <bool TA, bool TB>
 void launch_mid(const GemmArgs& g, dim3 grid, cudaStream_t s) {
-    if (g.n % 8 != 0) sgemm_mid_kernel<TA, TB, true><<<grid, kThreads, 0, s>>>(g);
-    else sgemm_mid_kernel<TA, TB, false><<<grid, kThreads, 0, s>>>(g);
+    if (g.n % 8 != 0) launch_dep(sgemm_mid_kernel<TA, TB, true>, dim3(grid), dim3(kThreads), 0, s, g);
+    else launch_dep(sgemm_mid_kernel<TA, TB, false>, dim3(grid), dim3(kThreads), 0, s, g);
 }
 
 }  // namespace

@@ -74,6 +74,7 @@ struct RowsCfg {
 template <int G, bool CACHED>
 __global__ void __launch_bounds__(RowsCfg<G>::kCta) softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ y, size_t rows,
                                                                         size_t reduce) {
+    grid_dependency_sync();
     constexpr int RPC = RowsCfg<G>::kRpc;
     __shared__ float red[32];
     const int g = threadIdx.x / G, t = threadIdx.x % G;
@@ -134,6 +135,7 @@ __global__ void __launch_bounds__(RowsCfg<G>::kCta) softmax_rows_kernel(const fl
 template <int G, bool CACHED>
 __global__ void __launch_bounds__(RowsCfg<G>::kCta) softmax_bwd_rows_kernel(const float* __restrict__ y, const float* __restrict__ go,
                                                                             float* __restrict__ gi, size_t rows, size_t reduce) {
+    grid_dependency_sync();
     constexpr int RPC = RowsCfg<G>::kRpc;
     __shared__ float red[32];
     const int g = threadIdx.x / G, t = threadIdx.x % G;
@@ -220,6 +222,7 @@ struct ShortTile {
 
 template <int RMAX>   // reduce <= RMAX: sizes the staging tile and the prefetch registers
 __global__ void __launch_bounds__(kShortThreads) softmax_short_kernel(const float* __restrict__ x, float* __restrict__ y, size_t rows, int reduce) {
+    grid_dependency_sync();
     constexpr int TR = 256, NU = TR * RMAX / kShortThreads;
     using Tile = ShortTile<TR, NU>;
     __shared__ float tile[RMAX * (TR + 1)];
@@ -270,6 +273,7 @@ __global__ void __launch_bounds__(kShortThreads) softmax_short_kernel(const floa
 template <int RMAX>
 __global__ void __launch_bounds__(kShortThreads) softmax_short_warp_kernel(const float* __restrict__ x, float* __restrict__ y, size_t rows,
                                                                           int reduce) {
+    grid_dependency_sync();
     __shared__ __align__(16) float stage[kShortThreads / 32][32 * RMAX];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* st = stage[warp];
@@ -316,6 +320,7 @@ __global__ void __launch_bounds__(kShortThreads) softmax_short_warp_kernel(const
 template <int RMAX>
 __global__ void __launch_bounds__(kShortThreads) softmax_bwd_short_kernel(const float* __restrict__ y, const float* __restrict__ go,
                                                                           float* __restrict__ gi, size_t rows, int reduce) {
+    grid_dependency_sync();
     constexpr int TR = 128, NU = TR * RMAX / kShortThreads;
     using Tile = ShortTile<TR, NU>;
     __shared__ float ty[RMAX * (TR + 1)];
@@ -364,6 +369,7 @@ __device__ __forceinline__ float cross_warp(float v, float (*red)[32]) {
 template <int W, bool CACHED>
 __global__ void __launch_bounds__(32 * W) softmax_cols_kernel(const float* __restrict__ x, float* __restrict__ y, size_t outer, size_t reduce,
                                                               size_t inner) {
+    grid_dependency_sync();
     __shared__ float red[W][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t itiles = (inner + 31) / 32, tiles = outer * itiles;
@@ -423,6 +429,7 @@ __global__ void __launch_bounds__(32 * W) softmax_cols_kernel(const float* __res
 template <int W, bool CACHED>
 __global__ void __launch_bounds__(32 * W) softmax_bwd_cols_kernel(const float* __restrict__ y, const float* __restrict__ go,
                                                                   float* __restrict__ gi, size_t outer, size_t reduce, size_t inner) {
+    grid_dependency_sync();
     __shared__ float red[W][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t itiles = (inner + 31) / 32, tiles = outer * itiles;
@@ -511,6 +518,7 @@ __device__ __forceinline__ float cross_groups(float v, float* red) {
 template <int TI>
 __global__ void __launch_bounds__(kStagedThreads) softmax_cols_staged_kernel(const float* __restrict__ x, float* __restrict__ y, size_t outer,
                                                                              size_t reduce, size_t inner) {
+    grid_dependency_sync();
     constexpr int JG = kStagedThreads / TI;
     extern __shared__ __align__(16) float smem[];
     const size_t tile_elems = reduce * TI;   // buffer b starts at smem + b * tile_elems
@@ -552,6 +560,7 @@ __global__ void __launch_bounds__(kStagedThreads) softmax_cols_staged_kernel(con
 template <int TI>
 __global__ void __launch_bounds__(kStagedThreads) softmax_bwd_cols_staged_kernel(const float* __restrict__ y, const float* __restrict__ go,
                                                                                  float* __restrict__ gi, size_t outer, size_t reduce, size_t inner) {
+    grid_dependency_sync();
     constexpr int JG = kStagedThreads / TI;
     extern __shared__ __align__(16) float smem[];
     const size_t tile_elems = reduce * TI;
@@ -601,10 +610,10 @@ bool launch_cols_staged(bool bwd, const float* a, const float* b, float* o, size
     const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
     if (bwd) {
         if (!cuda_ok(cudaFuncSetAttribute(softmax_bwd_cols_staged_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), "softmax smem")) return false;
-        softmax_bwd_cols_staged_kernel<TI><<<grid, kStagedThreads, bytes, s>>>(a, b, o, outer, reduce, inner);
+        launch_dep(softmax_bwd_cols_staged_kernel<TI>, dim3(grid), dim3(kStagedThreads), bytes, s, a, b, o, outer, reduce, inner);
     } else {
         if (!cuda_ok(cudaFuncSetAttribute(softmax_cols_staged_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), "softmax smem")) return false;
-        softmax_cols_staged_kernel<TI><<<grid, kStagedThreads, bytes, s>>>(a, o, outer, reduce, inner);
+        launch_dep(softmax_cols_staged_kernel<TI>, dim3(grid), dim3(kStagedThreads), bytes, s, a, o, outer, reduce, inner);
     }
     return true;
 }
@@ -639,22 +648,22 @@ template <int G>
 void launch_rows(bool bwd, const float* a, const float* b, float* o, size_t rows, size_t reduce, int sm, cudaStream_t s) {
     constexpr int CTA = RowsCfg<G>::kCta, RPC = RowsCfg<G>::kRpc;
     const int grid = grid_for((rows + RPC - 1) / RPC, sm, CTA);
-    if (bwd) softmax_bwd_rows_kernel<G, true><<<grid, CTA, 0, s>>>(a, b, o, rows, reduce);
-    else softmax_rows_kernel<G, true><<<grid, CTA, 0, s>>>(a, o, rows, reduce);
+    if (bwd) launch_dep(softmax_bwd_rows_kernel<G, true>, dim3(grid), dim3(CTA), 0, s, a, b, o, rows, reduce);
+    else launch_dep(softmax_rows_kernel<G, true>, dim3(grid), dim3(CTA), 0, s, a, o, rows, reduce);
 }
 template <int W>
 void launch_cols(bool bwd, const float* a, const float* b, float* o, size_t outer, size_t reduce, size_t inner, int sm, cudaStream_t s) {
     const int grid = grid_for(outer * ((inner + 31) / 32), sm, 32 * W);
-    if (bwd) softmax_bwd_cols_kernel<W, true><<<grid, 32 * W, 0, s>>>(a, b, o, outer, reduce, inner);
-    else softmax_cols_kernel<W, true><<<grid, 32 * W, 0, s>>>(a, o, outer, reduce, inner);
+    if (bwd) launch_dep(softmax_bwd_cols_kernel<W, true>, dim3(grid), dim3(32 * W), 0, s, a, b, o, outer, reduce, inner);
+    else launch_dep(softmax_cols_kernel<W, true>, dim3(grid), dim3(32 * W), 0, s, a, o, outer, reduce, inner);
 }
 
 template <int RMAX>
 void launch_short(bool bwd, const float* a, const float* b, float* o, size_t rows, int reduce, int sm, cudaStream_t s) {
-    if (bwd) softmax_bwd_short_kernel<RMAX><<<grid_for((rows + 127) / 128, sm, kShortThreads), kShortThreads, 0, s>>>(a, b, o, rows, reduce);
+    if (bwd) launch_dep(softmax_bwd_short_kernel<RMAX>, dim3(grid_for((rows + 127) / 128, sm, kShortThreads)), dim3(kShortThreads), 0, s, a, b, o, rows, reduce);
     else if (reduce % 4 != 0)   // the row pitch repeats over the banks at most every second lane
-        softmax_short_warp_kernel<RMAX><<<grid_for((rows + kShortThreads - 1) / kShortThreads, sm, kShortThreads), kShortThreads, 0, s>>>(a, o, rows, reduce);
-    else softmax_short_kernel<RMAX><<<grid_for((rows + 255) / 256, sm, kShortThreads), kShortThreads, 0, s>>>(a, o, rows, reduce);
+        launch_dep(softmax_short_warp_kernel<RMAX>, dim3(grid_for((rows + kShortThreads - 1) / kShortThreads, sm, kShortThreads)), dim3(kShortThreads), 0, s, a, o, rows, reduce);
+    else launch_dep(softmax_short_kernel<RMAX>, dim3(grid_for((rows + 255) / 256, sm, kShortThreads)), dim3(kShortThreads), 0, s, a, o, rows, reduce);
 }
 
 // forward: a = x, b unused; backward: a = y, b = go
@@ -669,8 +678,8 @@ void dispatch(bool bwd, const float* a, const float* b, float* o, size_t outer, 
         else if (reduce <= 256 * kV) launch_rows<256>(bwd, a, b, o, outer, reduce, sm, s);
         else if (reduce <= 512 * kV) launch_rows<512>(bwd, a, b, o, outer, reduce, sm, s);
         else if (reduce <= 1024 * kV) launch_rows<1024>(bwd, a, b, o, outer, reduce, sm, s);
-        else if (bwd) softmax_bwd_rows_kernel<256, false><<<grid_for(outer, sm, 256), 256, 0, s>>>(a, b, o, outer, reduce);
-        else softmax_rows_kernel<256, false><<<grid_for(outer, sm, 256), 256, 0, s>>>(a, o, outer, reduce);
+        else if (bwd) launch_dep(softmax_bwd_rows_kernel<256, false>, dim3(grid_for(outer, sm, 256)), dim3(256), 0, s, a, b, o, outer, reduce);
+        else launch_dep(softmax_rows_kernel<256, false>, dim3(grid_for(outer, sm, 256)), dim3(256), 0, s, a, o, outer, reduce);
     } else {
         if (try_cols_staged(bwd, a, b, o, outer, reduce, inner, sm, s)) return;
         if (reduce <= 8 * kV) launch_cols<8>(bwd, a, b, o, outer, reduce, inner, sm, s);
@@ -678,8 +687,8 @@ void dispatch(bool bwd, const float* a, const float* b, float* o, size_t outer, 
         else if (reduce <= 32 * kV) launch_cols<32>(bwd, a, b, o, outer, reduce, inner, sm, s);
         else {
             const int grid = grid_for(outer * ((inner + 31) / 32), sm, 256);
-            if (bwd) softmax_bwd_cols_kernel<8, false><<<grid, 256, 0, s>>>(a, b, o, outer, reduce, inner);
-            else softmax_cols_kernel<8, false><<<grid, 256, 0, s>>>(a, o, outer, reduce, inner);
+            if (bwd) launch_dep(softmax_bwd_cols_kernel<8, false>, dim3(grid), dim3(256), 0, s, a, b, o, outer, reduce, inner);
+            else launch_dep(softmax_cols_kernel<8, false>, dim3(grid), dim3(256), 0, s, a, o, outer, reduce, inner);
         }
     }
 }

@@ -23,6 +23,7 @@ constexpr int kTile = 64;
 
 __global__ void __launch_bounds__(256) transpose_tiles_kernel(const float* __restrict__ in, float* __restrict__ out, size_t rows, size_t cols,
                                                               size_t tiles_r, size_t tiles_c, size_t n_tiles) {
+    grid_dependency_sync();
     __shared__ float tile[kTile][kTile + 1];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8 threads, sixteen elements each
     for (size_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
@@ -59,6 +60,7 @@ struct GatherPlan {
 };
 
 __global__ void __launch_bounds__(256) permute_gather_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n, GatherPlan p) {
+    grid_dependency_sync();
     const size_t stride = (size_t)gridDim.x * 256;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
         size_t rem = i, off = 0;
@@ -114,14 +116,14 @@ bool permute(const float* in, float* out, const size_t* dims, const int* perm, i
         const size_t rows = out_cols, cols = out_rows;             // input matrix is [rows][cols]
         const size_t tiles_r = (rows + kTile - 1) / kTile, tiles_c = (cols + kTile - 1) / kTile, n_tiles = batch * tiles_r * tiles_c;
         const size_t cap = (size_t)c->sm_count * 16;
-        transpose_tiles_kernel<<<(unsigned)(n_tiles < cap ? n_tiles : cap), 256, 0, s>>>(in, out, rows, cols, tiles_r, tiles_c, n_tiles);
+        launch_dep(transpose_tiles_kernel, dim3((unsigned)(n_tiles < cap ? n_tiles : cap)), dim3(256), 0, s, in, out, rows, cols, tiles_r, tiles_c, n_tiles);
         return cuda_ok(cudaGetLastError(), "transpose launch");
     }
     GatherPlan p;
     p.rank = r;
     for (int i = 0; i < kMaxRank; ++i) { p.out_dims[i] = i < r ? od[i] : 1; p.in_strides[i] = i < r ? os[i] : 0; }
     const size_t want = (n + 255) / 256, cap = (size_t)c->sm_count * 16;
-    permute_gather_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, s>>>(in, out, n, p);
+    launch_dep(permute_gather_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, s, in, out, n, p);
     return cuda_ok(cudaGetLastError(), "permute launch");
 }
 
