@@ -177,6 +177,10 @@ bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch
 bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial_rows, cudaStream_t s);
 bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols,
                      float* scratch, cudaStream_t s);
+// mse_grad (elementwise.cu) over a [rows x cols] prediction plus, from the same pass, the column sums of the stored
+// gradient: the gradient of the bias that was added to make the prediction.
+bool mse_grad_colsum(const float* y, const float* t, const float* upstream, float inv_n, float* gy, float* bias_grad, size_t rows,
+                     size_t cols, bool round_tf32, float* scratch, cudaStream_t s);
 
 struct AdamTensor {
     float* p;

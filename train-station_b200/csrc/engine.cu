@@ -1022,23 +1022,45 @@ static bool apply_node(DeviceCtx* c, uint64_t out_id, Node& nd, const TensorP& g
                     // wants a gradient, this gradient's consumers are that matmul's two backward GEMMs and the bias
                     // column sum: store it already rounded to TF32, as a deferred GEMM that produces a gradient does.
                     bool round_out = false;
-                    if (matmul_precision() == 1) {
-                        auto sub = g_graph.ops.find(nd.inputs[0]);
-                        if (sub != g_graph.ops.end() && sub->second.op == Op::Sub && sub->second.needs[0] && !sub->second.needs[1]) {
-                            auto prod = g_graph.ops.find(sub->second.inputs[0]);
-                            if (prod != g_graph.ops.end() && prod->second.op == Op::Add) {
-                                // a row-bias add only: the other operand is the matmul result, the bias gets a column sum
-                                if (prod->second.dims0 != prod->second.dims1) {
-                                    const int big = prod->second.dims0.size() >= prod->second.dims1.size() ? 0 : 1;
-                                    auto mm = g_graph.ops.find(prod->second.inputs[big]);
-                                    round_out = mm != g_graph.ops.end() && mm->second.op == Op::MatMul;
+                    // When the minuend is (matmul result) + (row bias) and only it wants a gradient, the same pass also
+                    // yields the bias gradient (the column sums of this gradient), handed to the Add node's backward.
+                    uint64_t add_id = 0;
+                    size_t bias_rows = 0, bias_cols = 0;
+                    auto sub = g_graph.ops.find(nd.inputs[0]);
+                    if (sub != g_graph.ops.end() && sub->second.op == Op::Sub && sub->second.needs[0] && !sub->second.needs[1]) {
+                        auto prod = g_graph.ops.find(sub->second.inputs[0]);
+                        if (prod != g_graph.ops.end() && prod->second.op == Op::Add) {
+                            // a row-bias add only: the other operand is the matmul result, the bias gets a column sum
+                            if (prod->second.dims0 != prod->second.dims1) {
+                                const int big = prod->second.dims0.size() >= prod->second.dims1.size() ? 0 : 1;
+                                auto mm = g_graph.ops.find(prod->second.inputs[big]);
+                                if (matmul_precision() == 1) round_out = mm != g_graph.ops.end() && mm->second.op == Op::MatMul;
+                                const std::vector<size_t>& od = big == 0 ? prod->second.dims1 : prod->second.dims0;
+                                const std::vector<size_t>& other = big == 0 ? prod->second.dims0 : prod->second.dims1;
+                                size_t osz = 1; for (size_t v : od) osz *= v;
+                                size_t rows, cols;
+                                if (prod->second.needs[1 - big] && osz != r->size && is_suffix_broadcast(other, od, &rows, &cols) && cols > 1 &&
+                                    rows * cols == r->size && g_graph.grads.find(sub->second.inputs[0]) == g_graph.grads.end()) {
+                                    add_id = sub->second.inputs[0]; bias_rows = rows; bias_cols = cols;
                                 }
-                            } else {
-                                round_out = prod != g_graph.ops.end() && prod->second.op == Op::MatMul;
                             }
+                        } else if (matmul_precision() == 1) {
+                            round_out = prod != g_graph.ops.end() && prod->second.op == Op::MatMul;
                         }
                     }
-                    if (!pa || !pb || !k::mse_grad(pa, pb, up, scale, r->st->ptr, r->size, round_out, s)) return false;
+                    if (!pa || !pb) return false;
+                    if (add_id) {
+                        TensorP db = new_tensor(c, {bias_cols});
+                        if (!db) return false;
+                        float* scratch = c->alloc.alloc(k::colsum_scratch_elems(bias_rows, bias_cols) * sizeof(float));
+                        if (!scratch) return false;
+                        const bool ok = k::mse_grad_colsum(pa, pb, up, scale, r->st->ptr, db->st->ptr, bias_rows, bias_cols, round_out, scratch, s);
+                        c->alloc.free(scratch);   // reused only by later work on the same stream
+                        if (!ok) return false;
+                        g_graph.bias_grad_ready[add_id] = db;
+                    } else if (!k::mse_grad(pa, pb, up, scale, r->st->ptr, r->size, round_out, s)) {
+                        return false;
+                    }
                     r->st->tf32_clean = round_out;
                 } else {
                     const float* px = rptr(x);

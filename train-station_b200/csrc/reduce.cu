@@ -155,16 +155,39 @@ ColsumPlan plan_colsum(size_t rows, size_t cols, int sm_count, bool aligned) {
     return p;
 }
 
-// FUSED: gi = ref > 0 ? go : 0 is written and its column sums accumulated; otherwise plain sums of g.
-template <bool FUSED, bool VEC>
+// What stage 1 sums.  Plain: the columns of g.  ReluBwd: gi = ref > 0 ? g : 0 is written and its columns summed.
+// MseGrad: gi = (inv_n * *upstream) * (2 * (g - ref)), optionally rounded to TF32, is written and its columns summed:
+// the gradient of mean((y - t)^2) with respect to y and, in the same pass, of the bias that was added to make y
+// (the operations and their order are those of the stand-alone gradient kernel, so the bits are the same).
+enum ColsumMode { kColsumPlain = 0, kColsumReluBwd = 1, kColsumMseGrad = 2 };
+struct ColsumExtra { const float* upstream; float inv_n; int round_tf32; };
+
+template <int MODE>
+__device__ __forceinline__ float colsum_value(float g, float ref, float sc, int round_tf32) {
+    if (MODE == kColsumReluBwd) return ref > 0.0f ? g : 0.0f;
+    if (MODE == kColsumMseGrad) {
+        float v = __fmul_rn(sc, __fmul_rn(2.0f, __fsub_rn(g, ref)));
+        if (round_tf32) {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+            v = __uint_as_float(r);
+        }
+        return v;
+    }
+    return g;
+}
+
+template <int MODE, bool VEC>
 __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restrict__ g, const float* __restrict__ ref,
                                                           float* __restrict__ gi, float* __restrict__ partial, size_t rows,
-                                                          size_t cols, size_t rows_per_split) {
+                                                          size_t cols, size_t rows_per_split, ColsumExtra ex) {
     grid_dependency_sync();
+    constexpr bool FUSED = MODE != kColsumPlain;
     const int cl = threadIdx.x % kColLanes, rl = threadIdx.x / kColLanes;
     const size_t r0 = (size_t)blockIdx.y * rows_per_split;
     size_t r1 = r0 + rows_per_split;
     if (r1 > rows) r1 = rows;
+    const float sc = MODE == kColsumMseGrad ? __fmul_rn(ex.inv_n, __ldg(ex.upstream)) : 0.0f;
     __shared__ float4 sm[kRowLanes][kColLanes];
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (VEC) {
@@ -186,8 +209,8 @@ __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restric
                 float4 v = __ldcs(reinterpret_cast<const float4*>(g) + off);
                 if (FUSED) {
                     float4 x = __ldcs(reinterpret_cast<const float4*>(ref) + off);
-                    v.x = x.x > 0.0f ? v.x : 0.0f; v.y = x.y > 0.0f ? v.y : 0.0f;
-                    v.z = x.z > 0.0f ? v.z : 0.0f; v.w = x.w > 0.0f ? v.w : 0.0f;
+                    v.x = colsum_value<MODE>(v.x, x.x, sc, ex.round_tf32); v.y = colsum_value<MODE>(v.y, x.y, sc, ex.round_tf32);
+                    v.z = colsum_value<MODE>(v.z, x.z, sc, ex.round_tf32); v.w = colsum_value<MODE>(v.w, x.w, sc, ex.round_tf32);
                     __stcs(reinterpret_cast<float4*>(gi) + off, v);
                 }
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -199,7 +222,7 @@ __global__ void __launch_bounds__(kThreads) colsum_stage1(const float* __restric
             for (size_t r = r0 + rl; r < r1; r += kRowLanes) {
                 size_t off = r * cols + col;
                 float v = g[off];
-                if (FUSED) { v = ref[off] > 0.0f ? v : 0.0f; gi[off] = v; }
+                if (FUSED) { v = colsum_value<MODE>(v, ref[off], sc, ex.round_tf32); gi[off] = v; }
                 acc.x += v;
             }
         }
@@ -260,14 +283,16 @@ __global__ void __launch_bounds__(256) colsum_rows_kernel(const float* __restric
     }
 }
 
-template <bool FUSED>
-bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
+template <int MODE>
+bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s,
+                 ColsumExtra ex = ColsumExtra{nullptr, 0.0f, 0}) {
+    constexpr bool FUSED = MODE != kColsumPlain;
     if (cols == 0) return true;
     if (!out) { set_error("colsum: null output"); return false; }
     DeviceCtx* c = ctx();
     if (!c) return false;
     if (rows == 0) return fill(out, 0.0f, cols, s);
-    if (!g || (FUSED && (!ref || !gi))) { set_error("colsum: null pointer"); return false; }
+    if (!g || (FUSED && (!ref || !gi)) || (MODE == kColsumMseGrad && !ex.upstream)) { set_error("colsum: null pointer"); return false; }
     bool aligned = (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
                    (!FUSED || ((reinterpret_cast<uintptr_t>(ref) & 15) == 0 && (reinterpret_cast<uintptr_t>(gi) & 15) == 0));
     ColsumPlan p = plan_colsum(rows, cols, c->sm_count, aligned);
@@ -275,8 +300,8 @@ bool colsum_impl(const float* g, const float* ref, float* gi, float* out, size_t
     float* partial = p.splits > 1 ? scratch : out;
     dim3 grid(p.col_tiles, p.splits);
     ProfScope prof(kProfReduce, s, 4.0 * (double)rows * (double)cols * (FUSED ? 3 : 1), p.splits > 1 ? 2 : 1);
-    if (p.vec) launch_dep(colsum_stage1<FUSED, true>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split);
-    else launch_dep(colsum_stage1<FUSED, false>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split);
+    if (p.vec) launch_dep(colsum_stage1<MODE, true>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split, ex);
+    else launch_dep(colsum_stage1<MODE, false>, grid, dim3(kThreads), 0, s, g, ref, gi, partial, rows, cols, p.rows_per_split, ex);
     if (p.splits > 1) launch_dep(colsum_stage2, dim3((unsigned)((cols + kThreads - 1) / kThreads)), dim3(kThreads), 0, s, partial, out, cols, (int)p.splits);
     return cuda_ok(cudaGetLastError(), "colsum launch");
 }
@@ -298,7 +323,7 @@ size_t colsum_scratch_elems(size_t rows, size_t cols) {
     return s * cols;
 }
 bool colsum(const float* g, float* out, size_t rows, size_t cols, float* scratch, cudaStream_t s) {
-    return colsum_impl<false>(g, nullptr, nullptr, out, rows, cols, scratch, s);
+    return colsum_impl<kColsumPlain>(g, nullptr, nullptr, out, rows, cols, scratch, s);
 }
 bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial_rows, cudaStream_t s) {
     if (cols == 0) return true;
@@ -309,7 +334,11 @@ bool colsum_finish(const float* partial, float* out, size_t cols, size_t partial
 }
 bool relu_bwd_colsum(const float* ref, const float* go, float* gi, float* bias_grad, size_t rows, size_t cols, float* scratch,
                      cudaStream_t s) {
-    return colsum_impl<true>(go, ref, gi, bias_grad, rows, cols, scratch, s);
+    return colsum_impl<kColsumReluBwd>(go, ref, gi, bias_grad, rows, cols, scratch, s);
+}
+bool mse_grad_colsum(const float* y, const float* t, const float* upstream, float inv_n, float* gy, float* bias_grad, size_t rows,
+                     size_t cols, bool round_tf32, float* scratch, cudaStream_t s) {
+    return colsum_impl<kColsumMseGrad>(y, t, gy, bias_grad, rows, cols, scratch, s, ColsumExtra{upstream, inv_n, round_tf32 ? 1 : 0});
 }
 
 }  // namespace k
