@@ -287,7 +287,11 @@ bool launch_relu_backward_colsum_kernel(const float* ref, const float* grad_out,
  *   mask   != NULL : C[i,j] = mask[i,j] > 0 ? C[i,j] : 0      (mask is [m,n])
  * precision: 0/1/2 as for ts_set_matmul_precision, -1 = the process-wide mode.  Shapes the
  * tensor-core path cannot take (row strides that are not multiples of 4 elements, or very
- * small problems) run on the FP32 kernel in every mode. */
+ * small problems) run on the FP32 kernel in every mode.  In modes 1 and 2 a product with one
+ * dimension of at most 16 and long other dimensions (n <= 16 without transposition or with
+ * trans_a only; k <= 16 with trans_b only: a 10-class layer, its weight gradient, its input
+ * gradient) runs on FFMA kernels laid out along the long dimensions: FP32 products of the
+ * operands as given, a fixed but not the reference's summation order. */
 bool launch_gemm_kernel(const float* a, const float* b, float* c, unsigned long long m,
                         unsigned long long n, unsigned long long k, int trans_a, int trans_b,
                         const float* bias, int relu, const float* mask, int precision, void* stream);
