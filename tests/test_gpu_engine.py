@@ -329,3 +329,27 @@ def test_storage_is_recycled_across_steps(gpu):
     _mlp_device(gpu, ws, bs, x, None, "sum", True, steps=4)
     s1 = gpu.allocator_stats()
     assert s1["driver_allocations"] == s0["driver_allocations"], "steady-state steps must not reach cudaMalloc"
+
+
+def test_backward_seed_of_a_scalar_is_shared_and_cannot_be_overwritten(gpu):
+    """backward(None) on a one-element root seeds with a 1.0 that lives once per device (no launch to write it).  The
+    handle a caller gets for that gradient reads 1.0; writing into it (fill, upload, the raw pointer) lands in a private
+    copy, so the next backward still starts from 1.0."""
+    T = gpu.Tensor
+    x = T.from_slice(np.arange(6, dtype=np.float32), [2, 3]).with_requires_grad()
+    loss = x.mul_tensor(x).sum()
+    loss.backward(None)
+    g_root = loss.grad_by_value()
+    assert g_root is not None and g_root.data().tolist() == [1.0]
+    np.testing.assert_array_equal(x.grad_by_value().data(), 2 * np.arange(6, dtype=np.float32).reshape(2, 3))
+    g_root.fill(5.0)
+    assert g_root.data().tolist() == [5.0]
+    g_root.copy_from_host(np.array([7.0], np.float32))
+    assert g_root.data().tolist() == [7.0]
+    assert g_root.data_ptr() != 0
+    gpu.clear_gradients()
+    y = T.from_slice(np.arange(6, dtype=np.float32), [2, 3]).with_requires_grad()
+    loss2 = y.mul_tensor(y).sum()
+    loss2.backward(None)
+    assert loss2.grad_by_value().data().tolist() == [1.0]
+    np.testing.assert_array_equal(y.grad_by_value().data(), 2 * np.arange(6, dtype=np.float32).reshape(2, 3))

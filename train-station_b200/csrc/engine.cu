@@ -49,6 +49,7 @@ struct Storage {
     uint64_t tf32_copy_version = 0;
     float* tf32_lo = nullptr;          // 3xTF32 mode: rn_tf32(data - tf32_copy)
     uint64_t tf32_lo_version = 0;
+    bool constant = false;             // shared read-only contents (the 1.0 that seeds backward): written through a private copy only
     ~Storage() {
         // an upload nobody waited for must land before the block goes back to the allocator
         if (ready) { cudaEventSynchronize(ready); cudaEventDestroy(ready); }
@@ -120,6 +121,24 @@ static StorageP new_storage(DeviceCtx* c, size_t n) {
     if (!p) return nullptr;
     auto s = std::make_shared<Storage>();
     s->ptr = p; s->n = n; s->c = c;
+    return s;
+}
+
+// The one-element storage holding 1.0 that seeds backward() of a scalar: made once per device and shared by every
+// seed, so that a step does not spend a launch on writing a single float.  It is never written again: the entry points
+// that write into a tensor's storage in place give a tensor that holds it a private copy first (make_writable).
+static StorageP ones_scalar(DeviceCtx* c) {
+    static std::mutex mu;
+    static StorageP* cache = new StorageP[64];   // never destroyed: must outlive every tensor that shares it
+    std::lock_guard<std::mutex> lk(mu);
+    if (c->device < 0 || c->device >= 64) return nullptr;
+    StorageP& s = cache[c->device];
+    if (!s) {
+        StorageP fresh = new_storage(c, 1);
+        if (!fresh || !k::fill(fresh->ptr, 1.0f, 1, c->compute)) return nullptr;
+        fresh->constant = true;
+        s = fresh;
+    }
     return s;
 }
 
@@ -1268,7 +1287,11 @@ static bool backward(const TensorP& root, const TensorP& grad_output) {
     if (!c) return false;
     // seed: gradtrack/engine.rs:964-978
     TensorP seed = grad_output;
-    if (!seed) {
+    if (!seed && root->size == 1) {
+        seed = std::make_shared<TensorImpl>(root->dims);
+        seed->st = ones_scalar(c);
+        if (!seed->st) return false;
+    } else if (!seed) {
         seed = new_tensor(c, root->dims);
         if (!seed || !k::fill(seed->st->ptr, 1.0f, seed->size, c->compute)) return false;
     } else if (seed->size != root->size) {
@@ -1516,8 +1539,18 @@ TS_API bool ts_tensor_set_requires_grad(ts_tensor* t, bool rg) {
     t->t->requires_grad = rg;
     return true;
 }
+// Before a write into t's storage in place: a tensor that shares read-only contents gets its own copy of them.
+static bool make_writable(const TensorP& t) {
+    if (!t->st || !t->st->constant) return true;
+    StorageP priv = new_storage(t->st->c, t->st->n);
+    if (!priv) return false;
+    TS_CHECK(cudaMemcpyAsync(priv->ptr, t->st->ptr, (t->st->n ? t->st->n : 1) * sizeof(float), cudaMemcpyDeviceToDevice, t->st->c->compute));
+    t->st = priv;
+    return true;
+}
 TS_API float* ts_tensor_data_ptr(ts_tensor* t) {
     if (!t) { set_error("ts_tensor_data_ptr: null tensor"); return nullptr; }
+    if (!make_writable(t->t)) return nullptr;   // the caller may write through the pointer
     return const_cast<float*>(rptr(t->t));
 }
 TS_API bool ts_tensor_to_host(ts_tensor* t, float* out) {
@@ -1530,6 +1563,7 @@ TS_API bool ts_tensor_to_host(ts_tensor* t, float* out) {
 }
 TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
     if (!t || (!host && t->t->size)) { set_error("ts_tensor_copy_from_host: null argument"); return false; }
+    if (!make_writable(t->t)) return false;
     if (is_view(t->t)) {
         // a write through a view lands in the shared storage: upload in the view's order, then scatter through the inverse permutation
         const TensorP& v = t->t;
@@ -1560,6 +1594,7 @@ TS_API bool ts_tensor_copy_from_host(ts_tensor* t, const float* host) {
 }
 TS_API bool ts_tensor_fill(ts_tensor* t, float v) {
     if (!t) { set_error("ts_tensor_fill: null tensor"); return false; }
+    if (!make_writable(t->t)) return false;
     // (a view covers every element of the storage it shares exactly once, so filling it fills the storage)
     if (!rptr(is_view(t->t) ? view_base(t->t) : t->t) || !flush_pending({t->t->st.get()})) return false;
     Storage* st = t->t->st.get();
