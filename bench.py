@@ -811,7 +811,7 @@ def run_c2(steps, warmup, sizes=(20, 24, 28), compact=False):
 
 # ------------------------------------------------------------------------ single-kernel cases
 MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
-               "colsum", "sum", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
+               "colsum", "sum", "fill", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
                "softmax_inner", "transpose", "permute_021", "permute_gather", "reduce_rows", "reduce_cols", "reduce_all_max",
                "reduce_middle", "broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward",
                "matmul_batched_fp32", "matmul_batched_tf32")
@@ -901,6 +901,12 @@ def run_micro(args):
             launch = lambda: chk(lib.launch_mul_backward_kernel(x, y, g, o1, o2, n, None), name)
             work = 20.0 * n
         unit, peak = "GB/s", peaks["hbm_gbs"]
+    elif name == "fill":
+        # write-only: the ceiling for kernels that read (almost) nothing, such as a column plus a row broadcast to a matrix
+        n = n or (1 << 26)
+        o1 = empty(n)
+        launch = lambda: chk(lib.launch_fill_kernel(o1, 1.5, n, None), name)
+        work, unit, peak = 4.0 * n, "GB/s", peaks["hbm_gbs"]
     elif name in ("exp", "tanh", "sigmoid", "sigmoid_backward"):
         n = n or (1 << 26)
         x, g, o1 = dev(rng.standard_normal(n, dtype=np.float32)), dev(rng.standard_normal(n, dtype=np.float32)), empty(n)

@@ -342,6 +342,70 @@ __global__ void __launch_bounds__(kThreads) bcast_kernel(Ptrs<NIN, NOUT> p, Bcas
     }
 }
 
+// The same for rank 1 or 2 after merging (a row, a column, an outer product: the usual cases).  The (row, group within
+// the row) position of each of a thread's kUnroll groups is carried along and advanced by a constant per iteration, so
+// the loop has no division: with two 32-bit divisions per 16 bytes stored the general kernel is bound by instruction
+// issue, not by memory (a column plus a row broadcast to a matrix, which only writes: 3.7 TB/s against the 6.2 TB/s a
+// plain fill reaches).
+template <int NIN, int NOUT, class F, int VEC>
+__global__ void __launch_bounds__(kThreads) bcast2_kernel(Ptrs<NIN, NOUT> p, BcastGeom<NIN> g, size_t n_groups, F f) {
+    grid_dependency_sync();
+    const unsigned d0 = g.dims[0] / VEC;                                   // groups per row
+    const unsigned step = gridDim.x * kThreads * kUnroll;
+    const unsigned step_r = step / d0, step_c = step - step_r * d0;
+    size_t gi[kUnroll];
+    unsigned row[kUnroll], col[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        gi[u] = (size_t)blockIdx.x * kThreads * kUnroll + threadIdx.x + (size_t)u * kThreads;
+        row[u] = (unsigned)(gi[u] / d0);
+        col[u] = (unsigned)(gi[u] - (size_t)row[u] * d0);
+    }
+    while (gi[0] < n_groups) {
+        float xi[kUnroll][VEC][NIN];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (gi[u] >= n_groups) break;
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) {
+                const size_t off = (size_t)col[u] * VEC * g.stride[a][0] + (size_t)row[u] * g.stride[a][1];
+                if (VEC == 4 && g.stride[a][0] == 1) {
+                    const float4* q4 = reinterpret_cast<const float4*>(p.in[a] + off);
+                    const float4 v = g.reused[a] ? __ldg(q4) : __ldcs(q4);
+                    xi[u][0][a] = v.x; xi[u][1 % VEC][a] = v.y; xi[u][2 % VEC][a] = v.z; xi[u][3 % VEC][a] = v.w;
+                } else {
+                    const float v = __ldg(p.in[a] + off);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) xi[u][e][a] = v;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (gi[u] >= n_groups) break;
+            float xo[VEC][NOUT];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) f.apply(xi[u][e], xo[e]);
+#pragma unroll
+            for (int o = 0; o < NOUT; ++o) {
+                if (!p.out[o]) continue;
+                if (VEC == 4) {
+                    __stcs(reinterpret_cast<float4*>(p.out[o]) + gi[u], make_float4(xo[0][o], xo[1 % VEC][o], xo[2 % VEC][o], xo[3 % VEC][o]));
+                } else {
+                    p.out[o][gi[u]] = xo[0][o];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            gi[u] += step;
+            row[u] += step_r;
+            col[u] += step_c;
+            if (col[u] >= d0) { col[u] -= d0; ++row[u]; }
+        }
+    }
+}
+
 // dims (outermost first) and per-input strides over them; `contiguous_inputs` trailing inputs (the upstream
 // gradient of a backward pass) are read with the output's own contiguous strides.
 template <int NIN, int NOUT, class F>
@@ -396,7 +460,14 @@ bool launch_bcast(Ptrs<NIN, NOUT> p, const size_t* dims, int rank, const size_t*
     const size_t n_groups = vec ? n / 4 : n;
     const int grid = grid_for(n_groups, c->sm_count);
     const bool small = n_groups <= 0xFFFFFFFFull;
-    if (vec && small) launch_dep(bcast_kernel<NIN, NOUT, F, 4, unsigned>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+    if (g.rank <= 2 && small) {
+        if (g.rank == 1) {   // one row: the second axis does not exist
+            g.dims[1] = 1;
+            for (int a = 0; a < NIN; ++a) g.stride[a][1] = 0;
+        }
+        if (vec) launch_dep(bcast2_kernel<NIN, NOUT, F, 4>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+        else launch_dep(bcast2_kernel<NIN, NOUT, F, 1>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
+    } else if (vec && small) launch_dep(bcast_kernel<NIN, NOUT, F, 4, unsigned>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
     else if (vec) launch_dep(bcast_kernel<NIN, NOUT, F, 4, size_t>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
     else if (small) launch_dep(bcast_kernel<NIN, NOUT, F, 1, unsigned>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);
     else launch_dep(bcast_kernel<NIN, NOUT, F, 1, size_t>, dim3(grid), dim3(kThreads), 0, s, p, g, n_groups, f);

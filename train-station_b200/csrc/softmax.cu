@@ -670,6 +670,7 @@ void launch_short(bool bwd, const float* a, const float* b, float* o, size_t row
 void dispatch(bool bwd, const float* a, const float* b, float* o, size_t outer, size_t reduce, size_t inner, int sm, cudaStream_t s) {
     if (inner == 1) {
         if (reduce <= 8) launch_short<8>(bwd, a, b, o, outer, (int)reduce, sm, s);
+        else if (reduce <= 12) launch_short<12>(bwd, a, b, o, outer, (int)reduce, sm, s);   // 10 classes: 12 unrolled slots instead of 16
         else if (reduce <= 16) launch_short<16>(bwd, a, b, o, outer, (int)reduce, sm, s);
         else if (reduce <= kShortMax) launch_short<kShortMax>(bwd, a, b, o, outer, (int)reduce, sm, s);
         else if (reduce <= 32 * kV) launch_rows<32>(bwd, a, b, o, outer, reduce, sm, s);
