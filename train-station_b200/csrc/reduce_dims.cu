@@ -226,7 +226,11 @@ bool launch_forward(const float* x, const float* aux, float* out, const Plan& p,
         q.nr = 1; q.rdim[0] = splits; q.rstr[0] = p.n_out;
         q.n_out = p.n_out; q.n_red = splits;
         constexpr int OP2 = (OP == kMax || OP == kMin) ? OP : kSum;
-        if (splits > 32) {
+        if (OP2 == kSum && splits > 8 && p.n_out >= 1024) {
+            // many partial rows of many outputs (column sums of a tall matrix): lanes along the outputs, warps along the
+            // partial rows, so the rows are read as contiguous runs; rows added in a fixed order
+            if (!colsum_finish(scratch, out, p.n_out, splits, s)) return false;
+        } else if (splits > 32) {
             // many partials per output (few outputs): a warp per output instead of one thread walking them all
             const size_t want = (p.n_out + 7) / 8, cap = (size_t)sm * 32;
             launch_dep(reduce_reduced_inner_kernel<OP2>, dim3((unsigned)(want < cap ? want : cap)), dim3(kThreads), 0, s, scratch, nullptr, out, q, splits, 1);
