@@ -82,6 +82,14 @@ int* ts_device_error_word(void);
  * satisfied gives up, the kernel records an error code (101..104), drains its own copies with the full bound, frees
  * its tensor memory and returns; nothing faults and the context stays usable.  The two-CTA kernel ignores it. */
 void ts_debug_set_gemm_wait_budget(long long cycles);
+/* Which kernel launch_gemm_kernel would send a product to on a device with sm_count SMs: host arithmetic only, usable
+ * without a GPU.  epilogue: bit 0 bias, 1 ReLU, 2 mask, 3 store rounded to TF32, 4 column sums.  Returns
+ * 0 FP32 tiled kernel, 1 the same over a split K, 2 / 3 / 4 thin-product kernels (narrow result forward layout, narrow
+ * result weight-gradient layout, short reduction), 5 / 6 one-CTA tensor-core kernel on 128 x 128 / 128 x 256 tiles,
+ * 7 CTA pairs on 256 x 256 tiles, 8 / 9 one-CTA kernel over a split K on narrow / wide tiles; *splits receives the
+ * number of K splits (1 when there is none). */
+int ts_debug_gemm_route(unsigned long long m, unsigned long long n, unsigned long long k, int trans_a, int trans_b,
+                        int precision, int epilogue, int sm_count, unsigned long long* splits);
 /* The two-CTA tensor-core GEMM hands its tiles out from a counter (1, the default) or by a fixed stride per CTA pair (0);
  * negative: back to the default / the TS_GEMM_DYNAMIC environment variable.  For A/B measurements and for tests that
  * run both schedules. */

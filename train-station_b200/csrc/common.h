@@ -231,6 +231,14 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s);  // 
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s);   // dispatch
 // Products with one dimension of at most 16 (a 10-class output layer, its weight and input gradients) in the modes
 // without a fixed summation order: FFMA kernels laid out along the long dimensions (thin_gemm.cu).
+// Where a product goes (host arithmetic only; needs no device): the kernels act on these, ts_debug_gemm_route reports them.
+enum GemmRouteKind { kRouteFp32 = 0, kRouteFp32SplitK = 1, kRouteThinNN = 2, kRouteThinTN = 3, kRouteThinNT = 4, kRouteTc128 = 5,
+                     kRouteTc256 = 6, kRouteTcPairs = 7, kRouteTcSplitK128 = 8, kRouteTcSplitK256 = 9 };
+struct TcRoute { int kind; size_t splits; size_t kb_per_split; };
+struct GemmRoute { int kind; size_t splits; size_t kb_per_split; };
+TcRoute tc_route(const GemmArgs& g, int sm_count);
+GemmRoute gemm_route(const GemmArgs& g, int precision, int sm_count);
+int gemm_thin_kind(const GemmArgs& g);      // 0 none, 1 thin_n_nn, 2 thin_n_tn, 3 thin_k_nt
 bool gemm_thin_supported(const GemmArgs& g);
 bool gemm_thin_rounds(const GemmArgs& g);   // ... and this one would honour round_tf32
 bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s);

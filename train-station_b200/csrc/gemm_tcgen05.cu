@@ -945,13 +945,17 @@ int env_int(const char* name, int dflt, int lo, int hi) {
     static std::map<std::string, int> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lk(mu);
+    // what is cached is the variable's own value (or that it is unset or out of range): the default may differ from call
+    // to call (it can depend on the device's SM count)
+    constexpr int kUnset = -2147483647 - 1;
     auto it = cache.find(name);
-    if (it != cache.end()) return it->second;
-    int v = dflt;
-    if (const char* e = getenv(name)) v = atoi(e);
-    if (v < lo || v > hi) v = dflt;
-    cache[name] = v;
-    return v;
+    if (it == cache.end()) {
+        int v = kUnset;
+        if (const char* e = getenv(name)) v = atoi(e);
+        if (v < lo || v > hi) v = kUnset;
+        it = cache.emplace(name, v).first;
+    }
+    return it->second == kUnset ? dflt : it->second;
 }
 
 // TS_GEMM_DYNAMIC=0 (or ts_debug_set_gemm_dynamic(0)) goes back to the fixed stride, for A/B measurements and tests.
@@ -1053,6 +1057,81 @@ bool gemm_tc_supported(const GemmArgs& g) {
     return true;
 }
 
+// Which tensor-core kernel a supported product runs on: host arithmetic only, the one place these thresholds live
+// (gemm_tc acts on it, ts_debug_gemm_route reports it).
+TcRoute tc_route(const GemmArgs& g, int sm_count) {
+    TcRoute r{kRouteTc128, 1, 0};
+    const size_t sms = (size_t)(sm_count > 0 ? sm_count : 1);
+    // Large problems: pairs of CTAs on 256 x 256 tiles, as long as every pair gets at least one tile.
+    const size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
+    if (two_cta_enabled() && sms >= 2 && tiles_pair >= (size_t)env_int("TS_GEMM_2CTA_MIN_TILES", (int)(sms / 2), 1, 1 << 20)) {
+        r.kind = kRouteTcPairs;
+        return r;
+    }
+    const size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
+    const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
+    const size_t num_kb = (g.k + BK - 1) / BK;
+    // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
+    // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split.  FP32 mode never comes here
+    // (its order is fixed).  At this size a CTA is bound by what it pulls out of L2, (rows + columns of its tile) x its
+    // share of K, so of the two tile widths the one with the smaller such product is taken (1024 x 1024 over K = 4096:
+    // four splits of 128 x 256 tiles move a quarter less than two splits of 128 x 128 tiles).
+    if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && !g.colsum_partial && !g.colsum_out && tiles128 * 2 <= sms && num_kb >= 64 &&
+        split_k_enabled()) {
+        auto plan = [&](size_t tiles, size_t width, size_t* splits, size_t* kbps) {
+            size_t sp = sms / tiles;
+            if (sp > num_kb / 32) sp = num_kb / 32;          // at least 1024 elements of K per split
+            if (sp > 16) sp = 16;
+            if (sp < 1) sp = 1;
+            *kbps = (num_kb + sp - 1) / sp;
+            *splits = (num_kb + *kbps - 1) / *kbps;          // no empty split
+            return (BM + width) * *kbps;
+        };
+        size_t sp128 = 1, kb128 = 0, sp256 = 1, kb256 = 0;
+        const size_t cost128 = plan(tiles128, 128, &sp128, &kb128);
+        const size_t cost256 = g.n > 128 ? plan(tiles256, 256, &sp256, &kb256) : ~size_t(0);
+        const bool wide = cost256 < cost128;
+        const size_t splits = wide ? sp256 : sp128;
+        if (splits >= 2) {
+            r.kind = wide ? kRouteTcSplitK256 : kRouteTcSplitK128;
+            r.splits = splits;
+            r.kb_per_split = wide ? kb256 : kb128;
+            return r;
+        }
+    }
+    // 128 x 128 tiles while those fit in one wave (twice as many CTAs at work as 128 x 256 tiles would give); beyond
+    // that one wave of 128 x 256 tiles beats two of the narrow ones, because each CTA then pulls a third less through L2
+    // per flop (4096 x 1024 x 1024: 20.5 against 28.6 us).  TS_GEMM_BN256_MIN_TILES moves the switch-over.
+    if (g.n > 128 && tiles256 >= (size_t)env_int("TS_GEMM_BN256_MIN_TILES", (int)(sms / 2 + 1), 1, 1 << 20)) r.kind = kRouteTc256;
+    return r;
+}
+
+// FP32-kernel split of a long reduction in the modes without a fixed summation order (0: none)
+static size_t fp32_splits(const GemmArgs& g, int precision, int sm_count) {
+    if (!(precision >= 1 && g.trans_a && !g.trans_b && !g.bias && !g.relu && !g.mask && g.batch == 1 && g.k >= 2048 && split_k_enabled())) return 0;
+    const size_t tiles32 = ((g.m + 31) / 32) * ((g.n + 31) / 32);
+    size_t splits = 0;
+    for (size_t cand = 32; cand >= 2; cand /= 2)
+        if (g.k % cand == 0 && g.k / cand >= 128 && tiles32 * cand <= (size_t)sm_count * 8) { splits = cand; break; }
+    return (splits >= 2 && tiles32 <= (size_t)sm_count) ? splits : 0;
+}
+
+GemmRoute gemm_route(const GemmArgs& g, int precision, int sm_count) {
+    if (precision < 0) precision = matmul_precision();
+    if (precision >= 1) {
+        const int thin = gemm_thin_kind(g);
+        if (thin) return GemmRoute{thin == 1 ? kRouteThinNN : thin == 2 ? kRouteThinTN : kRouteThinNT, 1, 0};
+        if (gemm_tc_supported(g)) {
+            const TcRoute t = tc_route(g, sm_count);
+            return GemmRoute{t.kind, t.splits, t.kb_per_split};
+        }
+    }
+    GemmArgs h = g;
+    h.colsum_out = nullptr;   // the FP32 kernels make the column sums in a pass of their own
+    const size_t sp = fp32_splits(h, precision, sm_count);
+    return sp ? GemmRoute{kRouteFp32SplitK, sp, 0} : GemmRoute{kRouteFp32, 1, 0};
+}
+
 bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
     if (!gemm_tc_supported(g)) { set_error("gemm: shape or alignment not supported by the tensor-core kernel"); return false; }
     if (split3 && !(g.a_lo && g.b_lo)) {
@@ -1070,9 +1149,8 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
         return ok;
     }
     if (!split3 && (g.a_lo || g.b_lo)) { set_error("gemm: low parts given without the 3xTF32 mode"); return false; }
-    // Large problems: pairs of CTAs on 256 x 256 tiles, as long as every pair gets at least one tile.
-    size_t tiles_pair = ((g.m + 255) / 256) * ((g.n + 255) / 256);
-    const bool pairs = two_cta_enabled() && c->sm_count >= 2 && tiles_pair >= (size_t)env_int("TS_GEMM_2CTA_MIN_TILES", c->sm_count / 2, 1, 1 << 20);
+    const TcRoute route = tc_route(g, c->sm_count);
+    const bool pairs = route.kind == kRouteTcPairs;
     if (g.colsum_out && !g.colsum_partial) {
         // Column sums of the result from the epilogue: one partial row per 32 result rows of every tile the chosen
         // kernel walks (rows past m contribute zeros), in scratch, then one small launch that adds them in order.
@@ -1087,50 +1165,22 @@ bool gemm_tc(const GemmArgs& g, bool split3, DeviceCtx* c, cudaStream_t s) {
         return ok;
     }
     if (pairs) return launch_tc2_any(g, c, s);
-    const size_t sms = (size_t)c->sm_count;
-    const size_t tiles256 = ((g.m + BM - 1) / BM) * ((g.n + 255) / 256);
-    const size_t tiles128 = ((g.m + BM - 1) / BM) * ((g.n + 127) / 128);
-    const size_t num_kb = (g.k + BK - 1) / BK;
-    // A result with few tiles and a long reduction (the weight gradient of a small layer over a large batch) leaves
-    // most SMs idle while a few walk all of K.  Without an epilogue to apply, K is split: every (tile, split) pair is a
-    // work item of the same launch, the partial products land side by side in scratch and a second kernel adds them
-    // in split order, so the result does not depend on scheduling.  FP32 mode never comes here (its order is fixed).
-    // At this size a CTA is bound by what it pulls out of L2, (rows + columns of its tile) x its share of K, so of the
-    // two tile widths the one with the smaller such product is taken (1024 x 1024 over K = 4096: four splits of 128 x 256
-    // tiles move a quarter less than two splits of 128 x 128 tiles).
-    if (!g.bias && !g.relu && !g.mask && !g.round_tf32 && !g.colsum_partial && tiles128 * 2 <= sms && num_kb >= 64 && split_k_enabled()) {
-        auto plan = [&](size_t tiles, size_t width, size_t* splits, size_t* kbps) {
-            size_t sp = sms / tiles;
-            if (sp > num_kb / 32) sp = num_kb / 32;          // at least 1024 elements of K per split
-            if (sp > 16) sp = 16;
-            if (sp < 1) sp = 1;
-            *kbps = (num_kb + sp - 1) / sp;
-            *splits = (num_kb + *kbps - 1) / *kbps;          // no empty split
-            return (BM + width) * *kbps;
-        };
-        size_t sp128, kb128, sp256, kb256;
-        const size_t cost128 = plan(tiles128, 128, &sp128, &kb128);
-        const size_t cost256 = g.n > 128 ? plan(tiles256, 256, &sp256, &kb256) : ~size_t(0);
-        const bool wide = cost256 < cost128;
-        const size_t splits = wide ? sp256 : sp128, kbps = wide ? kb256 : kb128;
-        if (splits >= 2) {
-            const size_t mn = g.m * g.n;
-            float* part = c->alloc.alloc(splits * mn * sizeof(float));
-            if (!part) return false;
-            GemmArgs h = g;
-            h.c = part;
-            bool ok = (wide ? launch_tc_bn<256>(h, c, s, (uint32_t)splits, (uint32_t)kbps) : launch_tc_bn<128>(h, c, s, (uint32_t)splits, (uint32_t)kbps)) &&
-                      sum_slabs(part, g.c, mn, splits, s);
-            if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
-            c->alloc.free(part);
-            return ok;
-        }
+    if (route.kind == kRouteTcSplitK128 || route.kind == kRouteTcSplitK256) {
+        // every (tile, split) pair is a work item of the same launch, the partial products land side by side in scratch
+        // and a second kernel adds them in split order, so the result does not depend on scheduling
+        const size_t mn = g.m * g.n;
+        float* part = c->alloc.alloc(route.splits * mn * sizeof(float));
+        if (!part) return false;
+        GemmArgs h = g;
+        h.c = part;
+        bool ok = (route.kind == kRouteTcSplitK256 ? launch_tc_bn<256>(h, c, s, (uint32_t)route.splits, (uint32_t)route.kb_per_split)
+                                                   : launch_tc_bn<128>(h, c, s, (uint32_t)route.splits, (uint32_t)route.kb_per_split)) &&
+                  sum_slabs(part, g.c, mn, route.splits, s);
+        if (s != c->compute) cudaStreamSynchronize(s);   // the block is recycled in compute-stream order only
+        c->alloc.free(part);
+        return ok;
     }
-    // 128 x 128 tiles while those fit in one wave (twice as many CTAs at work as 128 x 256 tiles would give); beyond
-    // that one wave of 128 x 256 tiles beats two of the narrow ones, because each CTA then pulls a third less through L2
-    // per flop (4096 x 1024 x 1024: 20.5 against 28.6 us).  TS_GEMM_BN256_MIN_TILES moves the switch-over.
-    if (g.n <= 128 || tiles256 < (size_t)env_int("TS_GEMM_BN256_MIN_TILES", (int)(sms / 2 + 1), 1, 1 << 20)) return launch_tc_bn<128>(g, c, s);
-    return launch_tc_bn<256>(g, c, s);
+    return route.kind == kRouteTc256 ? launch_tc_bn<256>(g, c, s) : launch_tc_bn<128>(g, c, s);
 }
 
 bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
@@ -1149,25 +1199,20 @@ bool gemm(const GemmArgs& g, int precision, DeviceCtx* c, cudaStream_t s) {
         return ok;
     }
     // A shape the tensor-core kernel cannot take, in a mode that promises no summation order: when the result is small
-    // and K long (C4's [1024 x 10] weight gradient over K = 4096: 32 CTAs each walking the whole chain), K is split
-    // into equal parts that run as one batched launch of the FP32 kernel and are then added in split order.  This works
-    // on offsets alone when both operands are stored K-outermost (op(A) = A^T, op(B) = B: the weight-gradient layout).
-    if (precision >= 1 && g.trans_a && !g.trans_b && !g.bias && !g.relu && !g.mask && g.batch == 1 && g.k >= 2048 && c && split_k_enabled()) {
-        const size_t tiles32 = ((g.m + 31) / 32) * ((g.n + 31) / 32);
-        size_t splits = 0;
-        for (size_t cand = 32; cand >= 2; cand /= 2)
-            if (g.k % cand == 0 && g.k / cand >= 128 && tiles32 * cand <= (size_t)c->sm_count * 8) { splits = cand; break; }
-        if (splits >= 2 && tiles32 <= (size_t)c->sm_count) {
-            const size_t mn = g.m * g.n, ks = g.k / splits;
-            float* part = c->alloc.alloc(splits * mn * sizeof(float));
-            if (!part) return false;
-            GemmArgs h = g;
-            h.c = part; h.k = ks; h.batch = splits; h.batch_stride_a = ks * g.m; h.batch_stride_b = ks * g.n;
-            bool ok = sgemm(h, s) && sum_slabs(part, g.c, mn, splits, s);
-            if (s != c->compute) cudaStreamSynchronize(s);
-            c->alloc.free(part);
-            return ok;
-        }
+    // and K long (a [1024 x 10] weight gradient over K = 4096 with the thin kernels switched off: 32 CTAs each walking
+    // the whole chain), K is split into equal parts that run as one batched launch of the FP32 kernel and are then added
+    // in split order.  This works on offsets alone when both operands are stored K-outermost (op(A) = A^T, op(B) = B:
+    // the weight-gradient layout).
+    if (const size_t splits = c ? fp32_splits(g, precision, c->sm_count) : 0) {
+        const size_t mn = g.m * g.n, ks = g.k / splits;
+        float* part = c->alloc.alloc(splits * mn * sizeof(float));
+        if (!part) return false;
+        GemmArgs h = g;
+        h.c = part; h.k = ks; h.batch = splits; h.batch_stride_a = ks * g.m; h.batch_stride_b = ks * g.n;
+        bool ok = sgemm(h, s) && sum_slabs(part, g.c, mn, splits, s);
+        if (s != c->compute) cudaStreamSynchronize(s);
+        c->alloc.free(part);
+        return ok;
     }
     return sgemm(g, s);
 }
@@ -1201,6 +1246,19 @@ TS_API bool launch_gemm_colsum_kernel(const float* a, const float* b, float* cc,
     k::GemmArgs g{a, b, cc, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0, bias, relu != 0, mask};
     g.colsum_out = colsum_out;
     return k::gemm(g, precision, c, s);
+}
+
+TS_API int ts_debug_gemm_route(unsigned long long m, unsigned long long n, unsigned long long kk, int trans_a, int trans_b, int precision,
+                               int epilogue, int sm_count, unsigned long long* splits) {
+    // stand-in operand addresses: only their alignment is looked at
+    float* const aligned = reinterpret_cast<float*>(uintptr_t(1) << 20);
+    k::GemmArgs g{aligned, aligned, aligned, (size_t)m, (size_t)n, (size_t)kk, trans_a != 0, trans_b != 0,
+                  (epilogue & 1) ? aligned : nullptr, (epilogue & 2) != 0, (epilogue & 4) ? aligned : nullptr};
+    g.round_tf32 = (epilogue & 8) != 0;
+    g.colsum_out = (epilogue & 16) ? aligned : nullptr;
+    const k::GemmRoute r = k::gemm_route(g, precision, sm_count);
+    if (splits) *splits = r.splits;
+    return r.kind;
 }
 
 TS_API void ts_debug_set_gemm_dynamic(int enabled) { k::g_dynamic_tiles.store(enabled < 0 ? -1 : (enabled ? 1 : 0)); }

@@ -306,6 +306,7 @@ bool launch_nt(const GemmArgs& g, cudaStream_t s) {
 
 }  // namespace
 
+int gemm_thin_kind(const GemmArgs& g) { return thin_case(g); }
 bool gemm_thin_supported(const GemmArgs& g) { return thin_case(g) != 0; }
 bool gemm_thin_rounds(const GemmArgs& g) { const int t = thin_case(g); return t == 1 || t == 3; }
 
