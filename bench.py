@@ -523,7 +523,7 @@ def run_gpu(args, d: Dist):
                 extras[f"{cfg}_{pname}"] = run_config(cfg, pname, steps={"c1": 200, "c4": 100, "c3": 5}[cfg], warmup=3,
                                                       with_cpu=(pname == precs[0]), compact=True)
                 ts.release_cached_memory()
-        extras["c2"] = run_c2(steps=5, warmup=2, sizes=(24, 28), compact=True)
+        extras["c2"] = run_c2(steps=5, warmup=2, sizes=(20, 24, 28), compact=True)
         ts.release_cached_memory()
         line["configs"] = extras
         try:
