@@ -246,11 +246,23 @@ def cpu_baseline_for(ws, bs, x, t, loss_kind, relu_last, want_gx, batch, sample_
         ora.adam_update(st.w[l].reshape(-1), st.gw[l].reshape(-1), st.mw[l].reshape(-1), st.vw[l].reshape(-1), 1)
         ora.adam_update(st.b[l], st.gb[l], st.mb[l], st.vb[l], 1)
     t_adam = time.perf_counter() - t0
-    return {"value": 1.0 / (sec_w + t_adam), "unit": "steps/s", "cores": 1, "kind": "port",
+    return {"value": 1.0 / (sec_w + t_adam), "unit": "steps/s", "cores": 1, "kind": "port", "cpu_model": host_cpu_model(),
             "math_only": 1.0 / (sec_m + t_adam),
             "sample": f"{what}: {how} ({spent:.1f} s of CPU time) + one full Adam ({t_adam:.2f} s); `value` is the reference as written "
                       f"(operand deep copies, element-by-element broadcast of the bias, coordinate-walk transposes), `math_only` its "
                       f"arithmetic alone"}
+
+
+def host_cpu_model() -> str:
+    """The host CPU the one-thread baseline ran on (first `model name` of /proc/cpuinfo)."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 def cpu_baseline(sample_rows: int = 128):
