@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* 
 // rows of B in registers; a CTA covers 16 result rows (A's 16 rows sit in shared memory and are read by all threads at
 // once) by 1024 columns.  Every result is finished (bias, ReLU, mask, rounding) and stored as it is made, a row of
 // 4 KiB per step of the CTA; the column sums of the stored values over the CTA's 16 rows go to row blockIdx.x of
-// g.colsum_partial when that is set.  VEC: n % 4 == 0 and C, the mask and the bias are 16-byte aligned.
+// g.colsum_partial when that is set.  VEC: n % 4 == 0 and C and the mask are 16-byte aligned (float4 stores and loads).
 template <int KP, bool VEC>
 __global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
     __shared__ __align__(16) float as[kNtRows * KP];
