@@ -469,6 +469,11 @@ bool ts_dp_init(const unsigned char id[TS_DP_UNIQUE_ID_BYTES], int rank, int wor
 /* ts_dp_init waits at most TS_DP_INIT_TIMEOUT seconds (environment, default 300; 0 = for ever) for the other ranks:
  * a rank that never joins costs a bounded wait and an error, not a hang. */
 bool ts_dp_init_with_timeout(const unsigned char id[TS_DP_UNIQUE_ID_BYTES], int rank, int world_size, double timeout_seconds);
+/* How the data-parallel path would split a registered parameter of n elements over `world` ranks: returns 1 and the
+ * rank's slice [*lo, *lo + *count) when its gradient is reduce-scattered and updated slice by slice (large tensors
+ * whose size is a multiple of 8 * world, so that every slice starts on Adam's 8-element boundary), 0 with [0, n) when it
+ * is all-reduced and updated whole.  Host arithmetic only: usable without a GPU and without a communicator. */
+int ts_debug_dp_shard_plan(unsigned long long n, int world, int rank, unsigned long long* lo, unsigned long long* count);
 /* False once the communicator has reported an asynchronous error (a peer that died, a transport fault).  The
  * communicator is then aborted, so that no later call can block on it, and every later collective call fails with a
  * message.  Checked by the library at every collective it enqueues; a host may also poll it between steps. */

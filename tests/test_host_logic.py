@@ -124,3 +124,32 @@ def test_shard_weight_makes_unequal_shards_add_up_to_the_global_mean(ts, ora):
         np.testing.assert_allclose(weighted[l], full["gw"][l], rtol=1e-12, atol=1e-14)
         assert np.abs(plain[l] - full["gw"][l]).max() > 1e-4 * np.abs(full["gw"][l]).max()   # the unweighted sum is measurably off
     assert ts.distributed.shard_weight(64, 1, 4) == 1.0
+
+
+def test_data_parallel_shard_plan_for_every_world_size(ts):
+    """Which slice of a parameter a rank owns (host arithmetic, `ts_debug_dp_shard_plan`): the C5 tensors at 1, 2, 4 and
+    8 ranks, the slices tile the tensor, every slice starts on a multiple of 8 elements, small or indivisible tensors
+    stay whole."""
+    import ctypes as C
+    lib = ts._ffi.lib()
+
+    def plan(n, world, rank):
+        lo, cnt = C.c_ulonglong(0), C.c_ulonglong(0)
+        sliced = lib.ts_debug_dp_shard_plan(n, world, rank, C.byref(lo), C.byref(cnt))
+        return bool(sliced), lo.value, cnt.value
+
+    weights = [4096 * 8192, 8192 * 8192, 8192 * 4096]
+    biases = [8192, 8192, 4096]
+    for world in (2, 4, 8):
+        for n in weights:
+            covered = 0
+            for rank in range(world):
+                sliced, lo, cnt = plan(n, world, rank)
+                assert sliced and lo == covered and lo % 8 == 0 and cnt == n // world
+                covered += cnt
+            assert covered == n
+        for n in biases:
+            assert plan(n, world, world - 1) == (False, 0, n), "a few thousand elements: all-reduced, updated on every rank"
+    assert plan(weights[0], 1, 0) == (False, 0, weights[0])
+    assert plan((1 << 20) + 8, 8, 3) == (False, 0, (1 << 20) + 8), "not a multiple of 8 * world: kept whole"
+    assert plan(3 * (1 << 16), 3, 2) == (True, 2 * (1 << 16), 1 << 16)

@@ -80,6 +80,7 @@ SIGNATURES = {
     "launch_binary_broadcast_backward_kernel": (C.c_bool, [C.c_int, vp, u64p, C.c_int, vp, u64p, C.c_int, vp, vp, vp, vp]),
     "launch_scale_kernel": (C.c_bool, [vp, C.c_float, vp, u64, vp]),
     "launch_fill_kernel": (C.c_bool, [vp, C.c_float, u64, vp]),
+    "ts_debug_dp_shard_plan": (C.c_int, [u64, C.c_int, C.c_int, C.POINTER(u64), C.POINTER(u64)]),
     "ts_debug_gemm_route": (C.c_int, [u64, u64, u64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(u64)]),
     "launch_fill_from_scalar_kernel": (C.c_bool, [vp, vp, C.c_float, u64, vp]),
     "launch_unary_kernel": (C.c_bool, [C.c_int, vp, vp, u64, C.c_float, vp]),

@@ -481,6 +481,16 @@ static bool dp_gather_tf32_enabled() {
     return v == 1;
 }
 
+// Which part of a gradient of n elements rank `rank` of `world` owns after the sum: the whole of it ([0, n), not sliced)
+// when the tensor is small, when n is not a multiple of 8 * world, or when sharding is switched off; else the rank's
+// contiguous n / world elements.  Host arithmetic only (ts_debug_dp_shard_plan reports it without a device).
+static bool dp_shard_plan(size_t n, size_t world, size_t rank, size_t* lo, size_t* cnt) {
+    const bool slice = world > 1 && dp_shard_enabled() && n >= kMinShardElems && n % (8 * world) == 0;
+    *cnt = slice ? n / world : n;
+    *lo = slice ? rank * *cnt : 0;
+    return slice;
+}
+
 static bool dp_nccl_ok(NcclApi* nc, ncclResult_t r, const char* what) {
     if (r == ncclSuccess) return true;
     set_error("%s failed: %s", what, nc->GetErrorString(r));
@@ -560,10 +570,13 @@ static bool dp_reduce_leaf(DeviceCtx* c, uint64_t id, const TensorP& lg) {
     const size_t n = lg->size;
     const size_t world = (size_t)g_dp.world;
     auto have = g_dp.red.find(id);
-    bool slice = dp_shard_enabled() && n >= kMinShardElems && n % (8 * world) == 0;
-    if (have != g_dp.red.end() && (!have->second.sliced || have->second.gathered)) slice = false;   // the earlier sum is held in full
+    size_t lo = 0, cnt = n;
+    bool slice = dp_shard_plan(n, world, (size_t)g_dp.rank, &lo, &cnt);
+    if (slice && have != g_dp.red.end() && (!have->second.sliced || have->second.gathered)) {   // the earlier sum is held in full
+        slice = false;
+        lo = 0; cnt = n;
+    }
     float* p = lg->st->ptr;
-    const size_t cnt = slice ? n / world : n, lo = slice ? (size_t)g_dp.rank * cnt : 0;
     if (slice) {
         if (!dp_nccl_ok(nc, nc->ReduceScatter(p, p + lo, cnt, ncclFloat32, ncclSum, g_dp.comm, c->comm), "ncclReduceScatter")) return false;
     } else {
@@ -2584,6 +2597,14 @@ TS_API bool ts_dp_init(const unsigned char id_in[TS_DP_UNIQUE_ID_BYTES], int ran
     double t = 300.0;   // TS_DP_INIT_TIMEOUT (seconds; 0 = wait for ever)
     if (const char* e = getenv("TS_DP_INIT_TIMEOUT")) t = atof(e);
     return ts_dp_init_with_timeout(id_in, rank, world, t);
+}
+// Which elements of an n-element gradient a rank owns after the cross-rank sum (1: a slice, 0: all of it); for tests.
+TS_API int ts_debug_dp_shard_plan(unsigned long long n, int world, int rank, unsigned long long* lo, unsigned long long* count) {
+    size_t l = 0, c = 0;
+    const bool sliced = ts::dp_shard_plan((size_t)n, (size_t)(world > 0 ? world : 1), (size_t)(rank > 0 ? rank : 0), &l, &c);
+    if (lo) *lo = l;
+    if (count) *count = c;
+    return sliced ? 1 : 0;
 }
 // True while the communicator reports no asynchronous error.  On an error (a peer that died, a transport fault) the
 // communicator is aborted, so that nothing can block on it any more, and this and every later collective call fail.
