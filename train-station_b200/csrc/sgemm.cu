@@ -95,7 +95,31 @@ __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
     const bool vec_a = (reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && lda % 4 == 0;
     const bool vec_b = (reinterpret_cast<uintptr_t>(g.b) & 15) == 0 && ldb % 4 == 0;
     float ra[8], rb[8];
+    // Where this thread's two 128-bit loads of each operand start (at k = 0) and whether they lie inside the matrix: the
+    // index arithmetic of tile_load is done once, and a k-tile that lies wholly inside K (all but possibly the last)
+    // costs a pointer bump and a load per half instead of a dozen integer instructions that compete with the FFMAs for
+    // issue slots.  Anything else (edge rows or columns, odd pitches, the partial last tile) takes tile_load's guarded path.
+    const float* fa;   // this thread's first load of the NEXT k-tile of A (its second one lies 64 rows, or 8 k-rows, further on)
+    const float* fb;
+    bool fast;
+    {
+        const size_t xa = !TA ? m0 + t / 4 : m0 + (t % 32) * 4, xb = TB ? n0 + t / 4 : n0 + (t % 32) * 4;
+        fa = !TA ? g.a + xa * lda + (t % 4) * 4 : g.a + (size_t)(t / 32) * lda + xa;
+        fb = TB ? g.b + xb * ldb + (t % 4) * 4 : g.b + (size_t)(t / 32) * ldb + xb;
+        fast = vec_a && vec_b && (!TA ? xa + 64 < M : xa + 4 <= M) && (TB ? xb + 64 < N : xb + 4 <= N);
+    }
     auto load_tiles = [&](size_t k0) {
+        const float* pa = fa;
+        const float* pb = fb;
+        fa += !TA ? (size_t)BK : (size_t)BK * lda;     // calls come in k order, one per tile
+        fb += TB ? (size_t)BK : (size_t)BK * ldb;
+        if (fast && k0 + BK <= K) {
+            const float4 va0 = *reinterpret_cast<const float4*>(pa), va1 = *reinterpret_cast<const float4*>(pa + (!TA ? 64 : 8) * lda);
+            const float4 vb0 = *reinterpret_cast<const float4*>(pb), vb1 = *reinterpret_cast<const float4*>(pb + (TB ? 64 : 8) * ldb);
+            ra[0] = va0.x; ra[1] = va0.y; ra[2] = va0.z; ra[3] = va0.w; ra[4] = va1.x; ra[5] = va1.y; ra[6] = va1.z; ra[7] = va1.w;
+            rb[0] = vb0.x; rb[1] = vb0.y; rb[2] = vb0.z; rb[3] = vb0.w; rb[4] = vb1.x; rb[5] = vb1.y; rb[6] = vb1.z; rb[7] = vb1.w;
+            return;
+        }
         tile_load<!TA>(ra, g.a, lda, m0, M, k0, K, vec_a);
         tile_load<TB>(rb, g.b, ldb, n0, N, k0, K, vec_b);
     };
