@@ -833,7 +833,7 @@ def run_c2(steps, warmup, sizes=(20, 24, 28), compact=False):
 
 
 # ------------------------------------------------------------------------ single-kernel cases
-MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
+MICRO_CASES = ("gemm_nn", "gemm_nt", "gemm_tn", "gemm_nn_fp32", "gemm_nt_fp32", "gemm_tn_fp32", "gemm_nn_tf32x3", "adam", "add", "mul_backward", "relu_backward_colsum",
                "colsum", "sum", "fill", "library_tf32", "exp", "tanh", "sigmoid", "sigmoid_backward", "softmax_rows", "softmax_classes",
                "softmax_inner", "transpose", "permute_021", "permute_gather", "reduce_rows", "reduce_cols", "reduce_all_max",
                "reduce_middle", "broadcast_row", "broadcast_col", "broadcast_outer", "broadcast_mul_backward",
@@ -899,7 +899,8 @@ def run_micro(args):
         block = rng.standard_normal(1 << 24, dtype=np.float32)     # large operands repeat a 2^24-element block of random data
         fill = lambda count: np.resize(block, count)
         a, b, c = dev(fill(m * k)), dev(fill(k * nn)), empty(m * nn)
-        ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0), "gemm_nn_tf32x3": (0, 0)}[name]
+        ta, tb = {"gemm_nn": (0, 0), "gemm_nt": (0, 1), "gemm_tn": (1, 0), "gemm_nn_fp32": (0, 0), "gemm_nt_fp32": (0, 1),
+                  "gemm_tn_fp32": (1, 0), "gemm_nn_tf32x3": (0, 0)}[name]
         prec = 0 if name.endswith("fp32") else 2 if name.endswith("x3") else 1
         launch = lambda: chk(lib.launch_gemm_kernel(a, b, c, m, nn, k, ta, tb, None, 0, None, prec, None), name)
         # 3xTF32 does three tensor-core sweeps (plus the operand split) for the same algorithmic flop: its roofline is a third
