@@ -152,10 +152,15 @@ __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
                 }
             }
         } else {
+            // boustrophedon over the 8 x 8 outputs: consecutive FFMAs share one operand (a row's a value along the row, the
+            // b value at the turn), which is what the operand reuse of the register file rewards
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int jj = 0; jj < 8; ++jj) {
+                    const int j = (i & 1) ? 7 - jj : jj;
+                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                }
         }
     };
 
