@@ -476,7 +476,10 @@ __global__ void __launch_bounds__(kThreads) sgemm_mid_kernel(GemmArgs g) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int j = (i & 1) ? 3 - jj : jj;   // alternating direction: consecutive FFMAs share an operand
+                        acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                    }
             }
         }
     }
