@@ -155,12 +155,18 @@ __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
             // boustrophedon over the 8 x 8 outputs: consecutive FFMAs share one operand (a row's a value along the row, the
             // b value at the turn), which is what the operand reuse of the register file rewards
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int j = 0; j < 8; ++j) {
+                // two rows per instruction: the packed FP32 fused multiply-add of sm_100 (each half is an ordinary
+                // fmaf, so the bits are those of 64 single FFMAs) halves the instructions this issue-bound loop needs
+                const float2 bd = make_float2(bv[j], bv[j]);
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                    const int j = (i & 1) ? 7 - jj : jj;
-                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int ii = 0; ii < 4; ++ii) {
+                    const int ip = (j & 1) ? 3 - ii : ii;
+                    const float2 c = __ffma2_rn(make_float2(av[2 * ip], av[2 * ip + 1]), bd, make_float2(acc[2 * ip][j], acc[2 * ip + 1][j]));
+                    acc[2 * ip][j] = c.x;
+                    acc[2 * ip + 1][j] = c.y;
                 }
+            }
         }
     };
 
