@@ -480,12 +480,16 @@ __global__ void __launch_bounds__(kThreads) sgemm_mid_kernel(GemmArgs g) {
                     for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int j = 0; j < 4; ++j) {
+                    const float2 bd = make_float2(bv[j], bv[j]);   // two rows per packed FP32x2 fused multiply-add, as in sgemm_kernel
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const int j = (i & 1) ? 3 - jj : jj;   // alternating direction: consecutive FFMAs share an operand
-                        acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                    for (int ii = 0; ii < 2; ++ii) {
+                        const int ip = (j & 1) ? 1 - ii : ii;
+                        const float2 c = __ffma2_rn(make_float2(av[2 * ip], av[2 * ip + 1]), bd, make_float2(acc[2 * ip][j], acc[2 * ip + 1][j]));
+                        acc[2 * ip][j] = c.x;
+                        acc[2 * ip + 1][j] = c.y;
                     }
+                }
             }
         }
     }
