@@ -50,17 +50,24 @@ __device__ __forceinline__ void tile_load(float (&r)[8], const float* __restrict
         }
     }
 }
+// Column swizzle of the shared-memory tiles: in k-row p the 128 columns are stored at column ^ swz(p), which moves whole
+// groups of 8 floats inside each 32-float window by (p / 4) mod 4.  A k-contiguous operand is written as scalars, four
+// lanes of a warp holding the same column of four different groups of k-rows: without the swizzle those four hit one bank
+// (rows are 128 floats apart), with it they land in four different groups of banks.  Reads are 128-bit at multiples of
+// four columns, which the swizzle keeps whole.
+__device__ __forceinline__ int swz(int p) { return ((p >> 2) & 3) << 3; }
+
 template <bool K_CONTIG>
 __device__ __forceinline__ void tile_store(float (*sm)[BM], const float (&r)[8]) {
     const int t = threadIdx.x;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (K_CONTIG) {
-            const int x = t / 4 + 64 * h, kc = (t % 4) * 4;
+            const int kc = (t % 4) * 4, x = (t / 4 + 64 * h) ^ swz(kc);   // rows kc .. kc + 3 share one swizzle
 #pragma unroll
             for (int e = 0; e < 4; ++e) sm[kc + e][x] = r[4 * h + e];
         } else {
-            const int kr = t / 32 + 8 * h, x = (t % 32) * 4;
+            const int kr = t / 32 + 8 * h, x = ((t % 32) * 4) ^ swz(kr);
             *reinterpret_cast<float4*>(&sm[kr][x]) = make_float4(r[4 * h], r[4 * h + 1], r[4 * h + 2], r[4 * h + 3]);
         }
     }
@@ -128,10 +135,11 @@ __global__ void __launch_bounds__(kThreads, 2) sgemm_kernel(GemmArgs g) {
         tile_store<TB>(Bs[buf], rb);
     };
     auto k_step = [&](int buf, int p) {
-        float4 a0 = *reinterpret_cast<const float4*>(&As[buf][p][ty * 4]);
-        float4 a1 = *reinterpret_cast<const float4*>(&As[buf][p][64 + ty * 4]);
-        float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][p][tx * 4]);
-        float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][p][64 + tx * 4]);
+        const int ca = (ty * 4) ^ swz(p), cb = (tx * 4) ^ swz(p);
+        float4 a0 = *reinterpret_cast<const float4*>(&As[buf][p][ca]);
+        float4 a1 = *reinterpret_cast<const float4*>(&As[buf][p][64 + ca]);
+        float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][p][cb]);
+        float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][p][64 + cb]);
         float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
         float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         if (HAS_TAIL && (tail_lo || tail_hi)) {
