@@ -72,3 +72,22 @@ def test_package_does_not_import_the_oracle():
             assert "oracle" not in open(os.path.join(pkg, fn)).read(), fn
     for fn in os.listdir(os.path.join(pkg, "csrc")):
         assert "oracle" not in open(os.path.join(pkg, "csrc", fn)).read().lower(), fn
+
+
+def test_rust_binding_file_is_current_and_complete():
+    """include/train_station_b200.rs is what include/make_rust_bindings.py makes of the header today, and its extern
+    block names every declared function with the argument count the header gives (no Rust toolchain here: the file is
+    source for the reference's side, checked as text)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_rust_bindings", os.path.join(ROOT, "include", "make_rust_bindings.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text = gen.generate()
+    with open(os.path.join(ROOT, "include", "train_station_b200.rs")) as f:
+        assert f.read() == text, "run python include/make_rust_bindings.py"
+    bound = dict(re.findall(r"pub fn ([a-z_0-9]+)\((.*?)\)", text))
+    assert sorted(bound) == declared_symbols()
+    # the reference's own fifteen keep the spellings of src/cuda/mod.rs:139-208
+    assert bound["cuda_malloc"] == "size: u64" and bound["cuda_memcpy"] == "dst: *mut f32, src: *const f32, size: u64, kind: i32"
+    assert bound["launch_matmul_kernel"] == "a: *const f32, b: *const f32, result: *mut f32, m: u64, n: u64, k: u64, stream: *mut c_void"
+    assert gen.rust_type("const float* const*") == "*const *const f32" and gen.rust_type("ts_tensor* const*") == "*const *mut TsTensor"
