@@ -39,22 +39,25 @@ __device__ __forceinline__ float finish(const GemmArgs& g, float v, size_t row, 
     return v;
 }
 
-// ---- C[m x n] = A[m x k] . B[k x n], n <= NP.  A CTA takes 32 rows, a warp 4 of them at a time; the lanes split K
-// (lane l takes k = l, l + 32, ...: a warp reads 128 contiguous bytes of each row per step) and B sits in shared
-// memory in chunks of 512 rows, each row padded to a pitch that lets eight consecutive rows be read as float4 without
-// bank conflicts.  A chunk of B is fetched with all of a thread's loads in flight at once (one memory latency, not one
-// per element).  The 32 partial sums of every result are then added by a butterfly.
-template <int NP>
+// ---- C[m x n] = A[m x k] . B[k x n], n <= NP.  A warp takes R rows, a CTA 8 R; the lanes split K (lane l takes
+// k = l, l + 32, ...: a warp reads 128 contiguous bytes of each row per step, 8 R such loads in flight per lane) and B
+// sits in shared memory in chunks of KC rows, each row padded to a pitch that lets eight consecutive rows be read as
+// float4 without bank conflicts.  The 32 partial sums of every result are then added by a butterfly.  The kernel is bound
+// by memory latency, so what matters is how many loads are in flight per SM, and that depends on the size: with few rows
+// (a CTA per SM or fewer) four rows per warp and chunks of 512 rows fetched in one go are fastest (4096 rows: 9.9 us
+// against 13.2); with many rows that version's 160 registers hold an SM to one CTA and a fifth of HBM's rate, where two
+// rows per warp (about 75 registers, three or four CTAs per SM) and chunks of 1024 rows run 1.8 times as fast
+// (65536 x 10 over K = 1024: 0.113 against 0.203 ms).
+template <int NP, int R, int KC>
 __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
     constexpr int S = NP == 4 ? 4 : (NP == 16 ? 20 : 12);
-    constexpr int KC = 512;
-    constexpr int R = 4;
-    constexpr int PER = KC * NP / kThreads;   // elements of a B chunk per thread
+    constexpr int BATCH = KC * NP / kThreads <= 24 ? KC * NP / kThreads : 8;   // loads of a B chunk in flight per thread
+    static_assert((size_t)KC * S * sizeof(float) <= 48 * 1024, "a chunk of B must fit static shared memory");
     __shared__ __align__(16) float bs[KC * S];
     grid_dependency_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t M = g.m, N = g.n, K = g.k;
-    const size_t row0 = (size_t)blockIdx.x * 32 + (size_t)warp * R;
+    const size_t row0 = (size_t)blockIdx.x * (R * kThreads / 32) + (size_t)warp * R;
     const float* arow[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -69,17 +72,19 @@ __global__ void __launch_bounds__(kThreads) thin_n_nn_kernel(GemmArgs g) {
 
     for (size_t kc = 0; kc < K; kc += KC) {
         const int kn = (int)(K - kc < (size_t)KC ? K - kc : (size_t)KC);
-        float stage[PER];
-#pragma unroll
-        for (int t = 0; t < PER; ++t) {
-            const int idx = threadIdx.x + t * kThreads, kk = idx / NP, j = idx % NP;
-            stage[t] = (kk < kn && (size_t)j < N) ? __ldg(g.b + (kc + kk) * N + j) : 0.0f;
-        }
         __syncthreads();   // the previous chunk has been consumed
+        for (int base = 0; base < kn * NP; base += BATCH * kThreads) {
+            float stage[BATCH];
 #pragma unroll
-        for (int t = 0; t < PER; ++t) {
-            const int idx = threadIdx.x + t * kThreads, kk = idx / NP, j = idx % NP;
-            bs[kk * S + j] = stage[t];
+            for (int u = 0; u < BATCH; ++u) {
+                const int idx = base + threadIdx.x + u * kThreads, kk = idx / NP, j = idx % NP;
+                stage[u] = (kk < kn && (size_t)j < N) ? __ldg(g.b + (kc + kk) * N + j) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                const int idx = base + threadIdx.x + u * kThreads, kk = idx / NP, j = idx % NP;
+                if (kk < kn) bs[kk * S + j] = stage[u];
+            }
         }
         __syncthreads();
 #pragma unroll 8
@@ -177,6 +182,85 @@ __global__ void __launch_bounds__(kThreads) thin_n_tn_kernel(GemmArgs g, float* 
         float v = red[col * NP + j];
 #pragma unroll
         for (int w = 1; w < 8; ++w) v += red[(w * 32 + col) * NP + j];
+        o[e] = v;
+    }
+}
+
+// ---- The same product when A's row pitch allows 128-bit loads (m % 4 == 0, 16-byte aligned): a lane owns FOUR adjacent
+// columns of A, a CTA of four warps 128 columns over a slab of the k rows, the warps taking the slab's rows in turn with
+// four float4 loads in flight per lane.  Four times as many bytes in flight per load instruction as the kernel above and
+// small CTAs (five per SM): the kernel is bound by memory latency, and the scalar version reached a quarter of HBM's
+// rate.  K is cut into many short slabs (about four CTAs per SM), which a second launch adds in slab order.
+template <int NP>
+__global__ void __launch_bounds__(128) thin_n_tn4_kernel(GemmArgs g, float* out, unsigned rows_per_slab) {
+    constexpr int RC = 512, W = 4;                 // rows of B staged at a time; warps
+    constexpr int PER = RC * NP / 128;
+    __shared__ __align__(16) float bs[RC * NP];    // B's rows, then the warps' partial results [warp][column][j] (W * 128 * NP floats)
+    grid_dependency_sync();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t M = g.m, N = g.n, K = g.k;
+    const size_t col = (size_t)blockIdx.x * 128 + (size_t)lane * 4;
+    const size_t colc = col + 4 <= M ? col : 0;    // lanes past the end re-read the first columns and are not stored
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
+    const size_t r1 = r0 + rows_per_slab < K ? r0 + rows_per_slab : K;
+    float acc[4][NP];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) acc[c][j] = 0.0f;
+    for (size_t rc = r0; rc < r1; rc += RC) {
+        const int rn = (int)(r1 - rc < (size_t)RC ? r1 - rc : (size_t)RC);
+        __syncthreads();   // the previous chunk has been consumed
+        for (int base = 0; base < rn * NP; base += 8 * 128) {
+            float stage[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + threadIdx.x + u * 128, rr = idx / NP, j = idx % NP;
+                stage[u] = (rr < rn && (size_t)j < N) ? __ldg(g.b + (rc + rr) * N + j) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + threadIdx.x + u * 128;
+                if (idx < rn * NP) bs[idx] = stage[u];
+            }
+        }
+        __syncthreads();
+        const float* ap = g.a + rc * M + colc;
+#pragma unroll 4
+        for (int rr = warp; rr < rn; rr += W) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(ap + (size_t)rr * M));
+            const float4* bp = reinterpret_cast<const float4*>(bs + rr * NP);
+#pragma unroll
+            for (int q = 0; q < NP / 4; ++q) {
+                const float4 b = bp[q];
+                const float bq[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    acc[0][q * 4 + e] = fmaf(a.x, bq[e], acc[0][q * 4 + e]);
+                    acc[1][q * 4 + e] = fmaf(a.y, bq[e], acc[1][q * 4 + e]);
+                    acc[2][q * 4 + e] = fmaf(a.z, bq[e], acc[2][q * 4 + e]);
+                    acc[3][q * 4 + e] = fmaf(a.w, bq[e], acc[3][q * 4 + e]);
+                }
+            }
+        }
+    }
+    (void)PER;
+    __syncthreads();   // bs is reused for the warps' partial results
+    float* red = bs;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) red[((size_t)warp * 128 + lane * 4 + c) * NP + j] = acc[c][j];
+    __syncthreads();
+    // 128 columns x n results, added over the warps in warp order and written as one contiguous run of the slab
+    float* o = out + (size_t)blockIdx.y * M * N + (size_t)blockIdx.x * 128 * N;
+    const size_t cols_here = M - (size_t)blockIdx.x * 128 < 128 ? M - (size_t)blockIdx.x * 128 : 128;
+    const size_t valid = cols_here * N;
+    for (size_t e = threadIdx.x; e < valid; e += 128) {
+        const size_t c = e / N, j = e % N;
+        float v = red[c * NP + j];
+#pragma unroll
+        for (int w = 1; w < W; ++w) v += red[((size_t)w * 128 + c) * NP + j];
         o[e] = v;
     }
 }
@@ -287,13 +371,23 @@ int thin_case(const GemmArgs& g) {
 
 template <int NP>
 bool launch_nn(const GemmArgs& g, cudaStream_t s) {
-    launch_dep(thin_n_nn_kernel<NP>, dim3((unsigned)((g.m + 31) / 32)), dim3(kThreads), 0, s, g);
+    if (g.m >= 16384) {   // many rows: small CTAs, several per SM
+        constexpr int KC = NP == 4 ? 3072 : (NP == 16 ? 512 : 1024);
+        launch_dep(thin_n_nn_kernel<NP, 2, KC>, dim3((unsigned)((g.m + 15) / 16)), dim3(kThreads), 0, s, g);
+    } else {
+        launch_dep(thin_n_nn_kernel<NP, 4, 512>, dim3((unsigned)((g.m + 31) / 32)), dim3(kThreads), 0, s, g);
+    }
     return cuda_ok(cudaGetLastError(), "thin GEMM (NN) launch");
 }
 template <int NP>
 bool launch_tn(const GemmArgs& g, float* out, unsigned col_blocks, unsigned slabs, unsigned rows_per_slab, cudaStream_t s) {
     launch_dep(thin_n_tn_kernel<NP>, dim3(col_blocks, slabs), dim3(kThreads), 0, s, g, out, rows_per_slab);
     return cuda_ok(cudaGetLastError(), "thin GEMM (TN) launch");
+}
+template <int NP>
+bool launch_tn4(const GemmArgs& g, float* out, unsigned col_blocks, unsigned slabs, unsigned rows_per_slab, cudaStream_t s) {
+    launch_dep(thin_n_tn4_kernel<NP>, dim3(col_blocks, slabs), dim3(128), 0, s, g, out, rows_per_slab);
+    return cuda_ok(cudaGetLastError(), "thin GEMM (TN, 128-bit loads) launch");
 }
 template <int KP>
 bool launch_nt(const GemmArgs& g, cudaStream_t s) {
@@ -347,10 +441,16 @@ bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
         const size_t kp = (g.k + 3) / 4 * 4;
         return kp == 4 ? launch_nt<4>(g, s) : kp == 8 ? launch_nt<8>(g, s) : kp == 12 ? launch_nt<12>(g, s) : launch_nt<16>(g, s);
     }
-    // weight-gradient layout: enough slabs of the long reduction to give every SM about two CTAs, at least 64 rows each
-    const size_t col_blocks = (g.m + 31) / 32;
-    size_t slabs = (size_t)c->sm_count * 2 / col_blocks;
-    if (slabs > g.k / 64) slabs = g.k / 64;
+    // weight-gradient layout: K is cut into slabs whose partial results a second launch adds in slab order.  With 128-bit
+    // loads (m % 4 == 0, aligned A): 128 columns and 128 threads per CTA, about four CTAs per SM, at least 32 rows a slab;
+    // otherwise 32 columns and 256 threads per CTA, about two CTAs per SM, at least 64 rows a slab.
+    // (a reduction of a few thousand rows is faster on the first kernel with its few slabs: 10.0 against 13.3 us for
+    // 1024 x 10 over K = 4096; over K = 65536 the second one takes 0.089 against 0.156 ms)
+    const bool wide = g.m % 4 == 0 && al16(g.a) && g.k >= 16384;
+    const size_t col_blocks = wide ? (g.m + 127) / 128 : (g.m + 31) / 32;
+    size_t slabs = (size_t)c->sm_count * (wide ? 4 : 2) / col_blocks;
+    const size_t min_rows = wide ? 32 : 64;
+    if (slabs > g.k / min_rows) slabs = g.k / min_rows;
     if (slabs > 65535) slabs = 65535;
     if (slabs < 1) slabs = 1;
     size_t rows_per_slab = (g.k + slabs - 1) / slabs;
@@ -367,13 +467,17 @@ bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     bool ok;
     {
         ProfScope prof(kProfGemmFp32, s, flop);
-        ok = np == 4    ? launch_tn<4>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
-             : np == 8  ? launch_tn<8>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
-             : np == 12 ? launch_tn<12>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s)
-                        : launch_tn<16>(g, out, (unsigned)col_blocks, (unsigned)slabs, (unsigned)rows_per_slab, s);
+        const unsigned cb = (unsigned)col_blocks, sl = (unsigned)slabs, rps = (unsigned)rows_per_slab;
+        if (wide)
+            ok = np == 4 ? launch_tn4<4>(g, out, cb, sl, rps, s) : np == 8 ? launch_tn4<8>(g, out, cb, sl, rps, s)
+                 : np == 12 ? launch_tn4<12>(g, out, cb, sl, rps, s) : launch_tn4<16>(g, out, cb, sl, rps, s);
+        else
+            ok = np == 4 ? launch_tn<4>(g, out, cb, sl, rps, s) : np == 8 ? launch_tn<8>(g, out, cb, sl, rps, s)
+                 : np == 12 ? launch_tn<12>(g, out, cb, sl, rps, s) : launch_tn<16>(g, out, cb, sl, rps, s);
     }
     if (part) {
-        ok = ok && sum_slabs(part, g.c, mn, slabs, s);
+        // many slabs of a small result: lanes along the outputs, warps along the slabs (contiguous reads); few: one thread per output
+        ok = ok && (slabs > 8 && mn >= 1024 ? colsum_finish(part, g.c, mn, slabs, s) : sum_slabs(part, g.c, mn, slabs, s));
         if (s != c->compute) cudaStreamSynchronize(s);
         c->alloc.free(part);
     }
