@@ -39,7 +39,7 @@ def _exact(a, b):
 
 # forward layout: [m x k] . [k x n], n <= 16
 @pytest.mark.parametrize("m,n,k", [(4096, 10, 1024), (256, 1, 128), (259, 3, 130), (1000, 4, 513), (300, 12, 1500), (2049, 16, 1027),
-                                   (257, 7, 512), (65536 + 5, 10, 256)])
+                                   (257, 7, 512), (65536 + 5, 10, 256), (16384 + 3, 12, 2500), (20000, 16, 700)])
 def test_narrow_result_forward_layout(gpu, m, n, k):
     rng = np.random.default_rng(m + n + k)
     a, b = _ints(rng, (m, k)), _ints(rng, (k, n))
@@ -57,7 +57,8 @@ def test_narrow_result_forward_layout(gpu, m, n, k):
 
 
 # weight-gradient layout: [k x m]^T . [k x n], n <= 16, k the long reduction
-@pytest.mark.parametrize("m,n,k", [(1024, 10, 4096), (64, 1, 256), (1000, 5, 4099), (70, 16, 300), (513, 12, 777), (256, 8, 65536)])
+@pytest.mark.parametrize("m,n,k", [(1024, 10, 4096), (64, 1, 256), (1000, 5, 4099), (70, 16, 300), (513, 12, 777), (256, 8, 65536),
+                                   (1000, 10, 16400), (132, 16, 20000), (1001, 3, 16384)])
 def test_narrow_result_weight_gradient_layout(gpu, m, n, k):
     rng = np.random.default_rng(m * 3 + n + k)
     a, b = _ints(rng, (m, k), 3), _ints(rng, (k, n), 3)
