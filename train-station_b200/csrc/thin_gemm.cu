@@ -22,7 +22,9 @@ namespace {
 
 constexpr int kThin = 16;
 constexpr int kThreads = 256;
-constexpr int kNtRows = 16;   // result rows per CTA of the short-reduction kernel
+// result rows per CTA of the short-reduction kernel: 16, or 64 when there are many rows (a thread fetches its 4 x k
+// values of B once per CTA, which 16 rows of work do not amortise; on 4096 rows 64 would leave most SMs without a CTA)
+inline int nt_rows(size_t m) { return m >= 32768 ? 64 : 16; }
 
 __device__ __forceinline__ float rn_tf32(float x) {
     uint32_t r;
@@ -266,12 +268,13 @@ __global__ void __launch_bounds__(128) thin_n_tn4_kernel(GemmArgs g, float* out,
 }
 
 // ---- C[m x n] = A[m x k] . B[n x k]^T, k <= KP.  A thread owns four consecutive result columns and keeps their four
-// rows of B in registers; a CTA covers 16 result rows (A's 16 rows sit in shared memory and are read by all threads at
+// rows of B in registers; a CTA covers ROWS result rows (A's rows sit in shared memory and are read by all threads at
 // once) by 1024 columns.  Every result is finished (bias, ReLU, mask, rounding) and stored as it is made, a row of
-// 4 KiB per step of the CTA; the column sums of the stored values over the CTA's 16 rows go to row blockIdx.x of
+// 4 KiB per step of the CTA; the column sums of the stored values over the CTA's rows go to row blockIdx.x of
 // g.colsum_partial when that is set.  VEC: n % 4 == 0 and C and the mask are 16-byte aligned (float4 stores and loads).
-template <int KP, bool VEC>
+template <int KP, bool VEC, int ROWS>
 __global__ void __launch_bounds__(kThreads) thin_k_nt_kernel(GemmArgs g) {
+    constexpr int kNtRows = ROWS;
     __shared__ __align__(16) float as[kNtRows * KP];
     grid_dependency_sync();
     const size_t M = g.m, N = g.n, K = g.k;
@@ -391,10 +394,16 @@ bool launch_tn4(const GemmArgs& g, float* out, unsigned col_blocks, unsigned sla
 }
 template <int KP>
 bool launch_nt(const GemmArgs& g, cudaStream_t s) {
-    const dim3 grid((unsigned)((g.m + kNtRows - 1) / kNtRows), (unsigned)((g.n + 1023) / 1024));
+    const int rows = nt_rows(g.m);
+    const dim3 grid((unsigned)((g.m + rows - 1) / rows), (unsigned)((g.n + 1023) / 1024));
     const bool vec = g.n % 4 == 0 && al16(g.c) && (!g.mask || al16(g.mask));
-    if (vec) launch_dep(thin_k_nt_kernel<KP, true>, grid, dim3(kThreads), 0, s, g);
-    else launch_dep(thin_k_nt_kernel<KP, false>, grid, dim3(kThreads), 0, s, g);
+    if (rows == 64) {
+        if (vec) launch_dep(thin_k_nt_kernel<KP, true, 64>, grid, dim3(kThreads), 0, s, g);
+        else launch_dep(thin_k_nt_kernel<KP, false, 64>, grid, dim3(kThreads), 0, s, g);
+    } else {
+        if (vec) launch_dep(thin_k_nt_kernel<KP, true, 16>, grid, dim3(kThreads), 0, s, g);
+        else launch_dep(thin_k_nt_kernel<KP, false, 16>, grid, dim3(kThreads), 0, s, g);
+    }
     return cuda_ok(cudaGetLastError(), "thin GEMM (NT) launch");
 }
 
@@ -410,7 +419,7 @@ bool gemm_thin(const GemmArgs& g, DeviceCtx* c, cudaStream_t s) {
     if (g.colsum_out && !(which == 3 && g.colsum_partial)) {
         if (which == 3) {
             // column sums of the stored result: one partial row per CTA row of the kernel, added in row order
-            const size_t prow = (g.m + kNtRows - 1) / kNtRows;
+            const size_t prow = (g.m + nt_rows(g.m) - 1) / nt_rows(g.m);
             float* part = c->alloc.alloc(prow * g.n * sizeof(float));
             if (!part) return false;
             GemmArgs h = g;
